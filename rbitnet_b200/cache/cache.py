@@ -1,0 +1,148 @@
+"""Device storage of the cache: pages of keys and values per group of layers, page
+tables, and the fixed-size per-sequence state area.
+
+Layout of one group: ``pool[layer in group][0=k,1=v][page][kv head][position in page][head_dim]``
+in the engine's compute dtype.  A kv head's page is one contiguous
+[page_size, head_dim] tile.  ``table[slot][i]`` is the page that holds the
+slot's positions i*page_size .. (i+1)*page_size-1.
+
+State area: for every schedule entry whose mixer declares a ``StateNeed``, a
+tensor [n_slots, *shape]; a slot's rows are zeroed when the slot is given out.
+The Llama decoder needs none, so the area is empty for it.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..parts.base import CacheNeed, StateNeed
+from .allocator import SlotBook, CacheFull, ContextOverflow  # noqa: F401
+
+PAGE_SIZE = 64
+
+
+@dataclass
+class CacheLayerView:
+    """What a mixer sees of the cache for one run of a layer."""
+    k: torch.Tensor            # [n_pages, kv heads, page_size, head_dim]
+    v: torch.Tensor
+    page_table: torch.Tensor   # int32 [n_slots, max_pages], on the device
+    max_pages: int
+    page_size: int
+    n_kv_heads: int
+    head_dim: int
+    writes: bool               # False: this run reads what another run wrote
+    group: int
+
+
+class CacheGroup:
+    def __init__(self, need: CacheNeed, entries: List[int], n_pages: int, n_slots: int, max_pages: int,
+                 page_size: int, dtype, device):
+        self.need, self.entries = need, entries
+        self.n_pages = n_pages
+        self.pool = torch.zeros((len(entries), 2, n_pages, need.n_kv_heads, page_size, need.head_dim),
+                                dtype=dtype, device=device)
+        self.table_host = np.zeros((n_slots, max_pages), dtype=np.int32)
+        self.table = torch.zeros((n_slots, max_pages), dtype=torch.int32, device=device)
+        self.dirty = set()
+
+    def bytes(self) -> int:
+        return self.pool.numel() * self.pool.element_size()
+
+
+class SequenceCache:
+    """Slots for sequences; keys and values for each cached run of a layer; per-sequence state."""
+
+    def __init__(self, cache_needs: Dict[int, CacheNeed], reads: Dict[int, int],
+                 state_needs: Dict[int, StateNeed], max_tokens: int, max_seq: int, dtype, device,
+                 page_size: int = PAGE_SIZE, n_slots: Optional[int] = None):
+        """cache_needs: schedule entry -> need, for entries that write their own keys and values.
+        reads: schedule entry -> the entry whose cache it reads.  max_tokens: the most positions
+        all live sequences hold together, each rounded up to whole pages."""
+        self.page_size = page_size
+        self.max_seq = max_seq
+        self.max_pages = -(-max_seq // page_size)
+        n_pages = max(1, -(-max_tokens // page_size))
+        self.n_slots = n_slots if n_slots is not None else n_pages
+        self.device, self.dtype = device, dtype
+        by_need: Dict[CacheNeed, List[int]] = {}
+        for entry in sorted(cache_needs):
+            by_need.setdefault(cache_needs[entry], []).append(entry)
+        self.groups: List[CacheGroup] = [
+            CacheGroup(need, entries, n_pages, self.n_slots, self.max_pages, page_size, dtype, device)
+            for need, entries in by_need.items()]
+        self._where: Dict[int, tuple] = {}
+        for g, grp in enumerate(self.groups):
+            for i, entry in enumerate(grp.entries):
+                self._where[entry] = (g, i, True)
+        for entry, src in reads.items():
+            if src not in self._where or not self._where[src][2]:
+                raise ValueError(f"schedule entry {entry} reads the cache of entry {src}, which writes none")
+            g, i, _ = self._where[src]
+            self._where[entry] = (g, i, False)
+        self.book = SlotBook(self.n_slots, [grp.n_pages for grp in self.groups], page_size, max_seq)
+        self.states: Dict[int, torch.Tensor] = {
+            entry: torch.zeros((self.n_slots, *need.shape), dtype=need.dtype, device=device)
+            for entry, need in state_needs.items()}
+
+    # ---- slots
+    def alloc(self) -> int:
+        slot = self.book.alloc()
+        for st in self.states.values():
+            st[slot].zero_()
+        return slot
+
+    def free(self, slot: int) -> None:
+        self.book.free(slot)
+
+    def length(self, slot: int) -> int:
+        return self.book.length[slot]
+
+    def reserve(self, slot: int, n_new: int) -> None:
+        added = self.book.reserve(slot, n_new)
+        for g, pages in enumerate(added):
+            if pages:
+                have = len(self.book.pages[slot][g])
+                self.groups[g].table_host[slot, have - len(pages):have] = pages
+                self.groups[g].dirty.add(slot)
+
+    def advance(self, slot: int, n_new: int) -> None:
+        self.book.advance(slot, n_new)
+
+    def fits(self, lengths) -> bool:
+        """Whether new sequences that grow to these lengths fit beside what is live now."""
+        if len(lengths) > self.book.slots.n_free:
+            return False
+        pages = sum(-(-int(n) // self.page_size) for n in lengths)
+        return all(pages <= pool.n_free for pool in self.book.pools)
+
+    def upload_tables(self) -> None:
+        """Bring the device page tables up to date (rows that changed since the last call)."""
+        for g, grp in enumerate(self.groups):
+            for slot in sorted(grp.dirty):
+                n = len(self.book.pages[slot][g]) if slot in self.book.pages else 0
+                if n:
+                    # a pageable copy: staged by the driver before it returns, so the
+                    # host row may change again at once
+                    grp.table[slot, :n].copy_(torch.from_numpy(grp.table_host[slot, :n].copy()))
+            grp.dirty.clear()
+
+    # ---- views
+    def view(self, entry: int) -> CacheLayerView:
+        g, i, writes = self._where[entry]
+        grp = self.groups[g]
+        return CacheLayerView(grp.pool[i, 0], grp.pool[i, 1], grp.table, self.max_pages, self.page_size,
+                              grp.need.n_kv_heads, grp.need.head_dim, writes, g)
+
+    def has_view(self, entry: int) -> bool:
+        return entry in self._where
+
+    def state(self, entry: int) -> Optional[torch.Tensor]:
+        return self.states.get(entry)
+
+    def bytes(self) -> int:
+        return sum(g.bytes() for g in self.groups) + sum(s.numel() * s.element_size()
+                                                          for s in self.states.values())

@@ -1,0 +1,228 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, rotation of q and k
+// with the append to the paged cache, SiLU(gate)*up, and row gather.
+// All arithmetic is float32 whatever the storage dtype.
+#include "rb_common.cuh"
+
+#include <stdarg.h>
+#include <string.h>
+
+static thread_local char g_error[512];
+
+void rb_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+RB_EXPORT const char* rb_last_error() { return g_error; }
+
+RB_EXPORT int rb_abi_version() { return 1; }
+
+// ---------------------------------------------------------------- embedding
+// x[t, :] = table[ids[t], :] as float32 (crates/bitnet-core/src/llama/model.rs:230-232).
+// An id outside [0, V) is refused on the host before the launch; the kernel
+// writes zeros for one rather than read outside the table.
+template <typename TW>
+__global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                             const int* __restrict__ ids, int E, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < V;
+  const TW* row = table + (int64_t)(ok ? id : 0) * E;
+  float* o = out + (int64_t)t * E;
+  for (int j = threadIdx.x; j < E; j += blockDim.x) o[j] = ok ? rb_to_float<TW>(row[j]) : 0.f;
+}
+
+RB_EXPORT int rb_embed(float* out, const void* table, int table_dtype, const int* ids, int T, int E,
+                       int V, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(T > 0 && E > 0 && V > 0, "rb_embed: bad sizes T=%d E=%d V=%d", T, E, V);
+  const int threads = E >= 1024 ? 256 : 128;
+  if (table_dtype == RB_F32)
+    embed_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, E, V);
+  else if (table_dtype == RB_BF16)
+    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, E, V);
+  else
+    RB_FAIL("rb_embed: unknown dtype %d", table_dtype);
+  RB_CHECK_LAUNCH("rb_embed");
+  return 0;
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * w / sqrt(mean(x^2) + eps)  (crates/bitnet-core/src/llama/model.rs:93-100).
+// x is the float32 residual stream.  When `partials` is given, x first takes
+// in the sum of `n_partials` float32 slices [n_partials][T][E] (the pieces of a
+// matrix product that was split along its inner dimension) and the updated x is
+// written back, so the residual add and the norm read the row once.
+template <typename TO>
+__global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const float* __restrict__ w,
+                               const float* __restrict__ partials, int n_partials, int64_t partial_stride,
+                               int E, float eps) {
+  __shared__ float scratch[33];
+  extern __shared__ float row[];  // E floats
+  const int t = blockIdx.x;
+  float* xr = x + (int64_t)t * E;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < E; j += blockDim.x) {
+    float v = xr[j];
+    if (partials) {
+      for (int p = 0; p < n_partials; ++p) v += partials[p * partial_stride + (int64_t)t * E + j];
+      xr[j] = v;
+    }
+    row[j] = v;
+    ss += v * v;
+  }
+  ss = rb_block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / (float)E + eps);
+  TO* o = out + (int64_t)t * E;
+  for (int j = threadIdx.x; j < E; j += blockDim.x) o[j] = rb_from_float<TO>(row[j] * w[j] * r);
+}
+
+RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, const float* partials,
+                         int n_partials, int T, int E, float eps, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(T > 0 && E > 0, "rb_rmsnorm: bad sizes T=%d E=%d", T, E);
+  RB_REQUIRE((size_t)E * 4 <= 200 * 1024, "rb_rmsnorm: width %d exceeds the %d floats one block can hold",
+             E, 200 * 1024 / 4);
+  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
+  const size_t smem = (size_t)E * sizeof(float);
+  const int64_t pstride = (int64_t)T * E;
+  if (out_dtype == RB_F32) {
+    if (smem > 48 * 1024)
+      RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rmsnorm_kernel<float><<<T, threads, smem, stream>>>((float*)out, x, w, partials, n_partials, pstride, E, eps);
+  } else if (out_dtype == RB_BF16) {
+    if (smem > 48 * 1024)
+      RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    rmsnorm_kernel<__nv_bfloat16><<<T, threads, smem, stream>>>((__nv_bfloat16*)out, x, w, partials, n_partials,
+                                                               pstride, E, eps);
+  } else {
+    RB_FAIL("rb_rmsnorm: unknown dtype %d", out_dtype);
+  }
+  RB_CHECK_LAUNCH("rb_rmsnorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------- rotation + cache append
+// For every new token: rotate each q head and each k head by the token's
+// position (angle = pos * inv_freq[i], float32; pairs (2i,2i+1) when
+// `interleaved`, else (i, i+D/2)), write q to q_out[T,H,D], the rotated k and
+// the raw v to the token's place in the paged cache.
+// crates/bitnet-core/src/llama/model.rs:122-136 (rotation), :242-257 (append).
+// `qkv` rows hold [H*D | Kh*D | Kh*D]; with write_kv == 0 only q is read (a
+// layer that reads another layer's cache).  The whole head is rotated
+// (rot_dim == D); a rotated prefix is refused by the entry point.
+template <typename T>
+__global__ void rotate_append_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, int64_t qkv_stride,
+                                     const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
+                                     int rot_dim, int interleaved) {
+  const int t = blockIdx.x;
+  const int D = cache.head_dim, Kh = cache.n_kv_heads;
+  const int pos = tok_pos[t];
+  const int slot = tok_slot[t];
+  const T* row = qkv + (int64_t)t * qkv_stride;
+  const int half = D / 2;
+  const int n_rot_heads = H + (write_kv ? Kh : 0);
+  T* kdst = (T*)cache.k;
+  T* vdst = (T*)cache.v;
+  // q and k heads: one thread per pair
+  for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
+    const int head = idx / half, i = idx % half;
+    int a, b;
+    if (interleaved) { a = 2 * i; b = 2 * i + 1; } else { a = i; b = i + half; }
+    const T* src = row + (int64_t)head * D;  // q heads, then k heads, are contiguous
+    float x0 = rb_to_float<T>(src[a]);
+    float x1 = rb_to_float<T>(src[b]);
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    const float y0 = x0 * c - x1 * s;
+    const float y1 = x0 * s + x1 * c;
+    if (head < H) {
+      T* dst = q_out + ((int64_t)t * H + head) * D;
+      dst[a] = rb_from_float<T>(y0);
+      dst[b] = rb_from_float<T>(y1);
+    } else {
+      T* dst = kdst + rb_page_offset(cache, slot, pos, head - H);
+      dst[a] = rb_from_float<T>(y0);
+      dst[b] = rb_from_float<T>(y1);
+    }
+  }
+  if (write_kv) {
+    const T* vsrc = row + (int64_t)(H + Kh) * D;
+    for (int idx = threadIdx.x; idx < Kh * D; idx += blockDim.x) {
+      const int kvh = idx / D, d = idx % D;
+      vdst[rb_page_offset(cache, slot, pos, kvh) + d] = vsrc[idx];
+    }
+  }
+}
+
+RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride, int dtype,
+                               const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
+                               void* cache_v, const int* page_table, int max_pages, int page_size, int T, int H,
+                               int Kh, int D, int write_kv, int rot_dim, int interleaved, cudaStream_t stream) {
+  if (T == 0) return 0;
+  RB_REQUIRE(D % 2 == 0 && D > 0, "rb_rotate_append: head_dim %d must be even", D);
+  RB_REQUIRE(rot_dim == D, "rb_rotate_append: a rotated prefix of %d of %d is not built", rot_dim, D);
+  RB_REQUIRE(H > 0 && Kh >= 0 && page_size > 0, "rb_rotate_append: bad sizes H=%d Kh=%d page=%d", H, Kh, page_size);
+  RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
+  const int threads = 256;
+  if (dtype == RB_F32)
+    rotate_append_kernel<float><<<T, threads, 0, stream>>>((float*)q_out, (const float*)qkv, qkv_stride, inv_freq,
+                                                           tok_pos, tok_slot, c, H, write_kv, rot_dim, interleaved);
+  else if (dtype == RB_BF16)
+    rotate_append_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv,
+                                                                   qkv_stride, inv_freq, tok_pos, tok_slot, c, H,
+                                                                   write_kv, rot_dim, interleaved);
+  else
+    RB_FAIL("rb_rotate_append: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_rotate_append");
+  return 0;
+}
+
+// ---------------------------------------------------------------- SiLU(gate) * up
+// out[t, j] = silu(gu[t, j]) * gu[t, F + j], silu(v) = v / (1 + exp(-v)), in float32.
+// crates/bitnet-core/src/llama/model.rs:116-120, 297-302
+template <typename T>
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int F) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / F;
+    const int j = (int)(i % F);
+    const float g = rb_to_float<T>(gu[t * 2 * F + j]);
+    const float u = rb_to_float<T>(gu[t * 2 * F + F + j]);
+    out[i] = rb_from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int T, int F, cudaStream_t stream) {
+  if (T == 0) return 0;
+  const int64_t n = (int64_t)T * F;
+  const int threads = 256;
+  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+  if (dtype == RB_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, n, F);
+  else if (dtype == RB_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out,
+                                                                  (const __nv_bfloat16*)gate_up, n, F);
+  else
+    RB_FAIL("rb_silu_mul: unknown dtype %d", dtype);
+  RB_CHECK_LAUNCH("rb_silu_mul");
+  return 0;
+}
+
+// ---------------------------------------------------------------- row gather (float32 residual rows)
+__global__ void gather_rows_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                   const int* __restrict__ rows, int E) {
+  const int r = blockIdx.x;
+  const float* src = x + (int64_t)rows[r] * E;
+  float* dst = out + (int64_t)r * E;
+  for (int j = threadIdx.x; j < E; j += blockDim.x) dst[j] = src[j];
+}
+
+RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R, int E, cudaStream_t stream) {
+  if (R == 0) return 0;
+  gather_rows_kernel<<<R, 256, 0, stream>>>(out, x, rows, E);
+  RB_CHECK_LAUNCH("rb_gather_rows");
+  return 0;
+}

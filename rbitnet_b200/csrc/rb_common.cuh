@@ -1,0 +1,116 @@
+// Shared helpers of the rbitnet_b200 kernels (sm_100a only).
+//
+// Every exported entry point is `extern "C"`, takes raw device pointers, sizes
+// and the stream to launch on, and returns 0 or a negative code; the message
+// of the last failure of the calling thread is read with rb_last_error().
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define RB_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum RbDtype { RB_F32 = 0, RB_BF16 = 1 };
+
+void rb_set_error(const char* fmt, ...);
+
+#define RB_FAIL(...)                 \
+  do {                               \
+    rb_set_error(__VA_ARGS__);       \
+    return -1;                       \
+  } while (0)
+
+#define RB_REQUIRE(cond, ...)        \
+  do {                               \
+    if (!(cond)) RB_FAIL(__VA_ARGS__); \
+  } while (0)
+
+#define RB_CHECK_LAUNCH(name)                                                     \
+  do {                                                                            \
+    cudaError_t e__ = cudaGetLastError();                                         \
+    if (e__ != cudaSuccess) RB_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define RB_CUDA(call)                                                             \
+  do {                                                                            \
+    cudaError_t e__ = (call);                                                     \
+    if (e__ != cudaSuccess) RB_FAIL("%s failed: %s", #call, cudaGetErrorString(e__)); \
+  } while (0)
+
+// ---------------------------------------------------------------- scalar conversions
+template <typename T> __device__ __forceinline__ float rb_to_float(T v);
+template <> __device__ __forceinline__ float rb_to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float rb_to_float<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T rb_from_float(float v);
+template <> __device__ __forceinline__ float rb_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 rb_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// ---------------------------------------------------------------- reductions
+__device__ __forceinline__ float rb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float rb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 33 floats of shared
+// memory.  All threads get the result.
+__device__ __forceinline__ float rb_block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = rb_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = rb_warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+__device__ __forceinline__ float rb_block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = rb_warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : -INFINITY;
+    t = rb_warp_max(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// ---------------------------------------------------------------- paged cache addressing
+// One layer's keys (or values) live in pages of `page_size` positions:
+//   base[page][kv_head][position in page][d]
+// and a sequence's pages are listed in its row of the page table.
+struct RbPagedLayer {
+  void* k;                 // keys of this layer
+  void* v;                 // values of this layer
+  const int* page_table;   // [n_slots, max_pages]
+  int max_pages;           // row length of the page table
+  int page_size;           // positions per page
+  int n_kv_heads;
+  int head_dim;
+};
+
+__device__ __forceinline__ int64_t rb_page_offset(const RbPagedLayer& c, int slot, int pos, int kvh) {
+  const int page = c.page_table[(int64_t)slot * c.max_pages + pos / c.page_size];
+  return (((int64_t)page * c.n_kv_heads + kvh) * c.page_size + pos % c.page_size) * c.head_dim;
+}

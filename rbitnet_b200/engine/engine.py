@@ -1,0 +1,195 @@
+"""Engine: the entry point a program uses.  A model folder (or a configuration and a
+seed) in, token ids out.
+
+It keeps the reference façade's names where the reference has them
+(crates/bitnet-core/src/inference.rs:75-209): ``Engine.load_path``,
+``Engine.from_env`` (RBITNET_MODEL, and RBITNET_TOY / RBITNET_TOY_SEED for
+seeded random weights without a file), ``complete(prompt, max_tokens,
+temperature)``, ``is_ready``, ``model_summary``, ``tensor_count``,
+``tensor_names_preview``.  ``generate`` is the batched, ids-in ids-out call the
+reference lacks.
+"""
+from __future__ import annotations
+
+import os
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import models  # noqa: F401  (registers the architectures)
+from ..cache import SequenceCache, PAGE_SIZE
+from ..config import ModelConfig, load_config, get_architecture, config_from_dict, ConfigError
+from ..weights import read_model_tensors, random_tensors
+from .generate import GenerationLoop, GenerationResult
+from .model import Model
+from .step import Stepper, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, "f32": torch.float32}
+
+
+class TokenizerMissing(RuntimeError):
+    """``complete`` needs tokenizer.json beside the model, or RBITNET_TOKENIZER
+    (crates/bitnet-core/src/inference.rs:55-71)."""
+
+
+def _dtype(d):
+    if isinstance(d, torch.dtype):
+        return d
+    if d not in _DTYPES:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, found {d!r}")
+    return _DTYPES[d]
+
+
+def _no_parent_components(path) -> None:
+    # crates/bitnet-core/src/inference.rs:44-53
+    if ".." in Path(path).parts:
+        raise ValueError("path must not contain '..' components")
+
+
+class Engine:
+    def __init__(self, config: ModelConfig, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
+                 device="cuda:0", max_tokens: Optional[int] = None, max_seq: Optional[int] = None,
+                 max_batch: int = 64, page_size: int = PAGE_SIZE, max_batch_tokens: int = 8192,
+                 ops=None, model_path: Optional[Path] = None, verbose: bool = False):
+        """max_seq: longest sequence (default: the configuration's max positions).
+        max_tokens: cache size in positions over all live sequences, each rounded up to
+        whole pages (default: max_batch sequences of max_seq)."""
+        from ..kernels.ops import CudaOps
+        self.config = config
+        self.model_path = model_path
+        self.dtype = _dtype(dtype)
+        self.ops = ops if ops is not None else CudaOps(self.dtype, device, verbose_build=verbose)
+        self.spec = get_architecture(config.architecture).build_spec(config)
+        self._tensor_names = sorted(tensors)
+        self.model = Model(self.spec, tensors, self.ops)
+        self.max_seq = int(max_seq or self.spec.max_positions)
+        if self.max_seq > self.spec.max_positions:
+            raise ValueError(f"max_seq {self.max_seq} exceeds the model's max positions "
+                             f"{self.spec.max_positions}")
+        self.max_batch = max_batch
+        if max_tokens is None:
+            max_tokens = max_batch * (-(-self.max_seq // page_size) * page_size)
+        cache_needs, reads, state_needs = self.model.cache_plan()
+        self.cache = SequenceCache(cache_needs, reads, state_needs, max_tokens, self.max_seq, self.dtype,
+                                   self.ops.device, page_size=page_size)
+        self.stepper = Stepper(self.model, self.cache, self.ops, max_batch_tokens=max_batch_tokens)
+        self.stop_ids = list(self.spec.stop_ids)
+        self._tokenizer = None
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def load_path(cls, path, **kw) -> "Engine":
+        """A model folder with config.json and model.safetensors."""
+        path = Path(path)
+        config = load_config(path)
+        tensors = read_model_tensors(path)
+        return cls(config, tensors, model_path=path, **kw)
+
+    from_pretrained = load_path
+
+    @classmethod
+    def from_random(cls, config, seed: int = 42, **kw) -> "Engine":
+        """Seeded random weights, made in memory (no file)."""
+        if isinstance(config, dict):
+            config = config_from_dict(config)
+        spec = get_architecture(config.architecture).build_spec(config)
+        dtype = _dtype(kw.get("dtype", "bfloat16"))
+        dev = kw.get("device", "cuda:0") if torch.cuda.is_available() and kw.get("ops") is None else "cpu"
+        tensors = random_tensors(spec, seed, dtype=dtype, device=dev)
+        return cls(config, tensors, **kw)
+
+    @classmethod
+    def from_env(cls, **kw) -> "Engine":
+        """RBITNET_MODEL: a model folder.  Else RBITNET_TOY=1 with RBITNET_TOY_CONFIG
+        (a config.json) and RBITNET_TOY_SEED (default 42): random weights."""
+        path = os.environ.get("RBITNET_MODEL")
+        if path:
+            _no_parent_components(path)
+            return cls.load_path(path, **kw)
+        if os.environ.get("RBITNET_TOY") in ("1", "true", "yes"):
+            cfg_path = os.environ.get("RBITNET_TOY_CONFIG")
+            if not cfg_path:
+                raise ConfigError("RBITNET_TOY needs RBITNET_TOY_CONFIG, the config.json to draw weights for")
+            _no_parent_components(cfg_path)
+            import json
+            seed = int(os.environ.get("RBITNET_TOY_SEED", "42"))
+            return cls.from_random(json.loads(Path(cfg_path).read_text()), seed, **kw)
+        raise ConfigError("model not loaded: set RBITNET_MODEL (or RBITNET_TOY and RBITNET_TOY_CONFIG)")
+
+    # ------------------------------------------------------------------ information
+    def is_ready(self) -> bool:
+        return True
+
+    def tensor_count(self) -> int:
+        return len(self._tensor_names)
+
+    def tensor_names_preview(self, max_names: int) -> List[str]:
+        return self._tensor_names[:max_names]
+
+    def model_summary(self) -> str:
+        c = self.config
+        n = sum(int(np.prod(s)) for s in self.spec.expected_shapes().values())
+        return (f"{c.architecture} layers={len(self.spec.layers)} width={self.spec.width} "
+                f"vocab={self.spec.vocab_size} params={n} dtype={str(self.dtype).replace('torch.', '')} "
+                f"cache={self.cache.bytes() / 2**20:.1f}MiB")
+
+    # ------------------------------------------------------------------ stepping
+    def new_sequence(self) -> int:
+        return self.cache.alloc()
+
+    def end_sequence(self, slot: int) -> None:
+        self.cache.free(slot)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        return self.stepper.step(entries)
+
+    def _step_sample(self, feed, temperatures, uniforms) -> List[int]:
+        entries = [StepEntry(slot, toks, [len(toks) - 1]) for slot, toks in feed]
+        logits = self.stepper.step(entries)
+        params = torch.from_numpy(np.asarray([temperatures, uniforms], dtype=np.float32)).to(self.ops.device)
+        ids = self.ops.sample(logits, params[0], params[1])
+        return ids.tolist()
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.7,
+                 seed: int = 0, stop_ids: Optional[Sequence[int]] = None,
+                 max_batch: Optional[int] = None) -> List[GenerationResult]:
+        """Token-id prompts in, generated ids out, one result per prompt in order.
+        temperature <= 0 is greedy.  Defaults are the reference server's
+        (crates/bitnet-server/src/lib.rs:317, :358)."""
+        loop = GenerationLoop(self._step_sample, self.cache, max_batch or self.max_batch)
+        out = loop.run(prompts, max_tokens, temperature, seed,
+                       self.stop_ids if stop_ids is None else stop_ids)
+        self.last_stats = {"steps": loop.steps, "prefill_tokens": loop.prefill_tokens,
+                           "decode_tokens": loop.decode_tokens}
+        return out
+
+    def _load_tokenizer(self):
+        if self._tokenizer is None:
+            cand = os.environ.get("RBITNET_TOKENIZER")
+            paths = [Path(cand)] if cand else []
+            if self.model_path is not None:
+                paths.append(Path(self.model_path) / "tokenizer.json")
+            path = next((p for p in paths if p.is_file() and p.name == "tokenizer.json"), None)
+            if path is None:
+                raise TokenizerMissing("tokenizer.json not found beside the model (or set RBITNET_TOKENIZER)")
+            from tokenizers import Tokenizer
+            self._tokenizer = Tokenizer.from_file(str(path))
+        return self._tokenizer
+
+    def complete(self, prompt: str, max_tokens: int, temperature: float) -> str:
+        """Text in, text out, as crates/bitnet-core/src/inference.rs:183-208 /
+        crates/bitnet-core/src/llama/runtime.rs:34-78: encode with special tokens, stop at the
+        first of "</s>", "<|endoftext|>", "<|im_end|>" the tokenizer knows, decode
+        skipping special tokens."""
+        tok = self._load_tokenizer()
+        ids = tok.encode(prompt, add_special_tokens=True).ids
+        if not ids:
+            return ""
+        eos = next((tok.token_to_id(t) for t in ("</s>", "<|endoftext|>", "<|im_end|>")
+                    if tok.token_to_id(t) is not None), None)
+        res = self.generate([ids], max_tokens, temperature, stop_ids=[] if eos is None else [eos])[0]
+        return tok.decode(res.tokens, skip_special_tokens=True)

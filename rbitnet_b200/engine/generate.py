@@ -1,0 +1,123 @@
+"""The generation loop above the step function.
+
+Requests (token-id lists of unequal lengths) are taken in order into batches.
+A batch's prompts run in one step, then every live sequence advances one token
+per step.  A sampled stop token ends its sequence and is not emitted; a
+sequence also ends at ``max_tokens`` new tokens or when it has reached the
+longest length the cache holds.  A sequence that has ended leaves the batch and
+gives its slot back at once; the next batch uses the slots again.  No step runs
+after the last wanted token.
+
+The reference's loop handles one prompt: prompt token by token, then sample,
+append, forward until max_tokens or EOS
+(crates/bitnet-core/src/llama/runtime.rs:34-78; EOS not emitted :67-69; empty
+prompt gives an empty result :46-48).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from ..sampling.rng import uniform
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int]
+    finish_reason: str          # "stop" | "length" | "empty"
+    prompt_tokens: int
+
+
+@dataclass
+class _Live:
+    request: int
+    slot: int
+    last: int
+    out: List[int] = field(default_factory=list)
+
+
+class GenerationLoop:
+    """``step_sample(entries, temperatures, uniforms) -> list of token ids`` runs one step
+    over ``(slot, tokens)`` pairs and samples at each sequence's last token.  ``cache``
+    provides ``alloc() -> slot``, ``free(slot)``, ``length(slot)``, ``max_seq`` and
+    ``fits(lengths) -> bool`` (whether sequences growing to these lengths fit together)."""
+
+    def __init__(self, step_sample: Callable, cache, max_batch: int):
+        self.step_sample, self.cache, self.max_batch = step_sample, cache, max_batch
+        self.steps = 0
+        self.prefill_tokens = 0
+        self.decode_tokens = 0
+
+    def _take_batch(self, pending: List[int], prompts, max_tokens: int) -> List[int]:
+        batch: List[int] = []
+        lengths: List[int] = []
+        for r in pending:
+            if len(batch) >= self.max_batch:
+                break
+            n = len(prompts[r])
+            if n > self.cache.max_seq:
+                raise ValueError(f"request {r}: prompt of {n} tokens exceeds the longest sequence "
+                                 f"the cache holds ({self.cache.max_seq})")
+            grown = min(n + max_tokens, self.cache.max_seq)
+            if not self.cache.fits(lengths + [grown]):
+                break
+            batch.append(r)
+            lengths.append(grown)
+        if not batch:
+            raise ValueError(f"request {pending[0]} does not fit the cache even alone")
+        return batch
+
+    def run(self, prompts: Sequence[Sequence[int]], max_tokens: int, temperature: float = 0.0,
+            seed: int = 0, stop_ids: Sequence[int] = (),
+            on_token: Optional[Callable[[int, int], None]] = None) -> List[GenerationResult]:
+        stop = set(int(s) for s in stop_ids)
+        results: List[Optional[GenerationResult]] = [None] * len(prompts)
+        pending = []
+        for r, p in enumerate(prompts):
+            if len(p) == 0:
+                results[r] = GenerationResult([], "empty", 0)
+            elif max_tokens <= 0:
+                results[r] = GenerationResult([], "length", len(p))
+            else:
+                pending.append(r)
+        while pending:
+            batch = self._take_batch(pending, prompts, max_tokens)
+            pending = pending[len(batch):]
+            live = [_Live(r, self.cache.alloc(), -1) for r in batch]
+            try:
+                feed = [(s.slot, list(prompts[s.request])) for s in live]
+                self.prefill_tokens += sum(len(t) for _, t in feed)
+                while live:
+                    temps = [temperature] * len(live)
+                    us = [uniform(seed, s.request, len(s.out)) for s in live]
+                    sampled = self.step_sample(feed, temps, us)
+                    self.steps += 1
+                    still: List[_Live] = []
+                    for s, tok in zip(live, sampled):
+                        tok = int(tok)
+                        reason = None
+                        if tok in stop:
+                            reason = "stop"
+                        else:
+                            s.out.append(tok)
+                            s.last = tok
+                            if on_token is not None:
+                                on_token(s.request, tok)
+                            if len(s.out) >= max_tokens:
+                                reason = "length"
+                            elif self.cache.length(s.slot) >= self.cache.max_seq:
+                                reason = "length"       # no room to feed this token back
+                        if reason is None:
+                            still.append(s)
+                        else:
+                            results[s.request] = GenerationResult(s.out, reason, len(prompts[s.request]))
+                            self.cache.free(s.slot)
+                            s.slot = -1
+                    live = still
+                    feed = [(s.slot, [s.last]) for s in live]
+                    self.decode_tokens += len(live)
+            finally:
+                for s in live:
+                    if s.slot >= 0:
+                        self.cache.free(s.slot)
+        return results  # type: ignore[return-value]

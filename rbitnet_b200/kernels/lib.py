@@ -1,0 +1,69 @@
+"""Loads the built kernel library and declares its C entry points.
+
+There is no other implementation behind these calls: if the library cannot be
+built or loaded, ``load()`` raises, and so does everything that needs a kernel.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_int64, c_float, c_void_p, c_char_p
+from typing import Optional
+
+from .build import library_path
+
+P, I, L, F = c_void_p, c_int, c_int64, c_float
+
+_SIGNATURES = {
+    "rb_abi_version": [],
+    "rb_embed": [P, P, I, P, I, I, I, P],
+    "rb_rmsnorm": [P, I, P, P, P, I, I, I, F, P],
+    "rb_rotate_append": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+    "rb_silu_mul": [P, P, I, I, I, P],
+    "rb_gather_rows": [P, P, P, I, I, P],
+    "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, P],
+    "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
+    "rb_sample": [P, P, L, I, I, P, P, P],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+class KernelLibrary:
+    def __init__(self, path):
+        self.path = str(path)
+        self._dll = ctypes.CDLL(self.path)
+        self._dll.rb_last_error.restype = c_char_p
+        self._dll.rb_last_error.argtypes = []
+        self.launches = 0   # kernels launched through this library, for the bench's record
+        for name, argtypes in _SIGNATURES.items():
+            self.declare(name, argtypes)
+
+    def declare(self, name, argtypes, restype=c_int):
+        fn = getattr(self._dll, name)
+        fn.argtypes = argtypes
+        fn.restype = restype
+        return fn
+
+    def has(self, name) -> bool:
+        return hasattr(self._dll, name)
+
+    def call(self, name, *args, launches: int = 1):
+        rc = getattr(self._dll, name)(*args)
+        if rc != 0:
+            raise KernelError(self._dll.rb_last_error().decode(errors="replace") or f"{name} failed ({rc})")
+        self.launches += launches
+
+    def raw(self, name):
+        return getattr(self._dll, name)
+
+
+_LIB: Optional[KernelLibrary] = None
+
+
+def load(verbose: bool = True) -> KernelLibrary:
+    global _LIB
+    if _LIB is None:
+        _LIB = KernelLibrary(library_path(verbose=verbose))
+    return _LIB

@@ -1,0 +1,178 @@
+"""The operations a step is made of, on device tensors, each one a launch of this
+package's own CUDA kernels.
+
+``CudaOps(dtype)`` is the only implementation on the product path.  With
+``torch.float32`` every product is a float32 FFMA sum and every activation,
+cache entry and weight is float32 (no tensor-core or reduced-precision mode).
+With ``torch.bfloat16`` weights, activations between kernels and the cache are
+bfloat16, while the residual stream, norms, rotation angles, softmax and all
+accumulation stay float32.
+"""
+from __future__ import annotations
+
+from ctypes import c_void_p
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from .lib import load, KernelError
+
+F32, BF16 = 0, 1
+_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+@dataclass
+class LinearWeight:
+    """A weight matrix [out, in] made ready for ``linear``."""
+    w: torch.Tensor
+    n_out: int
+    n_in: int
+
+
+@dataclass
+class GateUpWeight:
+    """Gate and up matrices made ready for ``gated_linear``: rows [gate | up]."""
+    w: torch.Tensor
+    inner: int
+    n_in: int
+
+
+class CudaOps:
+    def __init__(self, dtype=torch.bfloat16, device="cuda:0", verbose_build: bool = True):
+        if dtype not in _CODE:
+            raise ValueError(f"compute dtype must be float32 or bfloat16, found {dtype}")
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: rbitnet_b200 runs its kernels on a B200 and has no other path")
+        self.dtype = dtype
+        self.code = _CODE[dtype]
+        self.device = torch.device(device)
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise KernelError(f"device {self.device} has compute capability {major}.{minor}; "
+                              "the kernels are built for sm_100a only")
+        self.lib = load(verbose=verbose_build)
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, t: torch.Tensor, dtype, what: str):
+        if t.dtype != dtype or not t.is_cuda or not t.is_contiguous():
+            raise KernelError(f"{what}: expected a contiguous {dtype} CUDA tensor, found {t.dtype} "
+                              f"on {t.device}, contiguous={t.is_contiguous()}")
+
+    def to_compute(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(device=self.device, dtype=self.dtype).contiguous()
+
+    # ------------------------------------------------------------------ weights
+    def prepare_embedding(self, table: torch.Tensor) -> torch.Tensor:
+        return self.to_compute(table)
+
+    def prepare_linear(self, weights: List[torch.Tensor]) -> LinearWeight:
+        """One matrix from the given ones stacked along the output axis."""
+        if len(weights) == 1:
+            w = self.to_compute(weights[0])
+        else:
+            w = torch.cat([self.to_compute(x) for x in weights], dim=0).contiguous()
+        return LinearWeight(w, w.shape[0], w.shape[1])
+
+    def prepare_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> GateUpWeight:
+        w = torch.cat([self.to_compute(gate), self.to_compute(up)], dim=0).contiguous()
+        return GateUpWeight(w, gate.shape[0], gate.shape[1])
+
+    # ------------------------------------------------------------------ ops
+    def embed(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        T, (V, E) = ids.shape[0], table.shape
+        out = torch.empty((T, E), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_embed", _ptr(out), _ptr(table), _CODE[table.dtype], _ptr(ids), T, E, V, self._stream())
+        return out
+
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, partials=None,
+                out_dtype=None) -> torch.Tensor:
+        self._check(x, torch.float32, "rmsnorm input")
+        T, E = x.shape
+        out = torch.empty((T, E), dtype=out_dtype or self.dtype, device=self.device)
+        n_part = 0 if partials is None else partials.shape[0]
+        self.lib.call("rb_rmsnorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), _ptr(partials), n_part,
+                      T, E, float(eps), self._stream())
+        return out
+
+    def linear(self, x: torch.Tensor, weight: LinearWeight, out_dtype=None,
+               accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x[T, in] * W[out, in]^T.  With ``accumulate_into`` (float32 [T, out]) the
+        product is added to it in float32 and it is returned."""
+        self._check(x, self.dtype, "linear input")
+        T, K = x.shape
+        if K != weight.n_in:
+            raise KernelError(f"linear: input width {K} does not match the weight's {weight.n_in}")
+        if accumulate_into is not None:
+            out, acc = accumulate_into, 1
+            self._check(out, torch.float32, "linear accumulate_into")
+        else:
+            out, acc = torch.empty((T, weight.n_out), dtype=out_dtype or self.dtype, device=self.device), 0
+        self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
+                      _ptr(weight.w), weight.w.stride(0), self.code, T, weight.n_out, K, acc, self._stream())
+        return out
+
+    def gated_linear(self, x: torch.Tensor, weight: GateUpWeight) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype."""
+        T = x.shape[0]
+        gu = self.linear(x, LinearWeight(weight.w, 2 * weight.inner, weight.n_in))
+        out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, T, weight.inner, self._stream())
+        return out
+
+    def rotate_append(self, qkv: torch.Tensor, rotary, meta, view, n_heads: int) -> torch.Tensor:
+        """Rotates q (and k) by position, appends k and v to the cache; returns q [T, H, D]."""
+        T = qkv.shape[0]
+        D, Kh = view.head_dim, view.n_kv_heads
+        if rotary is None:
+            inv_freq, interleaved, rot_dim = self._zeros_freq(D), False, D
+        else:
+            inv_freq, interleaved, rot_dim = rotary
+        want = (n_heads + (2 * Kh if view.writes else 0)) * D
+        if qkv.shape[1] != want:
+            raise KernelError(f"rotate_append: rows of {qkv.shape[1]} values, expected {want}")
+        q = torch.empty((T, n_heads, D), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_rotate_append", _ptr(q), _ptr(qkv), qkv.stride(0), self.code, _ptr(inv_freq),
+                      _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k), _ptr(view.v), _ptr(view.page_table),
+                      view.max_pages, view.page_size, T, n_heads, Kh, D, 1 if view.writes else 0, rot_dim,
+                      1 if interleaved else 0, self._stream())
+        return q
+
+    def _zeros_freq(self, D):
+        z = getattr(self, "_zf", None)
+        if z is None or z.shape[0] < D // 2:
+            self._zf = z = torch.zeros(max(D // 2, 1), dtype=torch.float32, device=self.device)
+        return z
+
+    def attention(self, q: torch.Tensor, meta, view, n_heads: int, scale: float,
+                  window: Optional[int]) -> torch.Tensor:
+        """Each new token's queries over its sequence's cached keys up to its own position."""
+        T, H, D = q.shape
+        out = torch.empty((T, H * D), dtype=self.dtype, device=self.device)
+        self.lib.call("rb_attention_simple", _ptr(out), _ptr(q), self.code, _ptr(view.k), _ptr(view.v),
+                      _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
+                      _ptr(meta.tok_slot), T, H, view.n_kv_heads, D, float(scale), int(window or 0),
+                      self._stream())
+        return out
+
+    def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        R, E = rows.shape[0], x.shape[1]
+        out = torch.empty((R, E), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gather_rows", _ptr(out), _ptr(x), _ptr(rows), R, E, self._stream())
+        return out
+
+    def sample(self, logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
+        """One token id per row of float32 logits; temperature <= 0 is the arg-max."""
+        self._check(logits, torch.float32, "sample logits")
+        R, V = logits.shape
+        out = torch.empty((R,), dtype=torch.int32, device=self.device)
+        self.lib.call("rb_sample", _ptr(out), _ptr(logits), logits.stride(0), R, V, _ptr(temperature),
+                      _ptr(uniform), self._stream())
+        return out
