@@ -1,0 +1,68 @@
+"""Shared pieces of the tests: model folders with random weights, and the one place
+where tolerances are stated."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+import plain_llama as plain
+from rbitnet_b200.config import config_from_dict
+from rbitnet_b200.config.registry import get_architecture
+from rbitnet_b200.weights import random_tensors, write_safetensors
+
+# Tolerances against the plain implementation run in float64 on the same stored
+# weights.  float32: rounding of float32 sums only.  bfloat16: activations between
+# kernels and the cache are rounded to bfloat16 (8 bits of mantissa) a few times
+# per layer; the residual stream, norms, softmax and sums are float32.
+TOL = {"float32": (1e-5, 1e-4), "bfloat16": (0.0, 2e-2)}
+
+
+def assert_close(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str = ""):
+    got, ref = got.detach().double().cpu(), ref.double()
+    assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    atol, rtol = TOL[dtype]
+    scale = float(ref.abs().max())
+    err = float((got - ref).abs().max())
+    assert err <= atol + rtol * scale, f"{what}: max error {err:.3e} > {atol} + {rtol} * {scale:.3e} ({dtype})"
+    return err
+
+
+def sharpen(tensors: dict, factor: float) -> dict:
+    """Scale every query and key projection so that attention scores spread out (random
+    small weights give nearly uniform attention, which would hide a wrong mask or position)."""
+    out = dict(tensors)
+    for name in tensors:
+        if name.endswith("q_proj.weight") or name.endswith("k_proj.weight"):
+            out[name] = tensors[name] * factor
+    return out
+
+
+def make_model_dir(folder, cfg_dict: dict, seed: int, store: str = "float32", factor: float = 4.0) -> Path:
+    """Writes config.json and model.safetensors; ``store`` is the dtype on file."""
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    cfg = config_from_dict(cfg_dict)
+    spec = get_architecture(cfg.architecture).build_spec(cfg)
+    tensors = sharpen(random_tensors(spec, seed), factor)
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[store]
+    tensors = {k: v.to(dt) for k, v in tensors.items()}
+    (folder / "config.json").write_text(json.dumps(cfg_dict))
+    write_safetensors(folder / "model.safetensors", tensors)
+    return folder
+
+
+class PlainModel:
+    """The plain implementation on a model folder, with whole-sequence logits cached."""
+
+    def __init__(self, folder):
+        self.cfg, self.tensors = plain.load_folder(folder)
+        self._memo = {}
+
+    def logits(self, tokens) -> torch.Tensor:
+        key = tuple(tokens)
+        if key not in self._memo:
+            self._memo[key] = plain.forward(self.cfg, self.tensors, list(tokens), torch.float64)
+        return self._memo[key]

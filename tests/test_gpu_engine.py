@@ -1,0 +1,178 @@
+"""The engine against the plain implementation, on the GPU, in 32-bit and in bfloat16:
+whole requests; the last 32 tokens one by one; batches of unequal lengths whose shorter
+requests end earlier, one batch after another so that slots are used again; long decoding;
+the first tokens of a sequence; greedy generation through the entry point."""
+import pytest
+import torch
+
+from helpers import assert_close, make_model_dir, PlainModel
+from tiny import TINY_A, TINY_B, prompts
+import plain_llama as plain
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 2)}
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (cfg, seed) in CONFIGS.items():
+        for store in DTYPES:
+            out[name, store] = make_model_dir(tmp_path_factory.mktemp(f"tiny{name}_{store}"), cfg, seed, store)
+    return out
+
+
+@pytest.fixture(scope="module")
+def engines(folders):
+    from rbitnet_b200 import Engine
+    made = {}
+
+    def get(name, dtype, **kw):
+        key = (name, dtype, tuple(sorted(kw.items())))
+        if key not in made:
+            made[key] = (Engine.load_path(folders[name, dtype], dtype=dtype, max_tokens=kw.pop("max_tokens", 2048), **kw),
+                         PlainModel(folders[name, dtype]))
+        return made[key]
+    return get
+
+
+def _cases():
+    return [(n, d) for n in CONFIGS for d in DTYPES]
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_whole_requests(engines, name, dtype):
+    from rbitnet_b200 import StepEntry
+    eng, ref = engines(name, dtype)
+    V = eng.config.vocab_size
+    for p in prompts([1, 2, 7, 33, 64, 65, 100], V, seed=5):
+        s = eng.new_sequence()
+        out = eng.step([StepEntry(s, p, list(range(len(p))))])
+        eng.end_sequence(s)
+        assert_close(out, ref.logits(p), dtype, f"whole len={len(p)}")
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_last_32_one_by_one(engines, name, dtype):
+    from rbitnet_b200 import StepEntry
+    eng, ref = engines(name, dtype)
+    V = eng.config.vocab_size
+    for p in prompts([33, 80, 127], V, seed=6):
+        s = eng.new_sequence()
+        n0 = len(p) - 32
+        outs = [eng.step([StepEntry(s, p[:n0], list(range(n0)))])]
+        for t in p[n0:]:
+            outs.append(eng.step([StepEntry(s, [t], [0])]))
+        eng.end_sequence(s)
+        assert_close(torch.cat(outs), ref.logits(p), dtype, f"tail32 len={len(p)}")
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_unequal_batches_with_slot_reuse(engines, name, dtype):
+    """Batches of unequal prompt and total lengths; shorter requests end earlier; three
+    batches in a row on a cache that only holds one batch, so every slot and page is used again."""
+    from rbitnet_b200 import StepEntry
+    eng, ref = engines(name, dtype, max_tokens=512)
+    V = eng.config.vocab_size
+    plans = [([5, 9, 3, 70], [8, 2, 12, 5]), ([1, 17, 6, 11], [12, 12, 1, 7]), ([64, 2, 31, 16], [3, 9, 4, 20])]
+    for b, (lens, decs) in enumerate(plans):
+        ps = prompts([n + d for n, d in zip(lens, decs)], V, seed=20 + b)
+        slots = [eng.new_sequence() for _ in ps]
+        got = [[] for _ in ps]
+        out = eng.step([StepEntry(s, p[:n], list(range(n))) for s, p, n in zip(slots, ps, lens)])
+        off = 0
+        for i, n in enumerate(lens):
+            got[i].append(out[off:off + n])
+            off += n
+        live = list(range(len(ps)))
+        k = 0
+        while live:
+            out = eng.step([StepEntry(slots[i], [ps[i][lens[i] + k]], [0]) for i in live])
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+            k += 1
+            for i in [i for i in live if decs[i] == k]:
+                eng.end_sequence(slots[i])
+            live = [i for i in live if decs[i] > k]
+        for i, p in enumerate(ps):
+            assert_close(torch.cat(got[i]), ref.logits(p), dtype, f"batch {b} request {i}")
+    assert eng.cache.book.live() == []
+    assert all(pool.n_free == pool.n for pool in eng.cache.book.pools)
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_long_decoding(engines, name, dtype):
+    """One token at a time from the very first token up to the model's longest sequence."""
+    from rbitnet_b200 import StepEntry
+    eng, ref = engines(name, dtype)
+    V, n = eng.config.vocab_size, eng.config.max_position_embeddings
+    p = prompts([n], V, seed=8)[0]
+    s = eng.new_sequence()
+    outs = [eng.step([StepEntry(s, [t], [0])]) for t in p]
+    eng.end_sequence(s)
+    got, want = torch.cat(outs), ref.logits(p)
+    assert_close(got[:4], want[:4], dtype, "first tokens")
+    assert_close(got, want, dtype, "long decoding")
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_context_overflow_is_refused(engines, name, dtype):
+    from rbitnet_b200 import StepEntry
+    from rbitnet_b200.cache import ContextOverflow
+    eng, _ = engines(name, dtype)
+    n = eng.config.max_position_embeddings
+    s = eng.new_sequence()
+    with pytest.raises(ContextOverflow):
+        eng.step([StepEntry(s, [1] * (n + 1), [])])
+    eng.end_sequence(s)
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_a_far_key_among_hundreds(engines, name, dtype):
+    """The answer depends on one early token only if attention reaches it: two sequences that
+    differ in their first token alone must differ in their last logits as the plain model says."""
+    from rbitnet_b200 import StepEntry
+    eng, ref = engines(name, dtype)
+    V, n = eng.config.vocab_size, eng.config.max_position_embeddings
+    base = prompts([n], V, seed=9)[0]
+    other = [(base[0] + 1) % V] + base[1:]
+    outs = []
+    for p in (base, other):
+        s = eng.new_sequence()
+        outs.append(eng.step([StepEntry(s, p, [n - 1])]))
+        eng.end_sequence(s)
+        assert_close(outs[-1], ref.logits(p)[-1:], dtype, "last logits")
+    want = (ref.logits(base)[-1] - ref.logits(other)[-1])
+    got = (outs[0][0] - outs[1][0]).double().cpu()
+    if dtype == "float32":
+        assert float(want.abs().max()) > 1e-4, "the plain model does not see the far key; test is void"
+        assert float((got - want).abs().max()) <= 1e-5 + 1e-3 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("name,dtype", _cases())
+def test_greedy_generation_through_the_entry_point(engines, name, dtype):
+    eng, ref = engines(name, dtype)
+    V = eng.config.vocab_size
+    ps = prompts([4, 19, 1, 8, 30], V, seed=10)
+    stop = [7]
+    res = eng.generate(ps, max_tokens=10, temperature=0.0, stop_ids=stop, max_batch=3)
+    assert eng.cache.book.live() == []
+    for p, r in zip(ps, res):
+        # every emitted token must be the plain model's arg-max given the tokens before it
+        # (within the dtype's tolerance at a near tie), and a stop token is never emitted
+        seq = list(p)
+        assert all(t not in stop for t in r.tokens)
+        full = ref.logits(seq + r.tokens) if r.tokens else None
+        for i, t in enumerate(r.tokens):
+            row = full[len(p) - 1 + i]
+            atol, rtol = (1e-5, 1e-4) if dtype == "float32" else (0.0, 2e-2)
+            assert float(row[t]) >= float(row.max()) - 2 * (atol + rtol * float(row.abs().max())), (i, t)
+        if r.finish_reason == "length":
+            assert len(r.tokens) == 10
+        else:
+            assert r.finish_reason == "stop" and len(r.tokens) < 10
+    if dtype == "float32":
+        for p, r in zip(ps, res):
+            assert r.tokens == plain.generate_greedy(ref.cfg, ref.tensors, p, 10, stop)
