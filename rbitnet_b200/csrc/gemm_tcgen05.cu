@@ -1,0 +1,442 @@
+// Tensor-core matrix product for sm_100a: C[tokens, out] = X[tokens, K] * W[out, K]^T, bfloat16
+// operands, float32 accumulation in tensor memory.
+//
+// Orientation.  The weight matrix is the M side of the tcgen05 instruction (128 rows of W per
+// CTA), the tokens are the N side (16..256 per CTA).  The same kernel therefore serves a
+// prefill of thousands of tokens (N tile 256) and a decode step of 1..64 tokens (N tile 16..64)
+// without wasting the 128-row M side on padding.  Both operands are K-major in shared memory:
+// TMA brings [rows, 64] boxes of W and X with the 128-byte swizzle, which is the canonical
+// K-major layout the instruction's shared-memory descriptors name.
+//
+// Roles in a CTA of 192 threads: warp 0 issues TMA loads into a ring of stages, warp 1 owns the
+// tensor memory and issues tcgen05.mma (one lane), warps 2..5 read the accumulators back with
+// tcgen05.ld and write the result.  K may be split over gridDim.z; then each split writes its
+// own float32 slice and the consumer adds the slices in a fixed order.
+//
+// Epilogues: plain store (bfloat16 or float32), add into a float32 matrix (the residual stream,
+// crates/bitnet-core/src/llama/model.rs:291-294, :303-306), float32 slices of a split product,
+// and SiLU(gate)*up from two accumulators (model.rs:297-302).
+//
+// Every wait on an mbarrier is bounded: after about two seconds the waiting thread records an
+// error code in a device word and the CTA leaves through the common exit, freeing its tensor
+// memory.  The host reads the word with rb_read_error_flag().
+#include "rb_common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <string>
+
+namespace {
+
+constexpr int BM = 128;        // weight rows per CTA (UMMA M)
+constexpr int BK = 64;         // 64 bfloat16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int W_TILE_BYTES = BM * BK * 2;
+
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_GATED = 3 };
+
+__device__ int g_error_flag = 0;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false (and the error word set) after ~2 s.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > 2000000000ull) {
+      atomicCAS(&g_error_flag, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                    // leading byte offset (unused with a swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset: next 8-row group
+  d |= (uint64_t)1 << 46;                    // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                    // 128-byte swizzle
+  return d;
+}
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4)                     // accumulator float32
+         | (1u << 7) | (1u << 10)      // A and B bfloat16
+         | ((uint32_t)(n >> 3) << 17)  // N
+         | ((uint32_t)(BM >> 4) << 24);  // M
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+  *p = __float2bfloat16_rn(v);
+}
+
+struct GemmParams {
+  void* C;            // output (or float32 slices for EPI_PARTIAL)
+  int64_t ldc;        // row stride of C in elements
+  int64_t slice;      // elements between split slices (EPI_PARTIAL)
+  int n_tokens;       // rows of X
+  int n_out;          // rows of W that produce output columns (the gate half for EPI_GATED)
+  int K;
+  int up_row0;        // EPI_GATED: first row of the up matrix inside W
+  int kb_per_split;   // 64-wide k blocks per split
+};
+
+template <int BN, int STAGES, int EPI, typename OutT>
+__global__ void __launch_bounds__(192, 1)
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
+  constexpr bool GATED = EPI == EPI_GATED;
+  constexpr int X_TILE_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = W_TILE_BYTES * (GATED ? 2 : 1) + X_TILE_BYTES;
+  constexpr int ACC_COLS = BN * (GATED ? 2 : 1);
+  constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
+  static_assert(ACC_COLS <= 512, "tensor memory has 512 columns");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ uint64_t empty_bar[STAGES];
+  __shared__ uint64_t accum_bar;
+  __shared__ uint32_t tmem_holder;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;          // first weight row of this CTA
+  const int t0 = blockIdx.y * BN;          // first token of this CTA
+  const int nkb_total = (p.K + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(nkb_total, kb_begin + p.kb_per_split);
+  const int nkb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1, 1)) break;
+        uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(stage, &tmW, k, n0, &full_bar[s]);
+        if (GATED) tma_load_2d(stage + W_TILE_BYTES, &tmW, k, p.up_row0 + n0, &full_bar[s]);
+        tma_load_2d(stage + W_TILE_BYTES * (GATED ? 2 : 1), &tmX, k, t0, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t phase = (i / STAGES) & 1;
+        ok = mbar_wait(&full_bar[s], phase, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint64_t dw = smem_desc_sw128(stage);
+        const uint64_t dx = smem_desc_sw128(stage + W_TILE_BYTES * (GATED ? 2 : 1));
+#pragma unroll
+        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+          const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
+          const uint64_t koff = (uint64_t)(k4 * UMMA_K * 2 >> 4);
+          umma_bf16(tmem_base, dw + koff, dx + koff, idesc, acc);
+          if (GATED) {
+            const uint64_t du = smem_desc_sw128(stage + W_TILE_BYTES);
+            umma_bf16(tmem_base + BN, du + koff, dx + koff, idesc, acc);
+          }
+        }
+        tcgen05_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
+      }
+      tcgen05_commit(&accum_bar);        // accumulators complete (or nothing was issued)
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;        // tensor-memory lanes 32*quarter .. +31 belong to this warp
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(&accum_bar, 0, 3);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    tcgen05_fence_after();
+    const int n = n0 + quarter * 32 + lane;           // output column = weight row
+    const bool n_ok = n < p.n_out;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t r[16], u[16];
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+        if (nkb > 0) {
+          tmem_ld16(taddr, r);
+          if (GATED) tmem_ld16(taddr + BN, u);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { r[j] = 0u; u[j] = 0u; }
+        }
+        if (t0 + c >= p.n_tokens) break;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + c + j;
+          if (t < p.n_tokens && n_ok) {
+            float v = __uint_as_float(r[j]);
+            if (EPI == EPI_GATED) {
+              const float up = __uint_as_float(u[j]);
+              v = v / (1.0f + expf(-v)) * up;
+              store_out<OutT>((OutT*)p.C + (int64_t)t * p.ldc + n, v);
+            } else if (EPI == EPI_ADD) {
+              float* dst = (float*)p.C + (int64_t)t * p.ldc + n;
+              *dst += v;
+            } else if (EPI == EPI_PARTIAL) {
+              ((float*)p.C)[(int64_t)blockIdx.z * p.slice + (int64_t)t * p.ldc + n] = v;
+            } else {
+              store_out<OutT>((OutT*)p.C + (int64_t)t * p.ldc + n, v);
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; int rows, cols; int64_t ld; int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    h = h * 1000003u ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] (cols contiguous), box [box_rows, 64],
+// 128-byte swizzle, zero fill outside.  Maps are cached by their arguments: they are pure
+// functions of them.
+int get_map(CUtensorMap* out, const void* ptr, int rows, int cols, int64_t ld, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+  }
+  EncodeTiledFn fn = encode_fn();
+  RB_REQUIRE(fn != nullptr, "rb_gemm: cuTensorMapEncodeTiled is not available from the driver");
+  RB_REQUIRE(((uintptr_t)ptr & 15) == 0, "rb_gemm: matrix base %p is not 16-byte aligned", ptr);
+  RB_REQUIRE((ld * 2) % 16 == 0, "rb_gemm: row stride of %lld elements is not a multiple of 8", (long long)ld);
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  RB_REQUIRE(r == CUDA_SUCCESS, "rb_gemm: cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %lld)", (int)r,
+             rows, cols, (long long)ld);
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *out;
+  return 0;
+}
+
+template <int BN, int STAGES, int EPI, typename OutT>
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int n_w_tiles, int n_t_tiles,
+           int splits, cudaStream_t stream) {
+  constexpr int stage_bytes = W_TILE_BYTES * (EPI == EPI_GATED ? 2 : 1) + BN * BK * 2;
+  constexpr int smem = STAGES * stage_bytes + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory");
+  auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  dim3 grid(n_w_tiles, n_t_tiles, splits);
+  kernel<<<grid, 192, smem, stream>>>(tw, tx, p);
+  RB_CHECK_LAUNCH("rb_gemm_tc");
+  return 0;
+}
+
+template <int EPI, typename OutT>
+int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int n_w_tiles,
+             int n_t_tiles, int splits, cudaStream_t stream) {
+  constexpr bool G = EPI == EPI_GATED;
+  switch (bn) {
+    case 16: return launch<16, G ? 5 : 10, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+    case 32: return launch<32, G ? 5 : 10, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+    case 64: return launch<64, G ? 5 : 8, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+    case 128: return launch<128, G ? 4 : 6, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+    case 256: return launch<256, G ? 3 : 4, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  }
+  RB_FAIL("rb_gemm_tc: no kernel for a token tile of %d", bn);
+}
+
+}  // namespace
+
+// The device word that a kernel sets when one of its bounded waits ran out (0: none).
+RB_EXPORT int rb_read_error_flag(int* value, int reset) {
+  int v = 0;
+  RB_CUDA(cudaMemcpyFromSymbol(&v, g_error_flag, sizeof(int)));
+  if (reset && v != 0) {
+    int z = 0;
+    RB_CUDA(cudaMemcpyToSymbol(g_error_flag, &z, sizeof(int)));
+  }
+  *value = v;
+  return 0;
+}
+
+// C (+)= X W^T on the tensor cores.
+//   epilogue 0: C[tokens, n_out] = product, c_dtype float32 or bfloat16
+//   epilogue 1: C (float32) += product                       (splits must be 1)
+//   epilogue 2: C is [splits][tokens][ldc] float32 slices; slice z holds the product over its part of K
+//   epilogue 3: W = [gate ; up] with up starting at row up_row0; C[tokens, n_out] = silu(gate)*up
+// Requirements (refused otherwise): bfloat16 X and W, K a multiple of 8, row strides multiples of 8
+// elements, 16-byte aligned bases.
+RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
+                         int64_t ldw, int w_rows, int n_out, int K, int epilogue, int up_row0, int splits,
+                         int token_tile, cudaStream_t stream) {
+  if (n_tokens == 0 || n_out == 0) return 0;
+  RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
+  RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
+  RB_REQUIRE(splits >= 1, "rb_gemm_tc: splits %d", splits);
+  RB_REQUIRE(epilogue == EPI_PARTIAL || splits == 1, "rb_gemm_tc: only the slice epilogue can split K");
+  const int nkb = (K + BK - 1) / BK;
+  RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
+  int bn = token_tile;
+  if (bn == 0) bn = n_tokens <= 16 ? 16 : n_tokens <= 32 ? 32 : n_tokens <= 64 ? 64 : n_tokens <= 128 ? 128 : 256;
+  CUtensorMap tw, tx;
+  if (get_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
+  if (get_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
+  GemmParams p;
+  p.C = C; p.ldc = ldc; p.slice = (int64_t)n_tokens * ldc; p.n_tokens = n_tokens; p.n_out = n_out; p.K = K;
+  p.up_row0 = up_row0; p.kb_per_split = (nkb + splits - 1) / splits;
+  RB_REQUIRE((int64_t)(splits - 1) * p.kb_per_split < nkb, "rb_gemm_tc: a split of K would be empty");
+  const int n_w_tiles = (n_out + BM - 1) / BM, n_t_tiles = (n_tokens + bn - 1) / bn;
+  RB_REQUIRE(n_t_tiles <= 65535 && splits <= 65535, "rb_gemm_tc: grid too large");
+  if (epilogue == EPI_STORE && c_dtype == RB_BF16)
+    return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  if (epilogue == EPI_STORE && c_dtype == RB_F32)
+    return dispatch<EPI_STORE, float>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  if (epilogue == EPI_ADD && c_dtype == RB_F32)
+    return dispatch<EPI_ADD, float>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  if (epilogue == EPI_PARTIAL && c_dtype == RB_F32)
+    return dispatch<EPI_PARTIAL, float>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  if (epilogue == EPI_GATED && c_dtype == RB_BF16)
+    return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  RB_FAIL("rb_gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, c_dtype);
+}

@@ -150,8 +150,10 @@ class Engine:
         entries = [StepEntry(slot, toks, [len(toks) - 1]) for slot, toks in feed]
         logits = self.stepper.step(entries)
         params = torch.from_numpy(np.asarray([temperatures, uniforms], dtype=np.float32)).to(self.ops.device)
-        ids = self.ops.sample(logits, params[0], params[1])
-        return ids.tolist()
+        ids = self.ops.sample(logits, params[0], params[1]).tolist()
+        if hasattr(self.ops, "check_errors"):
+            self.ops.check_errors()
+        return ids
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.7,

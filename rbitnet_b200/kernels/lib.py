@@ -23,6 +23,8 @@ _SIGNATURES = {
     "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, P],
     "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
     "rb_sample": [P, P, L, I, I, P, P, P],
+    "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, P],
+    "rb_read_error_flag": [P, I],
 }
 
 

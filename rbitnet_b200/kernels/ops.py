@@ -66,6 +66,15 @@ class CudaOps:
             raise KernelError(f"{what}: expected a contiguous {dtype} CUDA tensor, found {t.dtype} "
                               f"on {t.device}, contiguous={t.is_contiguous()}")
 
+    def check_errors(self) -> None:
+        """Raises if a kernel recorded that one of its bounded waits ran out."""
+        import ctypes
+        v = ctypes.c_int(0)
+        self.lib.call("rb_read_error_flag", ctypes.byref(v), 1, launches=0)
+        if v.value:
+            raise KernelError(f"a kernel gave up waiting (code {v.value}: 1 = loader, 2 = tensor-core issuer, "
+                              "3 = epilogue); its results are not valid")
+
     def to_compute(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(device=self.device, dtype=self.dtype).contiguous()
 
@@ -115,15 +124,34 @@ class CudaOps:
             self._check(out, torch.float32, "linear accumulate_into")
         else:
             out, acc = torch.empty((T, weight.n_out), dtype=out_dtype or self.dtype, device=self.device), 0
-        self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
-                      _ptr(weight.w), weight.w.stride(0), self.code, T, weight.n_out, K, acc, self._stream())
+        if self._tensor_core_ok(x, weight.w):
+            self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0), T,
+                          _ptr(weight.w), weight.w.stride(0), weight.n_out, weight.n_out, K, acc, 0, 1, 0,
+                          self._stream())
+        else:
+            self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
+                          _ptr(weight.w), weight.w.stride(0), self.code, T, weight.n_out, K, acc, self._stream())
         return out
+
+    def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
+        """The tcgen05 product takes bfloat16 operands whose rows TMA can address: inner size and
+        row strides multiples of 8 elements, 16-byte aligned bases.  Anything else runs on the
+        plain product."""
+        return (self.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+                and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and x.stride(1) == 1 and w.stride(1) == 1)
 
     def gated_linear(self, x: torch.Tensor, weight: GateUpWeight) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype."""
         T = x.shape[0]
-        gu = self.linear(x, LinearWeight(weight.w, 2 * weight.inner, weight.n_in))
         out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
+        if self._tensor_core_ok(x, weight.w):
+            # two accumulators per tile; the activation and the product happen on the way out
+            self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), T,
+                          _ptr(weight.w), weight.w.stride(0), 2 * weight.inner, weight.inner, weight.n_in,
+                          3, weight.inner, 1, 0, self._stream())
+            return out
+        gu = self.linear(x, LinearWeight(weight.w, 2 * weight.inner, weight.n_in))
         self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, T, weight.inner, self._stream())
         return out
 

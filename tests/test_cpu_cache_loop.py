@@ -1,0 +1,218 @@
+"""The cache's bookkeeping and the generation loop's decisions (no GPU)."""
+import random
+
+import pytest
+import torch
+
+from rbitnet_b200.cache import (FreeList, SlotBook, CacheFull, ContextOverflow, SequenceCache)
+from rbitnet_b200.parts import CacheNeed, StateNeed
+from rbitnet_b200.engine import GenerationLoop
+from rbitnet_b200.sampling import uniform
+
+
+def test_free_list_never_loses_or_doubles():
+    f = FreeList(5)
+    got = [f.take() for _ in range(5)]
+    assert sorted(got) == list(range(5))
+    with pytest.raises(CacheFull):
+        f.take()
+    f.give(3)
+    with pytest.raises(ValueError, match="not held"):
+        f.give(3)
+    with pytest.raises(ValueError, match="not held"):
+        f.give(99)
+    assert f.take() == 3
+
+
+def test_slot_book_random_walk_keeps_every_page_accounted_for():
+    rng = random.Random(0)
+    book = SlotBook(n_slots=6, pages_per_group=[20, 20], page_size=16, max_seq=100)
+    live = {}
+    for _ in range(3000):
+        op = rng.random()
+        if op < 0.25 and len(live) < 6:
+            s = book.alloc()
+            assert s not in live
+            live[s] = 0
+        elif op < 0.4 and live:
+            s = rng.choice(sorted(live))
+            book.free(s)
+            del live[s]
+        elif live:
+            s = rng.choice(sorted(live))
+            n = rng.randint(1, 40)
+            try:
+                book.reserve(s, n)
+                book.advance(s, n)
+                live[s] += n
+            except (CacheFull, ContextOverflow):
+                pass
+        # invariants: no page held twice, none lost, lengths right
+        for g, pool in enumerate(book.pools):
+            held = [p for s in live for p in book.pages[s][g]]
+            assert len(held) == len(set(held))
+            assert set(held) == set(pool.held)
+            assert pool.n_free + len(held) == pool.n
+        for s, n in live.items():
+            assert book.length[s] == n
+            assert all(len(pg) * 16 >= n for pg in book.pages[s])
+        assert book.slots.n_free + len(live) == 6
+    for s in list(live):
+        book.free(s)
+    assert all(p.n_free == p.n for p in book.pools)
+
+
+def test_slot_book_errors():
+    book = SlotBook(2, [4], 16, 50)
+    a = book.alloc()
+    with pytest.raises(ContextOverflow):
+        book.reserve(a, 51)
+    book.reserve(a, 50)                      # 4 pages
+    b = book.alloc()
+    with pytest.raises(CacheFull):
+        book.reserve(b, 1)
+    assert book.pools[0].n_free == 0 and book.pages[b] == [[]]   # a failed reserve keeps nothing
+    with pytest.raises(CacheFull, match="slots"):
+        book.alloc()
+    book.free(a)
+    with pytest.raises(ValueError, match="not live"):
+        book.free(a)
+    with pytest.raises(ValueError):
+        book.advance(b, 17)
+    book.reserve(b, 1)
+    book.advance(b, 1)
+
+
+def test_sequence_cache_groups_views_and_state():
+    needs = {0: CacheNeed(2, 16), 1: CacheNeed(2, 16, window=8), 2: CacheNeed(2, 16)}
+    cache = SequenceCache(needs, reads={3: 0}, state_needs={1: StateNeed((5,), torch.float32)},
+                          max_tokens=256, max_seq=128, dtype=torch.float32, device="cpu", page_size=16)
+    assert len(cache.groups) == 2                                  # all keys / a window: own storage
+    full = [g for g in cache.groups if g.need.window is None][0]
+    assert full.pool.shape == (2, 2, 16, 2, 16, 16)
+    assert cache.view(3).k.data_ptr() == cache.view(0).k.data_ptr() and not cache.view(3).writes
+    assert cache.view(2).k.data_ptr() != cache.view(0).k.data_ptr() and cache.view(2).writes
+    assert cache.view(1).group != cache.view(0).group
+    s = cache.alloc()
+    cache.state(1)[s] += 3.0
+    cache.reserve(s, 40)
+    cache.upload_tables()
+    cache.advance(s, 40)
+    pages = cache.book.pages[s][0]
+    assert cache.groups[0].table[s, :3].tolist() == pages and len(pages) == 3
+    assert cache.fits([128] * 1) and not cache.fits([128] * 2)     # 16 pages, 3 in use
+    cache.free(s)
+    s2 = cache.alloc()
+    assert s2 == s and float(cache.state(1)[s2].abs().sum()) == 0  # state zeroed on hand-out
+    with pytest.raises(ValueError, match="writes none"):
+        SequenceCache({0: CacheNeed(1, 8)}, reads={1: 5}, state_needs={}, max_tokens=64, max_seq=64,
+                      dtype=torch.float32, device="cpu")
+
+
+class _FakeCache:
+    def __init__(self, n_slots=4, max_seq=12, capacity=10 ** 9):
+        self.free_slots = list(range(n_slots))
+        self.max_seq, self.capacity = max_seq, capacity
+        self.len = {}
+        self.log = []
+
+    def alloc(self):
+        s = self.free_slots.pop(0)
+        self.len[s] = 0
+        self.log.append(("alloc", s))
+        return s
+
+    def free(self, s):
+        assert s in self.len, "freed twice"
+        del self.len[s]
+        self.free_slots.append(s)
+        self.log.append(("free", s))
+
+    def length(self, s):
+        return self.len[s]
+
+    def fits(self, lengths):
+        return len(lengths) <= len(self.free_slots) and sum(lengths) <= self.capacity
+
+
+def _script(cache, script):
+    """step_sample that returns, for the sequence in slot s, the next token of script[request]."""
+    calls = []
+    slot_req = {}
+
+    def step_sample(feed, temps, us):
+        calls.append([(s, list(t)) for s, t in feed])
+        out = []
+        for s, toks in feed:
+            if cache.len[s] == 0:
+                # identify the request by its prompt
+                slot_req[s] = next(r for r, (p, _) in enumerate(script) if list(p) == list(toks))
+                step_sample.count[slot_req[s]] = 0
+            cache.len[s] += len(toks)
+            r = slot_req[s]
+            out.append(script[r][1][step_sample.count[r]])
+            step_sample.count[r] += 1
+        return out
+    step_sample.count = {}
+    return step_sample, calls
+
+
+def test_loop_stop_length_and_early_leavers():
+    cache = _FakeCache(n_slots=3, max_seq=100)
+    script = [([1, 2, 3], [10, 11, 99, 12]),        # stops at 99 after 2 tokens
+              ([4], [20, 21, 22, 23, 24]),          # runs to max_tokens = 4
+              ([5, 6], [99]),                       # stops at once, emits nothing
+              ([7, 8, 9, 9], [30, 31, 32, 33])]     # second batch (only 3 slots)
+    fn, calls = _script(cache, script)
+    loop = GenerationLoop(fn, cache, max_batch=3)
+    res = loop.run([p for p, _ in script], max_tokens=4, temperature=0.0, stop_ids=[99])
+    assert [r.tokens for r in res] == [[10, 11], [20, 21, 22, 23], [], [30, 31, 32, 33]]
+    assert [r.finish_reason for r in res] == ["stop", "length", "stop", "length"]
+    # first batch: prompts of 3 requests in one step, then live ones, one token each
+    assert [len(t) for _, t in calls[0]] == [3, 1, 2]
+    assert [t for _, t in calls[1]] == [[10], [20]]           # request 2 left after the first step
+    assert [t for _, t in calls[2]] == [[11], [21]]
+    assert [t for _, t in calls[3]] == [[22]]                 # request 0 left; no step after the last token
+    assert len(calls) == 4 + 4
+    assert cache.len == {} and sorted(cache.free_slots) == [0, 1, 2]
+    allocs = [s for op, s in cache.log if op == "alloc"]
+    assert len(allocs) == 4 and len(set(allocs)) == 3          # the second batch uses a slot again
+    assert loop.prefill_tokens == 10 and loop.steps == 8
+
+
+def test_loop_ends_a_sequence_when_its_slot_is_full_and_handles_empty_prompts():
+    cache = _FakeCache(n_slots=2, max_seq=6)
+    script = [([1, 2, 3, 4], [5, 6, 7, 8, 9]), ([], [])]
+    fn, calls = _script(cache, script)
+    res = GenerationLoop(fn, cache, 2).run([p for p, _ in script], max_tokens=10)
+    # prompt 4 -> sample (len 4), feed -> 5, feed -> 6 = full: the token sampled then cannot be fed
+    assert res[0].tokens == [5, 6, 7] and res[0].finish_reason == "length"
+    assert res[1].tokens == [] and res[1].finish_reason == "empty"
+    assert GenerationLoop(fn, cache, 2).run([[1]], max_tokens=0)[0].finish_reason == "length"
+    with pytest.raises(ValueError, match="exceeds the longest"):
+        GenerationLoop(fn, cache, 2).run([[1] * 7], max_tokens=1)
+
+
+def test_loop_batches_by_cache_capacity_and_frees_on_error():
+    cache = _FakeCache(n_slots=8, max_seq=50, capacity=30)
+    script = [([1] * 5, [2, 2]), ([3] * 6, [4, 4]), ([5] * 20, [6, 6]), ([7] * 2, [8, 8])]
+    fn, calls = _script(cache, script)
+    GenerationLoop(fn, cache, 8).run([p for p, _ in script], max_tokens=2)
+    # 7 + 8 = 15 fit, + 22 = 37 does not: batches are [0, 1], [2, 3]
+    assert [len(t) for _, t in calls[0]] == [5, 6] and [len(t) for _, t in calls[2]] == [20, 2]
+
+    def boom(feed, temps, us):
+        raise RuntimeError("kernel failed")
+    c2 = _FakeCache(n_slots=2)
+    with pytest.raises(RuntimeError):
+        GenerationLoop(boom, c2, 2).run([[1, 2], [3]], max_tokens=3)
+    assert c2.len == {} and len(c2.free_slots) == 2
+
+
+def test_uniform_depends_on_seed_request_and_step_only():
+    a = [uniform(1, r, s) for r in range(4) for s in range(50)]
+    assert all(0.0 <= u < 1.0 for u in a) and len(set(a)) == len(a)
+    assert a == [uniform(1, r, s) for r in range(4) for s in range(50)]
+    assert uniform(2, 0, 0) != uniform(1, 0, 0)
+    assert abs(sum(uniform(3, 0, s) for s in range(4000)) / 4000 - 0.5) < 0.03
+    assert all(float(torch.tensor(u, dtype=torch.float32)) == u for u in a)   # exact in float32

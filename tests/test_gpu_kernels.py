@@ -1,0 +1,286 @@
+"""Each kernel alone against a plain torch float32 reference of the same operation, at sizes
+other than the engine's test models: widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd head counts and groups, token counts that do not fill a tile."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF16, F32 = torch.bfloat16, torch.float32
+
+
+@pytest.fixture(scope="module")
+def ops32():
+    from rbitnet_b200.kernels.ops import CudaOps
+    return CudaOps(F32)
+
+
+@pytest.fixture(scope="module")
+def ops16():
+    from rbitnet_b200.kernels.ops import CudaOps
+    return CudaOps(BF16)
+
+
+def _rel(got, ref):
+    return float((got.double() - ref.double()).abs().max()) / max(float(ref.double().abs().max()), 1e-30)
+
+
+def test_extension_is_loaded_from_the_tree(ops16):
+    import os
+    assert "librbitnet_b200_" in ops16.lib.path and os.path.isfile(ops16.lib.path)
+    maps = open("/proc/self/maps").read()
+    assert os.path.basename(ops16.lib.path) in maps
+
+
+@pytest.mark.parametrize("V,E,T", [(257, 48, 5), (1000, 272, 33)])
+def test_embed(ops32, ops16, V, E, T):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    table = torch.randn(V, E, device="cuda", generator=g)
+    ids = torch.randint(0, V, (T,), device="cuda", generator=g, dtype=torch.int32)
+    assert torch.equal(ops32.embed(ids, table), table[ids.long()])
+    tb = table.to(BF16)
+    assert torch.equal(ops16.embed(ids, tb), tb[ids.long()].float())
+
+
+@pytest.mark.parametrize("E,T,eps", [(48, 3, 1e-5), (272, 17, 1e-6), (4096, 5, 1e-5), (5000, 2, 1e-3)])
+def test_rmsnorm(ops32, ops16, E, T, eps):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(T, E, device="cuda", generator=g) * 3
+    w = 1 + 0.1 * torch.randn(E, device="cuda", generator=g)
+    ref = (x.double() * w.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps))
+    assert _rel(ops32.rmsnorm(x.clone(), w, eps), ref) < 2e-6
+    assert _rel(ops16.rmsnorm(x.clone(), w, eps), ref) < 5e-3
+    # with slices of a split product folded in: x += sum(slices), then the norm
+    parts = torch.randn(3, T, E, device="cuda", generator=g)
+    x2 = x.clone()
+    y = ops32.rmsnorm(x2, w, eps, partials=parts)
+    xs = x.double() + parts.double().sum(0)
+    assert _rel(x2, xs) < 1e-6
+    assert _rel(y, xs * w.double() / torch.sqrt((xs ** 2).mean(-1, keepdim=True) + eps)) < 2e-6
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 7, 5), (3, 100, 33), (70, 130, 257), (5, 48, 176)])
+def test_plain_product_is_true_float32(ops32, T, N, K):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(T, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g)
+    ref = x.double() @ w.double().T
+    got = ops32.linear(x, ops32.prepare_linear([w]))
+    assert _rel(got, ref) < 1e-6        # a reduced-precision matrix mode would give ~1e-3
+    acc = torch.randn(T, N, device="cuda", generator=g)
+    want = acc.double() + ref
+    ops32.linear(x, ops32.prepare_linear([w]), accumulate_into=acc)
+    assert _rel(acc, want) < 1e-6
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (5, 200, 96), (17, 1000, 176), (64, 384, 520), (100, 130, 4096),
+                                   (129, 257, 72), (300, 520, 1032), (700, 96, 48)])
+def test_tensor_core_product(ops16, T, N, K):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    ref = x.double() @ w.double().T
+    lw = ops16.prepare_linear([w])
+    assert ops16._tensor_core_ok(x, lw.w)
+    assert _rel(ops16.linear(x, lw, out_dtype=F32), ref) < 2e-5          # float32 accumulation
+    assert _rel(ops16.linear(x, lw), ref) < 5e-3                          # rounded to bfloat16 once
+    acc = torch.randn(T, N, device="cuda", generator=g)
+    want = acc.double() + ref
+    ops16.linear(x, lw, accumulate_into=acc)
+    assert _rel(acc, want) < 2e-5
+    ops16.check_errors()
+
+
+def test_product_refuses_to_guess_for_odd_inner_sizes(ops16):
+    """An inner size TMA cannot address goes to the plain product, with the same result."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(9, 77, device="cuda", generator=g).to(BF16)
+    w = torch.randn(50, 77, device="cuda", generator=g).to(BF16)
+    lw = ops16.prepare_linear([w])
+    assert not ops16._tensor_core_ok(x, lw.w)
+    assert _rel(ops16.linear(x, lw, out_dtype=F32), x.double() @ w.double().T) < 2e-5
+    from rbitnet_b200.kernels.lib import KernelError
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops16.lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 0)
+
+
+@pytest.mark.parametrize("T,F,K", [(1, 176, 64), (40, 352, 96), (130, 1000, 256), (300, 129, 72)])
+def test_gated_feed_forward_product(ops32, ops16, T, F, K):
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = torch.randn(T, K, device="cuda", generator=g)
+    wg = torch.randn(F, K, device="cuda", generator=g) / math.sqrt(K) * 2
+    wu = torch.randn(F, K, device="cuda", generator=g) / math.sqrt(K)
+    for ops, tol in ((ops32, 2e-6), (ops16, 6e-3)):
+        xx, g_, u_ = (t.to(ops.dtype) for t in (x, wg, wu))
+        gate, up = xx.double() @ g_.double().T, xx.double() @ u_.double().T
+        ref = gate / (1 + torch.exp(-gate)) * up
+        got = ops.gated_linear(xx, ops.prepare_gate_up(g_, u_))
+        assert got.shape == (T, F) and _rel(got, ref) < tol
+
+
+class _Meta:
+    pass
+
+
+def _paged(ops, n_slots, max_pages, page, Kh, D, lens, seed):
+    """A cache with shuffled pages, filled with random keys and values for sequences of ``lens``."""
+    from rbitnet_b200.cache import CacheLayerView
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    n_pages = n_slots * max_pages
+    k = torch.zeros(n_pages, Kh, page, D, device="cuda", dtype=ops.dtype)
+    v = torch.zeros_like(k)
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).to(torch.int32)
+    table = perm.reshape(n_slots, max_pages).cuda()
+    dense_k, dense_v = [], []
+    for s, n in enumerate(lens):
+        kk = torch.randn(n, Kh, D, device="cuda", generator=g).to(ops.dtype)
+        vv = torch.randn(n, Kh, D, device="cuda", generator=g).to(ops.dtype)
+        for p in range(n):
+            pg = int(table[s, p // page])
+            k[pg, :, p % page] = kk[p]
+            v[pg, :, p % page] = vv[p]
+        dense_k.append(kk)
+        dense_v.append(vv)
+    return CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0), dense_k, dense_v
+
+
+def _attn_ref(q, k, v, pos, scale, window):
+    """q [H, D] at position pos over k, v [n, Kh, D], float64."""
+    H, D = q.shape
+    G = H // k.shape[1]
+    lo = max(0, pos - window + 1) if window else 0
+    out = torch.zeros(H, D, dtype=torch.float64, device=q.device)
+    for h in range(H):
+        s = (k[lo:pos + 1, h // G].double() @ q[h].double()) * scale
+        out[h] = torch.softmax(s, 0) @ v[lo:pos + 1, h // G].double()
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("H,Kh,D,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 64, None), (6, 3, 48, 16, 5),
+                                                (8, 2, 128, 64, None), (5, 5, 80, 32, 40), (2, 1, 256, 16, None)])
+def test_attention_over_the_paged_cache(ops32, ops16, H, Kh, D, page, window):
+    """Queries at mixed positions of three sequences (prompt rows and single decode rows in one batch)."""
+    lens = [70, 9, 130]
+    scale = 0.7 / math.sqrt(D)
+    for ops, tol in ((ops32, 3e-6), (ops16, 8e-3)):
+        view, ks, vs = _paged(ops, 3, 4, page if page * 4 >= 130 else 64, Kh, D, lens, seed=7)
+        rows = [(0, 69), (1, 0), (1, 8), (2, 64), (2, 129), (0, 5)] + [(2, p) for p in range(100, 110)]
+        g = torch.Generator(device="cuda").manual_seed(8)
+        q = torch.randn(len(rows), H, D, device="cuda", generator=g).to(ops.dtype) * 2
+        meta = _Meta()
+        meta.tok_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32, device="cuda")
+        meta.tok_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32, device="cuda")
+        got = ops.attention(q, meta, view, H, scale, window)
+        for i, (s, p) in enumerate(rows):
+            ref = _attn_ref(q[i], ks[s], vs[s], p, scale, window)
+            assert _rel(got[i], ref) < tol, (i, s, p)
+
+
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops32):
+    """One key matches the query strongly.  Inside the mask it must dominate the output; one
+    position outside the window it must not be seen at all."""
+    H, Kh, D, page, n = 2, 1, 32, 16, 300
+    view, ks, vs = _paged(ops32, 1, 32, page, Kh, D, [n], seed=9)
+    q = torch.zeros(1, H, D, device="cuda")
+    q[0, :, 3] = 50.0
+    far = 17
+    for kk in (ks[0],):
+        kk[:, :, 3] = 0.0
+        kk[far, 0, 3] = 10.0
+    pg = int(view.page_table[0, far // page])
+    view.k[:, :, :, 3] = 0.0
+    view.k[pg, 0, far % page, 3] = 10.0
+    meta = _Meta()
+    meta.tok_slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    meta.tok_pos = torch.tensor([n - 1], dtype=torch.int32, device="cuda")
+    scale = 1 / math.sqrt(D)
+    out = ops32.attention(q, meta, view, H, scale, None).reshape(H, D)
+    assert _rel(out[0], vs[0][far, 0]) < 1e-5                       # the far key owns the softmax
+    w_in, w_out = n - far, n - far - 1                               # window that just reaches it / just misses
+    assert _rel(ops32.attention(q, meta, view, H, scale, w_in).reshape(H, D)[0], vs[0][far, 0]) < 1e-5
+    missed = ops32.attention(q, meta, view, H, scale, w_out).reshape(H, D)[0]
+    ref = vs[0][far + 1:n, 0].double().mean(0)                       # all other scores are equal (zero)
+    assert _rel(missed, ref) < 1e-5
+
+
+@pytest.mark.parametrize("H,Kh,D,interleaved", [(4, 2, 16, True), (3, 1, 32, False), (8, 8, 64, False), (2, 1, 128, True)])
+def test_rotation_and_cache_append(ops32, ops16, H, Kh, D, interleaved):
+    from rbitnet_b200.cache import CacheLayerView
+    theta = 10000.0 if interleaved else 500000.0
+    page, max_pages, n_slots = 16, 8, 3
+    rows = [(0, 0), (0, 1), (2, 100), (1, 15), (1, 16), (2, 127)]
+    T = len(rows)
+    for ops, tol in ((ops32, 2e-6), (ops16, 6e-3)):
+        g = torch.Generator(device="cuda").manual_seed(10)
+        qkv = torch.randn(T, (H + 2 * Kh) * D, device="cuda", generator=g).to(ops.dtype)
+        k = torch.zeros(n_slots * max_pages, Kh, page, D, device="cuda", dtype=ops.dtype)
+        v = torch.zeros_like(k)
+        table = torch.randperm(n_slots * max_pages).to(torch.int32).reshape(n_slots, max_pages).cuda()
+        view = CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0)
+        meta = _Meta()
+        meta.tok_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32, device="cuda")
+        meta.tok_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32, device="cuda")
+        i = torch.arange(D // 2, dtype=torch.float32)
+        inv = (1.0 / torch.pow(torch.tensor(theta), 2.0 * i / D)).cuda()
+        q = ops.rotate_append(qkv, (inv, interleaved, D), meta, view, H)
+
+        def rot(x, pos):     # x [heads, D] float64
+            ang = (torch.tensor(float(pos), dtype=torch.float32) * inv.cpu()).double()
+            c, s = torch.cos(ang), torch.sin(ang)
+            out = torch.empty_like(x)
+            if interleaved:
+                a, b = x[:, 0::2], x[:, 1::2]
+                out[:, 0::2], out[:, 1::2] = a * c - b * s, a * s + b * c
+            else:
+                a, b = x[:, :D // 2], x[:, D // 2:]
+                out[:, :D // 2], out[:, D // 2:] = a * c - b * s, a * s + b * c
+            return out
+
+        x = qkv.double().cpu()
+        for t, (slot, pos) in enumerate(rows):
+            assert _rel(q[t].cpu(), rot(x[t, :H * D].reshape(H, D), pos)) < tol
+            pg = int(table[slot, pos // page])
+            assert _rel(k[pg, :, pos % page].cpu(), rot(x[t, H * D:(H + Kh) * D].reshape(Kh, D), pos)) < tol
+            assert torch.equal(v[pg, :, pos % page].cpu().double(), x[t, (H + Kh) * D:].reshape(Kh, D))
+        written = sum(1 for _ in rows)
+        assert int((k.abs().sum(dim=(1, 3)) > 0).sum()) == written       # nothing else was touched
+
+
+@pytest.mark.parametrize("V", [257, 1000, 128256])
+def test_sampling(ops32, V):
+    import plain_llama as plain
+    g = torch.Generator(device="cuda").manual_seed(11)
+    R = 6
+    logits = torch.randn(R, V, device="cuda", generator=g) * 3
+    logits[1, 5] = float("nan")
+    logits[2, 40] = logits[2, 41] = 99.0                       # a tie: the lowest index wins
+    logits[3] = float("nan")
+    logits[3, 7] = -2.0
+    zero = torch.zeros(R, device="cuda")
+    got = ops32.sample(logits, zero, zero).tolist()
+    for r in range(R):
+        assert got[r] == plain.greedy_token(logits[r].cpu())
+    assert got[2] == 40 and got[3] == 7
+    temps = torch.tensor([0.5, 1.0, 0.8, 1.0, 2.0, 0.0], device="cuda")
+    for trial in range(5):
+        u = torch.rand(R, generator=torch.Generator().manual_seed(trial)).cuda()
+        got = ops32.sample(logits, temps, u).tolist()
+        for r in range(R - 1):
+            cdf = plain.temperature_cdf(torch.nan_to_num(logits[r].cpu(), nan=-float("inf")), float(temps[r]))
+            total, target = float(cdf[-1]), float(u[r]) * float(cdf[-1])
+            i = got[r]
+            below = float(cdf[i - 1]) if i > 0 else 0.0
+            assert below - 1e-5 * total <= target <= float(cdf[i]) + 1e-5 * total, (r, i)
+        assert got[R - 1] == plain.greedy_token(logits[R - 1].cpu())
+    # the edges of the unit interval
+    flat = torch.zeros(2, V, device="cuda")
+    one = torch.ones(2, device="cuda")
+    assert ops32.sample(flat, one, torch.tensor([0.0, 0.99999994], device="cuda")).tolist() == [0, V - 1]
+
+
+def test_gather_rows(ops32):
+    x = torch.randn(20, 48, device="cuda")
+    rows = torch.tensor([19, 0, 7, 7], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops32.gather_rows(x, rows), x[rows.long()])
