@@ -1,0 +1,282 @@
+"""Decode throughput of the Llama-3-8B-shaped model with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L] [--impl reference]
+
+A step is one decode step: one token for each of ``batch`` sequences whose cache already
+holds ``prompt_len`` tokens.  ``value`` is decoded tokens a second with the step chained on
+the device (the sampled ids feed the next step there); ``e2e`` is the same step driven
+through the engine's Python entry point with host token ids in and sampled ids out every
+step.  The line also carries a 2,048-token prefill, the decode step's memory roofline, and
+decode at batch 1 and 64.  Weights are random (there is no checkpoint to load) and the
+cache content is random; the work does not depend on either.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE.json configs[2]: the Llama-3-8B shape
+MODEL = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+             num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256, rope_theta=500000.0,
+             rms_norm_eps=1e-5, max_position_embeddings=8192, tie_word_embeddings=False, hidden_act="silu")
+FULL_LAYERS = 32
+PROMPT_LEN = 2048
+METRIC = "decode tok/s @ batch 8 (Llama-3-8B shape, 2048-token prompts, bf16)"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return self
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self, t0, t1):
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 7] or [r for _, r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(rows[0][1]),
+                "reasons": reasons, "samples": len(rows)}
+
+
+def fill_cache(engine, batch, context, room):
+    """``batch`` live sequences of ``context`` cached positions each (random keys and values),
+    with pages reserved for ``room`` more."""
+    import torch
+    slots = []
+    for _ in range(batch):
+        s = engine.new_sequence()
+        engine.cache.reserve(s, context + room)
+        engine.cache.advance(s, context)
+        slots.append(s)
+    engine.cache.upload_tables()
+    return slots
+
+
+def decode_bytes(engine, batch, context):
+    """What a decode step has to read: every weight it uses once, and the live sequences' cache."""
+    w = engine.model.weight_bytes()      # every matrix a step multiplies by (the embedding table is only gathered from)
+    per_token = sum(2 * g.need.n_kv_heads * g.need.head_dim * g.pool.element_size() * len(g.entries)
+                    for g in engine.cache.groups)
+    return w + batch * context * per_token
+
+
+def time_decode(engine, batch, context, steps, warmup, sampler=None):
+    """Device-chained decode steps, timed with CUDA events.  Returns (ms per step, launches per step,
+    clock summary)."""
+    import torch
+    slots = fill_cache(engine, batch, context, steps + warmup + 8)
+    g = engine.decode_graph(batch)
+    g.stage(slots, [1] * batch, [context] * batch, [0.0] * batch, [0.5] * batch)
+    if g.graph is None:
+        g.capture(pool=engine._graph_pool)
+        if engine._graph_pool is None:
+            engine._graph_pool = g.graph.pool()
+    g.stage(slots, [1] * batch, [context] * batch, [0.0] * batch, [0.5] * batch)
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = engine.ops.lib.launches
+    t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    launches = engine.ops.lib.launches - before
+    ms = e0.elapsed_time(e1) / steps
+    engine.ops.check_errors()
+    for s in slots:
+        engine.end_sequence(s)
+    clocks = sampler.summary(t0, t1) if sampler else None
+    return ms, launches, clocks
+
+
+def time_decode_e2e(engine, batch, context, steps, warmup):
+    """The same step through Engine: host token ids in (pinned copy), sampled ids out, every step."""
+    import torch
+    slots = fill_cache(engine, batch, context, 0)
+    feed = [(s, [1]) for s in slots]
+    temps, us = [0.0] * batch, [0.5] * batch
+    for _ in range(warmup):
+        ids = engine._step_sample(feed, temps, us)
+        feed = [(s, [i]) for s, i in zip(slots, ids)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ids = engine._step_sample(feed, temps, us)
+        feed = [(s, [i]) for s, i in zip(slots, ids)]
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    g = engine.decode_graph(batch)
+    for s in slots:
+        engine.end_sequence(s)
+    return dt / steps * 1e3, g.h2d_bytes, g.d2h_bytes
+
+
+def time_prefill(engine, tokens, reps=3):
+    import torch
+    from rbitnet_b200 import StepEntry
+    ids = torch.randint(0, engine.config.vocab_size, (tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+    times = []
+    for r in range(reps + 1):
+        s = engine.new_sequence()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        out = engine.step([StepEntry(s, ids, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        assert bool(torch.isfinite(out).all())
+        engine.end_sequence(s)
+        if r > 0:
+            times.append(e0.elapsed_time(e1))
+    return min(times)
+
+
+def prefill_flops(cfg, layers, tokens):
+    E, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, K, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = 2 * tokens * (E * (H + 2 * K) * D + H * D * E + 3 * E * F)
+    attn = 4 * H * D * tokens * (tokens + 1) / 2
+    return layers * (per_layer + attn) + 2 * E * V
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1/64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "azerothl/Rbitnet is a Rust workspace: no Rust toolchain in this image, no network to get "
+                          "one, and it loads GGUF files only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+
+    import torch
+    from rbitnet_b200 import Engine
+    pk = peaks()
+    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
+    room = steps + warmup + 16
+    max_tokens = max(b * (-(-(PROMPT_LEN + room) // 64) * 64) for b in batches) + 64 * 64
+    t_build = time.time()
+    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seq=8192, max_batch=64)
+    for g in engine.cache.groups:                   # random cache content; finite values, no work depends on it
+        g.pool.normal_(0.0, 1.0)
+    torch.cuda.synchronize()
+    build_s = time.time() - t_build
+
+    sampler = ClockSampler().start()
+    try:
+        ms, launches, clocks = time_decode(engine, args.batch, PROMPT_LEN, steps, warmup, sampler)
+        e2e_ms, h2d, d2h = time_decode_e2e(engine, args.batch, PROMPT_LEN, steps, warmup)
+        points, prefill = {}, None
+        if not args.no_points:
+            for b in (1, 64):
+                if b == args.batch:
+                    points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
+                else:
+                    pms, _, _ = time_decode(engine, b, PROMPT_LEN, max(8, steps // 2), warmup)
+                    points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+            pf_ms = time_prefill(engine, PROMPT_LEN)
+            flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
+            prefill = {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
+                       "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+                       "peak_tflops": pk["bf16_tflops_sustained"], "peak": f"bf16 sustained, {pk['source']}"}
+    finally:
+        sampler.stop()
+
+    nbytes = decode_bytes(engine, args.batch, PROMPT_LEN)
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    value = args.batch / ms * 1e3
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cache)",
+        "impl": "ours",
+        "config": {"model": "Llama-3-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False,
+                   "global_batch": args.batch, "seq_len": PROMPT_LEN, "max_context": 8192,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read once per step)",
+                   "step": "one decode token per sequence, CUDA graph, sampled on device"},
+        "e2e": {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": nbytes,
+                     "peak_source": pk["source"]},
+        "build_s": round(build_s, 1),
+    }
+    if prefill is not None:
+        line["prefill"] = prefill
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -226,3 +226,22 @@ RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R,
   RB_CHECK_LAUNCH("rb_gather_rows");
   return 0;
 }
+
+// ---------------------------------------------------------------- decode bookkeeping on the device
+// After a decode step has sampled: the sampled ids become the next step's tokens and every
+// position moves on by one, so that steps can follow one another without the host.
+__global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ tok_pos,
+                                      const int* __restrict__ sampled, int B) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B) {
+    token_ids[i] = sampled[i];
+    tok_pos[i] += 1;
+  }
+}
+
+RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled, int B, cudaStream_t stream) {
+  if (B == 0) return 0;
+  decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(token_ids, tok_pos, sampled, B);
+  RB_CHECK_LAUNCH("rb_decode_advance");
+  return 0;
+}

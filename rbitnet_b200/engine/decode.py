@@ -1,0 +1,92 @@
+"""A decode step captured as a CUDA graph: one token for each of B sequences, sampled on
+the device.
+
+A decode step is a chain of some hundred small kernels; launched one by one from the
+host, the gaps between them cost as much as the kernels.  The chain is therefore
+captured once per batch size and replayed.  Which sequences, tokens and positions a
+replay works on is data in fixed device buffers (slot ids index the cache's page
+tables), so one graph serves any B sequences.  Per step the host writes one small
+pinned buffer, copies it, replays, and reads B sampled ids back.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .step import SeqChunk, StepContext, StepMeta
+
+
+class DecodeGraph:
+    def __init__(self, model, cache, ops, batch: int):
+        self.model, self.cache, self.ops, self.B = model, cache, ops, batch
+        B, dev = batch, ops.device
+        # [tokens | positions | slots | wanted rows | temperatures | uniforms] as one int32 buffer
+        self.buf = torch.zeros(6 * B, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(6 * B, dtype=torch.int32).pin_memory()
+        self.host_np = self.host.numpy()
+        self.host_f = self.host_np.view(np.float32)
+        self.host_np[3 * B:4 * B] = np.arange(B, dtype=np.int32)
+        self.token_ids, self.tok_pos, self.tok_slot, self.want = (self.buf[i * B:(i + 1) * B] for i in range(4))
+        fl = self.buf.view(torch.float32)
+        self.temps, self.uniforms = fl[4 * B:5 * B], fl[5 * B:6 * B]
+        self.out_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.meta = StepMeta(self.token_ids, self.tok_pos, self.tok_slot, self.want, B, B,
+                             [SeqChunk(0, 0, 1, i) for i in range(B)], True, cache.max_seq)
+        self.graph = None
+        self.sampled = None
+        self.kernels = 0
+
+    def _body(self):
+        logits = self.model.forward(StepContext(self.ops, self.meta, self.cache))
+        sampled = self.ops.sample(logits, self.temps, self.uniforms)
+        self.ops.decode_advance(self.token_ids, self.tok_pos, sampled)
+        return sampled
+
+    def capture(self, pool=None):
+        """The buffers must hold a valid step (live slots with reserved room) while this runs:
+        the step is executed once for real before it is recorded."""
+        keep = self.buf.clone()
+        side = torch.cuda.Stream(device=self.ops.device)
+        side.wait_stream(torch.cuda.current_stream(self.ops.device))
+        with torch.cuda.stream(side):
+            self._body()
+        torch.cuda.current_stream(self.ops.device).wait_stream(side)
+        self.buf.copy_(keep)
+        before = self.ops.lib.launches
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=pool):
+            self.sampled = self._body()
+        self.kernels = self.ops.lib.launches - before
+        self.buf.copy_(keep)
+        return self
+
+    # ---- one step, host tokens in, host ids out
+    def stage(self, slots: Sequence[int], tokens: Sequence[int], positions: Sequence[int],
+              temperatures: Sequence[float], uniforms: Sequence[float]) -> None:
+        B = self.B
+        h = self.host_np
+        h[0:B] = tokens
+        h[B:2 * B] = positions
+        h[2 * B:3 * B] = slots
+        self.host_f[4 * B:5 * B] = temperatures
+        self.host_f[5 * B:6 * B] = uniforms
+        self.buf.copy_(self.host, non_blocking=True)
+
+    def replay(self) -> None:
+        self.graph.replay()
+        self.ops.lib.launches += self.kernels
+
+    def read(self) -> List[int]:
+        self.out_host.copy_(self.sampled, non_blocking=True)
+        torch.cuda.current_stream(self.ops.device).synchronize()
+        return self.out_host.tolist()
+
+    @property
+    def h2d_bytes(self) -> int:
+        return self.host.numel() * 4
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.out_host.numel() * 4

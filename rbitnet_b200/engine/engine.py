@@ -53,7 +53,8 @@ class Engine:
     def __init__(self, config: ModelConfig, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
                  device="cuda:0", max_tokens: Optional[int] = None, max_seq: Optional[int] = None,
                  max_batch: int = 64, page_size: int = PAGE_SIZE, max_batch_tokens: int = 8192,
-                 ops=None, model_path: Optional[Path] = None, verbose: bool = False):
+                 ops=None, model_path: Optional[Path] = None, verbose: bool = False,
+                 use_graphs: bool = True):
         """max_seq: longest sequence (default: the configuration's max positions).
         max_tokens: cache size in positions over all live sequences, each rounded up to
         whole pages (default: max_batch sequences of max_seq)."""
@@ -78,6 +79,10 @@ class Engine:
         self.stepper = Stepper(self.model, self.cache, self.ops, max_batch_tokens=max_batch_tokens)
         self.stop_ids = list(self.spec.stop_ids)
         self._tokenizer = None
+        #: decode steps run as captured CUDA graphs (one per batch size)
+        self.use_graphs = use_graphs and ops is None
+        self._graphs = {}
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -146,7 +151,39 @@ class Engine:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         return self.stepper.step(entries)
 
+    def decode_graph(self, batch: int):
+        """The captured decode step for ``batch`` sequences (made at first use).  Needs ``batch``
+        live slots with room for one more token each at the time of the first call."""
+        g = self._graphs.get(batch)
+        if g is None:
+            from .decode import DecodeGraph
+            g = DecodeGraph(self.model, self.cache, self.ops, batch)
+            self._graphs[batch] = g
+        return g
+
+    def _decode_step(self, feed, temperatures, uniforms) -> List[int]:
+        slots = [s for s, _ in feed]
+        positions = [self.cache.length(s) for s in slots]
+        for s in slots:
+            self.cache.reserve(s, 1)
+        self.cache.upload_tables()
+        g = self.decode_graph(len(feed))
+        g.stage(slots, [t[0] for _, t in feed], positions, temperatures, uniforms)
+        if g.graph is None:
+            g.capture(pool=self._graph_pool)
+            if self._graph_pool is None:
+                self._graph_pool = g.graph.pool()
+        g.replay()
+        ids = g.read()
+        for s in slots:
+            self.cache.advance(s, 1)
+        return ids
+
     def _step_sample(self, feed, temperatures, uniforms) -> List[int]:
+        if self.use_graphs and all(len(t) == 1 for _, t in feed):
+            ids = self._decode_step(feed, temperatures, uniforms)
+            self.ops.check_errors()
+            return ids
         entries = [StepEntry(slot, toks, [len(toks) - 1]) for slot, toks in feed]
         logits = self.stepper.step(entries)
         params = torch.from_numpy(np.asarray([temperatures, uniforms], dtype=np.float32)).to(self.ops.device)

@@ -25,6 +25,7 @@ _SIGNATURES = {
     "rb_sample": [P, P, L, I, I, P, P, P],
     "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, P],
     "rb_read_error_flag": [P, I],
+    "rb_decode_advance": [P, P, P, I, P],
 }
 
 

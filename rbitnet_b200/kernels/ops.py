@@ -204,3 +204,8 @@ class CudaOps:
         self.lib.call("rb_sample", _ptr(out), _ptr(logits), logits.stride(0), R, V, _ptr(temperature),
                       _ptr(uniform), self._stream())
         return out
+
+    def decode_advance(self, token_ids: torch.Tensor, tok_pos: torch.Tensor, sampled: torch.Tensor) -> None:
+        """token_ids <- sampled; tok_pos += 1 (the next decode step's inputs, made on the device)."""
+        self.lib.call("rb_decode_advance", _ptr(token_ids), _ptr(tok_pos), _ptr(sampled), token_ids.shape[0],
+                      self._stream())
