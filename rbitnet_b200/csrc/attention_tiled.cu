@@ -1,0 +1,425 @@
+// Tiled attention over the paged cache for the bfloat16 path: prefill (many query rows per
+// sequence) and decode (one token per sequence, keys split over several CTAs).
+//
+// One CTA works for ONE kv head of ONE sequence.  Its rows are (token, query head) pairs of the
+// heads that share this kv head (row r -> token r / G, head kvh*G + r % G), so the G query heads
+// of a group reuse every key and value the CTA loads.  Keys and values come in tiles of 64
+// positions, which is one page (or an aligned part of a page) of the cache: a contiguous
+// [64, D] block per kv head, fetched with cp.async into a double buffer.
+//
+// Per tile: S = Q K^T on mma.sync (bfloat16 in, float32 out); the score is (q.k)*scale with
+// the scale folded into the exponent; causal and window masks by position; running max and sum
+// in float32; P rounded to bfloat16 only as the operand of P V, accumulated in float32.
+// crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound, P V), :102-114 (softmax).
+//
+// Prefill mode: 4 warps take 16 rows each and all 64 keys of a tile.  Decode mode: the rows are
+// one token's G heads (G <= 16); the 4 warps take 16 keys each of every tile and are merged at
+// the end; with n_splits > 1 each CTA covers a part of the sequence's tiles and writes an
+// unnormalised partial (max, sum, O) that rb_attention_combine merges in split order.
+#include "rb_common.cuh"
+
+namespace {
+
+constexpr int TILE_KEYS = 64;
+constexpr int WARPS = 4;
+constexpr int ROWS = 16 * WARPS;   // rows of a prefill CTA
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct AttnParams {
+  const __nv_bfloat16* q;   // [T, H, D]
+  __nv_bfloat16* out;       // [T, H*D]
+  RbPagedLayer cache;
+  const int* tok_pos;
+  const int* tok_slot;
+  const int* tile_tok0;     // prefill: first token (row of the batch) of each tile
+  const int* tile_ntok;     // prefill: tokens in each tile (same sequence, consecutive positions)
+  int H, G;
+  float scale_log2;         // scale * log2(e)
+  int window;               // 0: none
+  float* part_o;            // decode: [T, H, n_splits, D]
+  float* part_ml;           // decode: [T, H, n_splits, 2]
+  int n_splits;
+};
+
+// Row stride of the shared tiles: D values plus 8 of padding, so that the eight 16-byte rows an
+// ldmatrix reads fall into different banks for every D that is a multiple of 16.
+template <int D> struct Smem {
+  static constexpr int LD = D + 8;
+  static constexpr int Q_ELEMS = ROWS * LD;
+  static constexpr int KV_ELEMS = TILE_KEYS * LD;
+  static constexpr size_t BYTES = (size_t)(Q_ELEMS + 4 * KV_ELEMS) * 2;
+};
+
+template <int D, bool DECODE>
+__global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
+  using S = Smem<D>;
+  constexpr int LD = S::LD;
+  constexpr int NT = DECODE ? 2 : 8;          // 8-key column tiles of S per warp
+  constexpr int DT = D / 8;                   // 8-wide column tiles of O
+  extern __shared__ __align__(16) uint8_t smem_bytes[];
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
+  __nv_bfloat16* sK = sQ + S::Q_ELEMS;        // [2][64][LD]
+  __nv_bfloat16* sV = sK + 2 * S::KV_ELEMS;   // [2][64][LD]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int kvh = blockIdx.y;
+  const int G = p.G, H = p.H;
+  int tok0, ntok;
+  if (DECODE) { tok0 = blockIdx.x; ntok = 1; } else { tok0 = p.tile_tok0[blockIdx.x]; ntok = p.tile_ntok[blockIdx.x]; }
+  const int slot = p.tok_slot[tok0];
+  const int pos0 = p.tok_pos[tok0];
+  const int n_rows = ntok * G;
+  const int key_hi = pos0 + ntok - 1;                                    // last key any row may see
+  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;      // first key any row may see
+  int kt_begin = key_lo / TILE_KEYS, kt_end = key_hi / TILE_KEYS + 1;
+  if (DECODE && p.n_splits > 1) {
+    const int per = (kt_end - kt_begin + p.n_splits - 1) / p.n_splits;
+    kt_begin += blockIdx.z * per;
+    kt_end = min(kt_end, kt_begin + per);
+  }
+
+  // ---- Q rows into shared memory (rows beyond n_rows are zero)
+  for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += WARPS * 32) {
+    const int r = idx / (D / 8), c = idx % (D / 8);
+    if (DECODE && r >= 16) break;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows) {
+      const int tok = tok0 + r / G, head = kvh * G + r % G;
+      v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
+  }
+
+  const __nv_bfloat16* Kbase = reinterpret_cast<const __nv_bfloat16*>(p.cache.k);
+  const __nv_bfloat16* Vbase = reinterpret_cast<const __nv_bfloat16*>(p.cache.v);
+  auto load_tile = [&](int kt, int buf) {
+    const int key0 = kt * TILE_KEYS;
+    const int page = p.cache.page_table[(int64_t)slot * p.cache.max_pages + key0 / p.cache.page_size];
+    const int64_t off = (((int64_t)page * p.cache.n_kv_heads + kvh) * p.cache.page_size + key0 % p.cache.page_size) * D;
+    const __nv_bfloat16* ksrc = Kbase + off;
+    const __nv_bfloat16* vsrc = Vbase + off;
+    __nv_bfloat16* kd = sK + buf * S::KV_ELEMS;
+    __nv_bfloat16* vd = sV + buf * S::KV_ELEMS;
+    for (int idx = threadIdx.x; idx < TILE_KEYS * (D / 8); idx += WARPS * 32) {
+      const int r = idx / (D / 8), c = idx % (D / 8);
+      cp_async16(kd + r * LD + c * 8, ksrc + r * D + c * 8);
+      cp_async16(vd + r * LD + c * 8, vsrc + r * D + c * 8);
+    }
+  };
+
+  // ---- per-warp state
+  const int rb = DECODE ? 0 : warp * 16;          // first row of this warp
+  const int kw0 = DECODE ? warp * 16 : 0;         // first key of a tile this warp takes
+  float o[DT][4];
+#pragma unroll
+  for (int i = 0; i < DT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  // rows g and g+8 of this warp: their positions and validity
+  int row_pos[2], row_lo[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = rb + g + 8 * h;
+    row_ok[h] = r < n_rows;
+    row_pos[h] = pos0 + r / G;
+    row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+  }
+
+  if (kt_begin < kt_end) {
+    load_tile(kt_begin, 0);
+    cp_async_commit();
+  }
+  for (int kt = kt_begin; kt < kt_end; ++kt) {
+    const int buf = (kt - kt_begin) & 1;
+    if (kt + 1 < kt_end) {
+      load_tile(kt + 1, buf ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const __nv_bfloat16* tK = sK + buf * S::KV_ELEMS;
+    const __nv_bfloat16* tV = sV + buf * S::KV_ELEMS;
+    const int key_base = kt * TILE_KEYS + kw0;
+
+    // a warp whose rows see none of this tile's keys skips it (prefill: tiles past the diagonal)
+    const bool warp_has_rows = DECODE || rb < n_rows;
+    const int warp_last_pos = DECODE ? pos0 : pos0 + min(n_rows - 1, rb + 15) / G;
+    if (warp_has_rows && key_base <= warp_last_pos) {
+      // ---- S = Q K^T
+      float s[NT][4];
+#pragma unroll
+      for (int i = 0; i < NT; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, smem_addr(sQ + (rb + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + kk * 16 + (lane >> 4) * 8));
+#pragma unroll
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t b[4];
+          // matrices: (keys nt*8.., d lo), (keys nt*8.., d hi), (keys (nt+1)*8.., d lo), (keys (nt+1)*8.., d hi)
+          ldmatrix_x4(b, smem_addr(tK + (kw0 + nt * 8 + (lane >> 4) * 8 + (lane & 7)) * LD + kk * 16 + ((lane >> 3) & 1) * 8));
+          mma_bf16(s[nt], a, b[0], b[1]);
+          mma_bf16(s[nt + 1], a, b[2], b[3]);
+        }
+      }
+      // ---- mask, running max
+      float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int h = c >> 1;
+          const int key = key_base + nt * 8 + t4 * 2 + (c & 1);
+          const bool ok = row_ok[h] && key <= row_pos[h] && key >= row_lo[h];
+          const float v = ok ? s[nt][c] * p.scale_log2 : -INFINITY;
+          s[nt][c] = v;
+          m_new[h] = fmaxf(m_new[h], v);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];      // a row with nothing allowed so far
+        corr[h] = exp2f(m_run[h] - m_use[h]);                    // exp2(-inf) = 0 on the first tile
+        m_run[h] = m_new[h];
+        l_run[h] *= corr[h];
+      }
+#pragma unroll
+      for (int i = 0; i < DT; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0];
+        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+      }
+      // ---- P = exp2(S - m), row sums, P V
+      uint32_t pa[NT / 2][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const float p0 = exp2f(s[nt][0] - m_use[0]), p1 = exp2f(s[nt][1] - m_use[0]);
+        const float p2 = exp2f(s[nt][2] - m_use[1]), p3 = exp2f(s[nt][3] - m_use[1]);
+        l_run[0] += p0 + p1;
+        l_run[1] += p2 + p3;
+        pa[nt / 2][(nt & 1) * 2 + 0] = pack_bf16(p0, p1);
+        pa[nt / 2][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int j = 0; j < NT / 2; ++j) {
+#pragma unroll
+        for (int dn = 0; dn < DT; dn += 2) {
+          uint32_t b[4];
+          // matrices: (keys 0-7, d dn), (keys 8-15, d dn), (keys 0-7, d dn+1), (keys 8-15, d dn+1)
+          ldmatrix_x4_trans(b, smem_addr(tV + (kw0 + j * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + (dn + (lane >> 4)) * 8));
+          mma_bf16(o[dn], pa[j], b[0], b[1]);
+          mma_bf16(o[dn + 1], pa[j], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();   // the other buffer is refilled at the top of the next round
+  }
+
+  // ---- row sums over the four threads of a quad
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+
+  if (!DECODE) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = rb + g + 8 * h;
+      if (r >= n_rows) continue;
+      const int tok = tok0 + r / G, head = kvh * G + r % G;
+      const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
+      __nv_bfloat16* dst = p.out + ((int64_t)tok * H + head) * D;
+#pragma unroll
+      for (int dn = 0; dn < DT; ++dn) {
+        *reinterpret_cast<uint32_t*>(dst + dn * 8 + t4 * 2) = pack_bf16(o[dn][2 * h] * inv, o[dn][2 * h + 1] * inv);
+      }
+    }
+    return;
+  }
+
+  // ---- decode: merge the four warps (each saw a quarter of every tile's keys)
+  // shared layout (over the K/V buffers, free now): per warp [16 rows][D] O, then [16] m, [16] l
+  float* mO = reinterpret_cast<float*>(sK);
+  float* mM = mO + WARPS * 16 * D;
+  float* mL = mM + WARPS * 16;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + 8 * h;
+#pragma unroll
+    for (int dn = 0; dn < DT; ++dn) {
+      mO[(warp * 16 + r) * D + dn * 8 + t4 * 2] = o[dn][2 * h];
+      mO[(warp * 16 + r) * D + dn * 8 + t4 * 2 + 1] = o[dn][2 * h + 1];
+    }
+    if (t4 == 0) {
+      mM[warp * 16 + r] = m_run[h];
+      mL[warp * 16 + r] = l_run[h];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < n_rows * D; idx += WARPS * 32) {
+    const int r = idx / D, d = idx % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, mM[w * 16 + r]);
+    const float mu = m == -INFINITY ? 0.f : m;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float f = exp2f(mM[w * 16 + r] - mu);
+      acc += mO[(w * 16 + r) * D + d] * f;
+      l += mL[w * 16 + r] * f;
+    }
+    const int head = kvh * G + r;
+    if (p.n_splits > 1) {
+      const int64_t base = ((int64_t)tok0 * H + head) * p.n_splits + blockIdx.z;
+      p.part_o[base * D + d] = acc;
+      if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
+    } else {
+      p.out[((int64_t)tok0 * H + head) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+  }
+}
+
+// Merges the partials of a split decode in split order.
+__global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, int n_splits, int D) {
+  const int64_t th = blockIdx.x;   // token * H + head
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(th * n_splits + s) * 2]);
+  const float mu = m == -INFINITY ? 0.f : m;
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) l += part_ml[(th * n_splits + s) * 2 + 1] * exp2f(part_ml[(th * n_splits + s) * 2] - mu);
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s)
+      acc += part_o[(th * n_splits + s) * D + d] * exp2f(part_ml[(th * n_splits + s) * 2] - mu);
+    out[th * D + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int D, bool DECODE>
+int launch_one(const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  auto kernel = attn_tiled_kernel<D, DECODE>;
+  size_t smem = Smem<D>::BYTES;
+  if (DECODE) {
+    const size_t merge = (size_t)(WARPS * 16 * D + 2 * WARPS * 16) * 4;
+    const size_t kv = (size_t)4 * Smem<D>::KV_ELEMS * 2;
+    if (merge > kv) smem += merge - kv;
+  }
+  static bool configured = false;
+  if (!configured) {
+    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  kernel<<<grid, WARPS * 32, smem, stream>>>(p);
+  RB_CHECK_LAUNCH("rb_attention_tiled");
+  return 0;
+}
+
+template <bool DECODE>
+int launch_d(int D, const AttnParams& p, dim3 grid, cudaStream_t stream) {
+  switch (D) {
+    case 16: return launch_one<16, DECODE>(p, grid, stream);
+    case 32: return launch_one<32, DECODE>(p, grid, stream);
+    case 48: return launch_one<48, DECODE>(p, grid, stream);
+    case 64: return launch_one<64, DECODE>(p, grid, stream);
+    case 80: return launch_one<80, DECODE>(p, grid, stream);
+    case 96: return launch_one<96, DECODE>(p, grid, stream);
+    case 112: return launch_one<112, DECODE>(p, grid, stream);
+    case 128: return launch_one<128, DECODE>(p, grid, stream);
+    case 160: return launch_one<160, DECODE>(p, grid, stream);
+    case 192: return launch_one<192, DECODE>(p, grid, stream);
+    case 256: return launch_one<256, DECODE>(p, grid, stream);
+  }
+  RB_FAIL("rb_attention_tiled: head_dim %d is not built (16..128 in steps of 16, 160, 192, 256)", D);
+}
+
+}  // namespace
+
+// Whether the tiled kernel takes these sizes (the caller uses the plain kernel otherwise).
+RB_EXPORT int rb_attention_tiled_supports(int H, int Kh, int D, int page_size, int decode) {
+  if (Kh <= 0 || H % Kh) return 0;
+  const int G = H / Kh;
+  const bool d_ok = (D % 16 == 0 && D >= 16 && D <= 128) || D == 160 || D == 192 || D == 256;
+  if (!d_ok || page_size % TILE_KEYS) return 0;
+  if (decode) return G <= 16;
+  return G <= ROWS;
+}
+
+// Prefill: n_tiles tiles of tokens; tile i covers tile_ntok[i] <= 64/G tokens of one sequence
+// starting at batch row tile_tok0[i].
+RB_EXPORT int rb_attention_prefill(void* out, const void* q, const void* cache_k, const void* cache_v,
+                                   const int* page_table, int max_pages, int page_size, const int* tok_pos,
+                                   const int* tok_slot, const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                                   int H, int Kh, int D, float scale, int window, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  RB_REQUIRE(rb_attention_tiled_supports(H, Kh, D, page_size, 0), "rb_attention_prefill: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+  p.cache = RbPagedLayer{(void*)cache_k, (void*)cache_v, page_table, max_pages, page_size, Kh, D};
+  p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.tile_tok0 = tile_tok0; p.tile_ntok = tile_ntok;
+  p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  p.part_o = nullptr; p.part_ml = nullptr; p.n_splits = 1;
+  return launch_d<false>(D, p, dim3(n_tiles, Kh, 1), stream);
+}
+
+// Decode: one token per sequence (batch row b is sequence b's token).  With n_splits > 1,
+// part_o [B, H, n_splits, D] and part_ml [B, H, n_splits, 2] float32 are scratch.
+RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k, const void* cache_v,
+                                  const int* page_table, int max_pages, int page_size, const int* tok_pos,
+                                  const int* tok_slot, int B, int H, int Kh, int D, float scale, int window,
+                                  float* part_o, float* part_ml, int n_splits, cudaStream_t stream) {
+  if (B == 0) return 0;
+  RB_REQUIRE(rb_attention_tiled_supports(H, Kh, D, page_size, 1), "rb_attention_decode: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
+  RB_REQUIRE(n_splits >= 1 && n_splits <= 65535, "rb_attention_decode: n_splits %d", n_splits);
+  RB_REQUIRE(n_splits == 1 || (part_o && part_ml), "rb_attention_decode: split decode needs scratch");
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+  p.cache = RbPagedLayer{(void*)cache_k, (void*)cache_v, page_table, max_pages, page_size, Kh, D};
+  p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.tile_tok0 = nullptr; p.tile_ntok = nullptr;
+  p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
+  if (launch_d<true>(D, p, dim3(B, Kh, n_splits), stream) != 0) return -1;
+  if (n_splits > 1) {
+    attn_combine_kernel<<<B * H, D >= 128 ? 128 : 64, 0, stream>>>((__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
+    RB_CHECK_LAUNCH("rb_attention_combine");
+  }
+  return 0;
+}

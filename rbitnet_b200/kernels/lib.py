@@ -26,6 +26,8 @@ _SIGNATURES = {
     "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, P],
     "rb_read_error_flag": [P, I],
     "rb_decode_advance": [P, P, P, I, P],
+    "rb_attention_prefill": [P, P, P, P, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
+    "rb_attention_decode": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
 }
 
 
@@ -42,6 +44,7 @@ class KernelLibrary:
         self.launches = 0   # kernels launched through this library, for the bench's record
         for name, argtypes in _SIGNATURES.items():
             self.declare(name, argtypes)
+        self.declare("rb_attention_tiled_supports", [I, I, I, I, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

@@ -183,12 +183,53 @@ class CudaOps:
                   window: Optional[int]) -> torch.Tensor:
         """Each new token's queries over its sequence's cached keys up to its own position."""
         T, H, D = q.shape
+        Kh = view.n_kv_heads
         out = torch.empty((T, H * D), dtype=self.dtype, device=self.device)
-        self.lib.call("rb_attention_simple", _ptr(out), _ptr(q), self.code, _ptr(view.k), _ptr(view.v),
-                      _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
-                      _ptr(meta.tok_slot), T, H, view.n_kv_heads, D, float(scale), int(window or 0),
-                      self._stream())
+        win = int(window or 0)
+        if self.dtype == torch.bfloat16 and meta.single_token and \
+                self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 1):
+            n_splits = self._decode_splits(T, Kh, meta.max_context)
+            part_o = part_ml = None
+            if n_splits > 1:
+                part_o = torch.empty((T, H, n_splits, D), dtype=torch.float32, device=self.device)
+                part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=self.device)
+            self.lib.call("rb_attention_decode", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
+                          _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
+                          _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, _ptr(part_o), _ptr(part_ml),
+                          n_splits, self._stream(), launches=2 if n_splits > 1 else 1)
+        elif self.dtype == torch.bfloat16 and \
+                self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 0):
+            tok0, ntok, n_tiles = self._prefill_tiles(meta, 64 // (H // Kh))
+            self.lib.call("rb_attention_prefill", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
+                          _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
+                          _ptr(meta.tok_slot), _ptr(tok0), _ptr(ntok), n_tiles, H, Kh, D, float(scale), win,
+                          self._stream())
+        else:
+            self.lib.call("rb_attention_simple", _ptr(out), _ptr(q), self.code, _ptr(view.k), _ptr(view.v),
+                          _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
+                          _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, self._stream())
         return out
+
+    @staticmethod
+    def _decode_splits(batch: int, n_kv_heads: int, max_context: int) -> int:
+        """Parts a decode's keys are cut into so that about two CTAs per SM have work."""
+        tiles = max(1, -(-max_context // 64))
+        return max(1, min(32, tiles, -(-296 // (batch * n_kv_heads))))
+
+    def _prefill_tiles(self, meta, tokens_per_tile: int):
+        """Tiles of at most ``tokens_per_tile`` consecutive tokens of one sequence (device int32 arrays);
+        made once per step and kept on the step's meta."""
+        import numpy as np
+        key = ("attention_tiles", tokens_per_tile)
+        if key not in meta.extra:
+            tok0, ntok = [], []
+            for c in meta.seqs:
+                for i in range(0, c.n_new, tokens_per_tile):
+                    tok0.append(c.offset + i)
+                    ntok.append(min(tokens_per_tile, c.n_new - i))
+            dev = torch.from_numpy(np.asarray([tok0, ntok], dtype=np.int32)).to(self.device)
+            meta.extra[key] = (dev[0], dev[1], len(tok0))
+        return meta.extra[key]
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         R, E = rows.shape[0], x.shape[1]

@@ -129,18 +129,20 @@ def _paged(ops, n_slots, max_pages, page, Kh, D, lens, seed):
     from rbitnet_b200.cache import CacheLayerView
     g = torch.Generator(device="cuda").manual_seed(seed)
     n_pages = n_slots * max_pages
-    k = torch.zeros(n_pages, Kh, page, D, device="cuda", dtype=ops.dtype)
-    v = torch.zeros_like(k)
+    # places no sequence owns hold large values: a key read past a sequence's end would show
+    k = (torch.randn(n_pages, Kh, page, D, device="cuda", generator=g) * 30).to(ops.dtype)
+    v = (torch.randn(n_pages, Kh, page, D, device="cuda", generator=g) * 30).to(ops.dtype)
     perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).to(torch.int32)
-    table = perm.reshape(n_slots, max_pages).cuda()
+    table_host = perm.reshape(n_slots, max_pages)
+    table = table_host.cuda()
     dense_k, dense_v = [], []
     for s, n in enumerate(lens):
         kk = torch.randn(n, Kh, D, device="cuda", generator=g).to(ops.dtype)
         vv = torch.randn(n, Kh, D, device="cuda", generator=g).to(ops.dtype)
-        for p in range(n):
-            pg = int(table[s, p // page])
-            k[pg, :, p % page] = kk[p]
-            v[pg, :, p % page] = vv[p]
+        for p0 in range(0, n, page):
+            pg, m = int(table_host[s, p0 // page]), min(page, n - p0)
+            k[pg, :, :m] = kk[p0:p0 + m].transpose(0, 1)
+            v[pg, :, :m] = vv[p0:p0 + m].transpose(0, 1)
         dense_k.append(kk)
         dense_v.append(vv)
     return CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0), dense_k, dense_v
@@ -158,24 +160,64 @@ def _attn_ref(q, k, v, pos, scale, window):
     return out.reshape(-1)
 
 
-@pytest.mark.parametrize("H,Kh,D,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 64, None), (6, 3, 48, 16, 5),
-                                                (8, 2, 128, 64, None), (5, 5, 80, 32, 40), (2, 1, 256, 16, None)])
+def _meta(rows, single_token=False, max_context=512):
+    """rows: (slot, position) per batch row; consecutive positions of one slot form one chunk."""
+    from rbitnet_b200.engine.step import SeqChunk
+    m = _Meta()
+    m.tok_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32, device="cuda")
+    m.tok_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32, device="cuda")
+    m.seqs, i = [], 0
+    while i < len(rows):
+        j = i + 1
+        while j < len(rows) and rows[j][0] == rows[i][0] and rows[j][1] == rows[j - 1][1] + 1:
+            j += 1
+        m.seqs.append(SeqChunk(rows[i][0], rows[i][1], j - i, i))
+        i = j
+    m.single_token, m.max_context, m.extra = single_token, max_context, {}
+    m.n_tokens = len(rows)
+    return m
+
+
+ATTN_CASES = [(4, 2, 16, 16, None), (3, 1, 32, 64, None), (6, 3, 48, 16, 5), (8, 2, 128, 64, None),
+              (5, 5, 80, 32, 40), (2, 1, 256, 16, None), (6, 2, 64, 64, 100), (32, 8, 128, 128, None),
+              (7, 7, 96, 64, None), (4, 1, 112, 64, 33), (18, 1, 16, 64, None), (2, 2, 256, 64, None)]
+
+
+@pytest.mark.parametrize("H,Kh,D,page,window", ATTN_CASES)
 def test_attention_over_the_paged_cache(ops32, ops16, H, Kh, D, page, window):
-    """Queries at mixed positions of three sequences (prompt rows and single decode rows in one batch)."""
-    lens = [70, 9, 130]
+    """Queries at mixed positions of three sequences: runs of prompt rows (long enough to cross
+    tiles and the diagonal) and single rows in one batch."""
+    lens = [200, 9, 130]
     scale = 0.7 / math.sqrt(D)
+    max_pages = -(-256 // page)
     for ops, tol in ((ops32, 3e-6), (ops16, 8e-3)):
-        view, ks, vs = _paged(ops, 3, 4, page if page * 4 >= 130 else 64, Kh, D, lens, seed=7)
-        rows = [(0, 69), (1, 0), (1, 8), (2, 64), (2, 129), (0, 5)] + [(2, p) for p in range(100, 110)]
+        view, ks, vs = _paged(ops, 3, max_pages, page, Kh, D, lens, seed=7)
+        rows = ([(0, 69), (1, 0), (1, 8), (2, 64), (2, 129), (0, 5)] + [(2, p) for p in range(100, 110)]
+                + [(0, p) for p in range(30, 200)] + [(1, p) for p in range(0, 9)])
         g = torch.Generator(device="cuda").manual_seed(8)
         q = torch.randn(len(rows), H, D, device="cuda", generator=g).to(ops.dtype) * 2
-        meta = _Meta()
-        meta.tok_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32, device="cuda")
-        meta.tok_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32, device="cuda")
-        got = ops.attention(q, meta, view, H, scale, window)
+        got = ops.attention(q, _meta(rows), view, H, scale, window)
         for i, (s, p) in enumerate(rows):
+            if i > 20 and i % 7:
+                continue
             ref = _attn_ref(q[i], ks[s], vs[s], p, scale, window)
             assert _rel(got[i], ref) < tol, (i, s, p)
+
+
+@pytest.mark.parametrize("H,Kh,D,page,window", ATTN_CASES)
+@pytest.mark.parametrize("max_context", [64, 700])
+def test_decode_attention_with_split_keys(ops16, H, Kh, D, page, window, max_context):
+    """One token per sequence at the end of sequences of very different lengths; the keys are cut
+    into parts (how many depends on the batch and on max_context) and merged."""
+    lens = [1, 700, 64, 65, 333]
+    scale = 1.3 / math.sqrt(D)
+    view, ks, vs = _paged(ops16, len(lens), -(-704 // page), page, Kh, D, lens, seed=12)
+    rows = [(s, n - 1) for s, n in enumerate(lens)]
+    g = torch.Generator(device="cuda").manual_seed(13)
+    q = torch.randn(len(rows), H, D, device="cuda", generator=g).to(BF16) * 2
+    got = ops16.attention(q, _meta(rows, single_token=True, max_context=max_context), view, H, scale, window)
+    for i, (s, p) in enumerate(rows):
+        assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, window)) < 8e-3, (i, s, p)
 
 
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops32):
@@ -192,9 +234,7 @@ def test_attention_finds_one_far_key_and_respects_the_window_edge(ops32):
     pg = int(view.page_table[0, far // page])
     view.k[:, :, :, 3] = 0.0
     view.k[pg, 0, far % page, 3] = 10.0
-    meta = _Meta()
-    meta.tok_slot = torch.zeros(1, dtype=torch.int32, device="cuda")
-    meta.tok_pos = torch.tensor([n - 1], dtype=torch.int32, device="cuda")
+    meta = _meta([(0, n - 1)])
     scale = 1 / math.sqrt(D)
     out = ops32.attention(q, meta, view, H, scale, None).reshape(H, D)
     assert _rel(out[0], vs[0][far, 0]) < 1e-5                       # the far key owns the softmax
@@ -219,9 +259,7 @@ def test_rotation_and_cache_append(ops32, ops16, H, Kh, D, interleaved):
         v = torch.zeros_like(k)
         table = torch.randperm(n_slots * max_pages).to(torch.int32).reshape(n_slots, max_pages).cuda()
         view = CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0)
-        meta = _Meta()
-        meta.tok_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32, device="cuda")
-        meta.tok_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32, device="cuda")
+        meta = _meta(rows)
         i = torch.arange(D // 2, dtype=torch.float32)
         inv = (1.0 / torch.pow(torch.tensor(theta), 2.0 * i / D)).cuda()
         q = ops.rotate_append(qkv, (inv, interleaved, D), meta, view, H)
