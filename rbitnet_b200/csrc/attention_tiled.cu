@@ -423,3 +423,54 @@ RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k,
   }
   return 0;
 }
+
+// ---------------------------------------------------------------- decode without caller scratch
+// See rb_no_alloc.h.  The scratch of the split decode lives in this file-scope device array.
+// In host code its name is only a handle for the runtime, not a device address; the address
+// each device maps it to is looked up once per device and that pointer goes to the kernels.
+#include "rb_no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_static_scratch[RB_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the static scratch on the current device (set up at the first call there).
+int static_scratch(float** ptr) {
+  int dev = -1;
+  RB_CUDA(cudaGetDevice(&dev));
+  RB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "rb_attention_decode_static: device %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    RB_CUDA(cudaGetSymbolAddress((void**)&p, g_static_scratch));
+    RB_REQUIRE(p != nullptr, "rb_attention_decode_static: no device address for the static scratch");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *ptr = g_static_scratch_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+RB_EXPORT int rb_attention_decode_static(void* out, const void* q, const void* cache_k, const void* cache_v,
+                                         const int* page_table, int max_pages, int page_size, const int* tok_pos,
+                                         const int* tok_slot, int B, int H, int Kh, int D, float scale, int window,
+                                         int n_splits, cudaStream_t stream) {
+  if (B == 0) return 0;
+  RB_REQUIRE(B > 0 && H > 0 && D > 0 && n_splits >= 1, "rb_attention_decode_static: bad sizes B=%d H=%d D=%d splits=%d",
+             B, H, D, n_splits);
+  const long long need = (long long)B * H * n_splits * (D + 2);
+  RB_REQUIRE(need <= (long long)RB_STATIC_SCRATCH_FLOATS,
+             "rb_attention_decode_static: B*H*n_splits*(D+2) = %lld float32 values of scratch exceed the static "
+             "array's %d; use fewer splits or rb_attention_decode with caller scratch",
+             need, (int)RB_STATIC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  if (static_scratch(&scratch) != 0) return -1;
+  float* part_o = scratch;                                       // [B, H, n_splits, D]
+  float* part_ml = scratch + (size_t)B * H * n_splits * D;       // [B, H, n_splits, 2]
+  return rb_attention_decode(out, q, cache_k, cache_v, page_table, max_pages, page_size, tok_pos, tok_slot, B, H,
+                             Kh, D, scale, window, part_o, part_ml, n_splits, stream);
+}

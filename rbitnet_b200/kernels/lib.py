@@ -28,6 +28,7 @@ _SIGNATURES = {
     "rb_decode_advance": [P, P, P, I, P],
     "rb_attention_prefill": [P, P, P, P, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
+    "rb_attention_decode_static": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, I, P],
 }
 
 
