@@ -200,6 +200,8 @@ def main():
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1/64 points")
+    ap.add_argument("--phase", default="all", choices=["all", "prefill"],
+                    help="'prefill': only the 2,048-token prefill, one short line (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -225,6 +227,12 @@ def main():
         g.pool.normal_(0.0, 1.0)
     torch.cuda.synchronize()
     build_s = time.time() - t_build
+
+    if args.phase == "prefill":
+        pf_ms = time_prefill(engine, PROMPT_LEN, reps=max(1, min(3, steps)))
+        print(json.dumps({"phase": "prefill", "tokens": PROMPT_LEN, "layers": args.layers, "ms": round(pf_ms, 3),
+                          "tokens_per_s": round(PROMPT_LEN / pf_ms * 1e3, 1)}))
+        return 0
 
     sampler = ClockSampler().start()
     try:

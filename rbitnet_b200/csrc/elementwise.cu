@@ -113,16 +113,25 @@ RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, con
 // `qkv` rows hold [H*D | Kh*D | Kh*D]; with write_kv == 0 only q is read (a
 // layer that reads another layer's cache).  The whole head is rotated
 // (rot_dim == D); a rotated prefix is refused by the entry point.
-template <typename T>
-__global__ void rotate_append_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, int64_t qkv_stride,
+// TI is the type of the input rows: the compute type T, or float when the rows are the float32
+// slices of a product that was split along its inner dimension (n_slices of them, slice_stride
+// elements apart), which are summed here in slice order.
+template <typename T, typename TI>
+__global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict__ qkv, int64_t qkv_stride,
+                                     int n_slices, int64_t slice_stride,
                                      const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
-                                     int rot_dim, int interleaved) {
+                                     int interleaved) {
   const int t = blockIdx.x;
   const int D = cache.head_dim, Kh = cache.n_kv_heads;
   const int pos = tok_pos[t];
   const int slot = tok_slot[t];
-  const T* row = qkv + (int64_t)t * qkv_stride;
+  const TI* row = qkv + (int64_t)t * qkv_stride;
+  auto value = [&](int64_t i) {
+    float v = rb_to_float<TI>(row[i]);
+    for (int s = 1; s < n_slices; ++s) v += rb_to_float<TI>(row[s * slice_stride + i]);
+    return v;
+  };
   const int half = D / 2;
   const int n_rot_heads = H + (write_kv ? Kh : 0);
   T* kdst = (T*)cache.k;
@@ -132,52 +141,70 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const T* __restrict_
     const int head = idx / half, i = idx % half;
     int a, b;
     if (interleaved) { a = 2 * i; b = 2 * i + 1; } else { a = i; b = i + half; }
-    const T* src = row + (int64_t)head * D;  // q heads, then k heads, are contiguous
-    float x0 = rb_to_float<T>(src[a]);
-    float x1 = rb_to_float<T>(src[b]);
-    float s, c;
-    sincosf((float)pos * inv_freq[i], &s, &c);
-    const float y0 = x0 * c - x1 * s;
-    const float y1 = x0 * s + x1 * c;
-    if (head < H) {
-      T* dst = q_out + ((int64_t)t * H + head) * D;
-      dst[a] = rb_from_float<T>(y0);
-      dst[b] = rb_from_float<T>(y1);
-    } else {
-      T* dst = kdst + rb_page_offset(cache, slot, pos, head - H);
-      dst[a] = rb_from_float<T>(y0);
-      dst[b] = rb_from_float<T>(y1);
-    }
+    const int64_t src = (int64_t)head * D;  // q heads, then k heads, are contiguous
+    const float x0 = value(src + a);
+    const float x1 = value(src + b);
+    float sn, cs;
+    sincosf((float)pos * inv_freq[i], &sn, &cs);
+    const float y0 = x0 * cs - x1 * sn;
+    const float y1 = x0 * sn + x1 * cs;
+    T* dst = head < H ? q_out + ((int64_t)t * H + head) * D : kdst + rb_page_offset(cache, slot, pos, head - H);
+    dst[a] = rb_from_float<T>(y0);
+    dst[b] = rb_from_float<T>(y1);
   }
   if (write_kv) {
-    const T* vsrc = row + (int64_t)(H + Kh) * D;
+    const int64_t vsrc = (int64_t)(H + Kh) * D;
     for (int idx = threadIdx.x; idx < Kh * D; idx += blockDim.x) {
       const int kvh = idx / D, d = idx % D;
-      vdst[rb_page_offset(cache, slot, pos, kvh) + d] = vsrc[idx];
+      vdst[rb_page_offset(cache, slot, pos, kvh) + d] = rb_from_float<T>(value(vsrc + idx));
     }
   }
 }
 
+// in_dtype: dtype of qkv (the compute dtype, or RB_F32 slices for a bfloat16 cache); n_slices >= 1.
 RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride, int dtype,
                                const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
                                void* cache_v, const int* page_table, int max_pages, int page_size, int T, int H,
-                               int Kh, int D, int write_kv, int rot_dim, int interleaved, cudaStream_t stream) {
+                               int Kh, int D, int write_kv, int rot_dim, int interleaved, int in_dtype,
+                               int n_slices, int64_t slice_stride, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(D % 2 == 0 && D > 0, "rb_rotate_append: head_dim %d must be even", D);
   RB_REQUIRE(rot_dim == D, "rb_rotate_append: a rotated prefix of %d of %d is not built", rot_dim, D);
   RB_REQUIRE(H > 0 && Kh >= 0 && page_size > 0, "rb_rotate_append: bad sizes H=%d Kh=%d page=%d", H, Kh, page_size);
+  RB_REQUIRE(n_slices >= 1, "rb_rotate_append: n_slices %d", n_slices);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
   const int threads = 256;
-  if (dtype == RB_F32)
-    rotate_append_kernel<float><<<T, threads, 0, stream>>>((float*)q_out, (const float*)qkv, qkv_stride, inv_freq,
-                                                           tok_pos, tok_slot, c, H, write_kv, rot_dim, interleaved);
-  else if (dtype == RB_BF16)
-    rotate_append_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv,
-                                                                   qkv_stride, inv_freq, tok_pos, tok_slot, c, H,
-                                                                   write_kv, rot_dim, interleaved);
+  if (dtype == RB_F32 && in_dtype == RB_F32)
+    rotate_append_kernel<float, float><<<T, threads, 0, stream>>>((float*)q_out, (const float*)qkv, qkv_stride,
+        n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
+  else if (dtype == RB_BF16 && in_dtype == RB_BF16)
+    rotate_append_kernel<__nv_bfloat16, __nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)q_out,
+        (const __nv_bfloat16*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv,
+        interleaved);
+  else if (dtype == RB_BF16 && in_dtype == RB_F32)
+    rotate_append_kernel<__nv_bfloat16, float><<<T, threads, 0, stream>>>((__nv_bfloat16*)q_out, (const float*)qkv,
+        qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
   else
-    RB_FAIL("rb_rotate_append: unknown dtype %d", dtype);
+    RB_FAIL("rb_rotate_append: unsupported dtypes %d <- %d", dtype, in_dtype);
   RB_CHECK_LAUNCH("rb_rotate_append");
+  return 0;
+}
+
+// x[i] += sum over slices of partials[s][i], in slice order (float32).
+__global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partials, int n_partials,
+                                    int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = x[i];
+    for (int p = 0; p < n_partials; ++p) v += partials[p * n + i];
+    x[i] = v;
+  }
+}
+
+RB_EXPORT int rb_add_partials(float* x, const float* partials, int n_partials, int64_t n, cudaStream_t stream) {
+  if (n == 0 || n_partials == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  add_partials_kernel<<<blocks, 256, 0, stream>>>(x, partials, n_partials, n);
+  RB_CHECK_LAUNCH("rb_add_partials");
   return 0;
 }
 

@@ -249,6 +249,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         uint32_t r[16], u[16];
+        __syncwarp();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
         if (nkb > 0) {
           tmem_ld16(taddr, r);
@@ -259,23 +260,30 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int j = 0; j < 16; ++j) { r[j] = 0u; u[j] = 0u; }
         }
         if (t0 + c >= p.n_tokens) break;
+        // rows of this chunk that exist (none for a lane whose weight row is beyond the matrix);
+        // no lane leaves the loop early: tcgen05.ld is executed by the whole warp
+        const int t_left = n_ok ? p.n_tokens - (t0 + c) : 0;
+        if (EPI == EPI_ADD) {
+          // all loads first, then all stores: the read-modify-write of the 16 rows overlaps
+          float* dst = (float*)p.C + (int64_t)(t0 + c) * p.ldc + n;
+          float old[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int t = t0 + c + j;
-          if (t < p.n_tokens && n_ok) {
+          for (int j = 0; j < 16; ++j) old[j] = j < t_left ? dst[(int64_t)j * p.ldc] : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]);
+        } else if (EPI == EPI_PARTIAL) {
+          float* dst = (float*)p.C + (int64_t)blockIdx.z * p.slice + (int64_t)(t0 + c) * p.ldc + n;
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < t_left) dst[(int64_t)j * p.ldc] = __uint_as_float(r[j]);
+        } else {
+          OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
             float v = __uint_as_float(r[j]);
-            if (EPI == EPI_GATED) {
-              const float up = __uint_as_float(u[j]);
-              v = v / (1.0f + expf(-v)) * up;
-              store_out<OutT>((OutT*)p.C + (int64_t)t * p.ldc + n, v);
-            } else if (EPI == EPI_ADD) {
-              float* dst = (float*)p.C + (int64_t)t * p.ldc + n;
-              *dst += v;
-            } else if (EPI == EPI_PARTIAL) {
-              ((float*)p.C)[(int64_t)blockIdx.z * p.slice + (int64_t)t * p.ldc + n] = v;
-            } else {
-              store_out<OutT>((OutT*)p.C + (int64_t)t * p.ldc + n, v);
-            }
+            if (EPI == EPI_GATED) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
+            if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
           }
         }
       }

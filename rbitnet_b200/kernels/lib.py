@@ -17,12 +17,14 @@ _SIGNATURES = {
     "rb_abi_version": [],
     "rb_embed": [P, P, I, P, I, I, I, P],
     "rb_rmsnorm": [P, I, P, P, P, I, I, I, F, P],
-    "rb_rotate_append": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+    "rb_rotate_append": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, L, P],
+    "rb_add_partials": [P, P, I, L, P],
     "rb_silu_mul": [P, P, I, I, I, P],
     "rb_gather_rows": [P, P, P, I, I, P],
     "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, P],
     "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
-    "rb_sample": [P, P, L, I, I, P, P, P],
+    "rb_sample": [P, P, L, I, I, P, P, P, P],
+    "rb_sample_chunks": [I],
     "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, P],
     "rb_read_error_flag": [P, I],
     "rb_decode_advance": [P, P, P, I, P],

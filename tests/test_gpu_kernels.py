@@ -322,3 +322,56 @@ def test_gather_rows(ops32):
     x = torch.randn(20, 48, device="cuda")
     rows = torch.tensor([19, 0, 7, 7], dtype=torch.int32, device="cuda")
     assert torch.equal(ops32.gather_rows(x, rows), x[rows.long()])
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 4096), (8, 100, 1032), (64, 4096, 1024), (33, 520, 2048)])
+def test_split_product_slices_add_up(ops16, T, N, K):
+    """Few tokens and few weight tiles: the inner dimension is cut into parts.  The slices are
+    folded by the consumer: the next norm (residual case) or the rotation (q, k, v case)."""
+    g = torch.Generator(device="cuda").manual_seed(14)
+    x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    lw = ops16.prepare_linear([w])
+    assert ops16._k_splits(T, N, K) > 1
+    ref = x.double() @ w.double().T
+    y = ops16.linear(x, lw, allow_split=True)
+    from rbitnet_b200.kernels.ops import SplitProduct
+    assert isinstance(y, SplitProduct) and y.slices.shape[0] == ops16._k_splits(T, N, K)
+    assert _rel(y.slices.sum(0), ref) < 2e-5
+    # residual case: the slices wait, and the norm folds them while it reads the row
+    acc = torch.randn(T, N, device="cuda", generator=g)
+    want = acc.double() + ref
+    ops16.linear(x, lw, accumulate_into=acc, deferred_ok=True)
+    assert ops16._pending
+    wn = torch.ones(N, device="cuda")
+    h = ops16.rmsnorm(acc, wn, 1e-5, out_dtype=F32)
+    assert _rel(acc, want) < 2e-5
+    assert _rel(h, want / torch.sqrt((want ** 2).mean(-1, keepdim=True) + 1e-5)) < 2e-5
+    # ... or any other reader settles them first
+    acc2 = torch.randn(T, N, device="cuda", generator=g)
+    want2 = acc2.double() + ref
+    ops16.linear(x, lw, accumulate_into=acc2, deferred_ok=True)
+    rows = torch.arange(T, dtype=torch.int32, device="cuda")
+    assert _rel(ops16.gather_rows(acc2, rows), want2) < 2e-5
+    assert not ops16._pending
+    ops16.check_errors()
+
+
+def test_rotation_reads_split_slices(ops16):
+    from rbitnet_b200.cache import CacheLayerView
+    from rbitnet_b200.kernels.ops import SplitProduct
+    H, Kh, D, page = 4, 2, 32, 64
+    rows = [(0, 3), (1, 70), (0, 4)]
+    g = torch.Generator(device="cuda").manual_seed(15)
+    slices = torch.randn(3, len(rows), (H + 2 * Kh) * D, device="cuda", generator=g)
+    whole = slices.sum(0).to(BF16)
+    inv = (1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(D // 2, dtype=torch.float32) / D)).cuda()
+    outs = []
+    for src in (SplitProduct(slices), whole):
+        k = torch.zeros(4, Kh, page, D, device="cuda", dtype=BF16)
+        v = torch.zeros_like(k)
+        table = torch.tensor([[0, 1], [2, 3]], dtype=torch.int32, device="cuda")
+        view = CacheLayerView(k, v, table, 2, page, Kh, D, True, 0)
+        outs.append((ops16.rotate_append(src, (inv, False, D), _meta(rows), view, H), k, v))
+    for a, b in zip(outs[0], outs[1]):
+        assert _rel(a, b.double()) < 8e-3      # the same up to the one extra rounding of `whole`
