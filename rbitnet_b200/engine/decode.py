@@ -48,12 +48,17 @@ class DecodeGraph:
         """The buffers must hold a valid step (live slots with reserved room) while this runs:
         the step is executed once for real before it is recorded."""
         keep = self.buf.clone()
+        # the trial run below must leave no trace: appending keys and values again is harmless,
+        # but per-sequence state would be advanced twice
+        states = {e: st.clone() for e, st in self.cache.states.items()}
         side = torch.cuda.Stream(device=self.ops.device)
         side.wait_stream(torch.cuda.current_stream(self.ops.device))
         with torch.cuda.stream(side):
             self._body()
         torch.cuda.current_stream(self.ops.device).wait_stream(side)
         self.buf.copy_(keep)
+        for e, st in states.items():
+            self.cache.states[e].copy_(st)
         before = self.ops.lib.launches
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, pool=pool):

@@ -1,0 +1,350 @@
+"""Each part of a layer alone against the plain implementation's function for it, and the
+generality of the way layers are put together: a schedule that names a layer twice and lets a
+run read another run's cache, a window, and a toy mixer with state of its own that is defined
+here, registered, built and stepped without touching the package's files."""
+import json
+import math
+from dataclasses import dataclass
+from typing import ClassVar
+
+import pytest
+import torch
+
+import plain_llama as plain
+from helpers import assert_close, make_model_dir, PlainModel
+from tiny import TINY_A, TINY_B, prompts
+
+pytestmark = pytest.mark.gpu
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _ops(dtype):
+    from rbitnet_b200.kernels.ops import CudaOps
+    return CudaOps(DTYPES[dtype])
+
+
+def _ctx(ops, cache, chunks):
+    """A step context for chunks [(slot, start, n_new)] packed in order."""
+    import numpy as np
+    from rbitnet_b200.engine.step import SeqChunk, StepContext, build_meta
+    seqs, off = [], 0
+    for slot, start, n in chunks:
+        seqs.append(SeqChunk(slot, start, n, off))
+        off += n
+    meta = build_meta(seqs, np.zeros(off, dtype=np.int32), np.zeros(0, dtype=np.int32), ops.device)
+    return StepContext(ops, meta, cache)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,eps", [(48, 1e-5), (272, 1e-6)])
+def test_norm_part(dtype, width, eps):
+    from rbitnet_b200.parts import build_part, PartSpec
+    ops = _ops(dtype)
+    part = build_part("norm", PartSpec("rmsnorm", {"width": width, "eps": eps}))
+    assert part.weight_shapes() == {"weight": ((width,), "norm")}
+    w = 1 + 0.1 * torch.randn(width)
+    part.bind({"weight": w.to(DTYPES[dtype]).cuda()}, ops)
+    x = torch.randn(7, width) * 2
+    got = part.forward(_ctx(ops, None, [(0, 0, 7)]), x.cuda())
+    ref = plain.rmsnorm(x.double(), w.to(DTYPES[dtype]).double(), eps)
+    assert_close(got, ref, dtype, "rmsnorm part")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_feed_forward_part(dtype):
+    from rbitnet_b200.parts import build_part, PartSpec
+    ops = _ops(dtype)
+    E, F, T = 72, 200, 9
+    part = build_part("feed_forward", PartSpec("gated_dense", {"width": E, "inner": F, "activation": "silu"}))
+    dt = DTYPES[dtype]
+    w = {"gate": (torch.randn(F, E) / 6).to(dt), "up": (torch.randn(F, E) / 6).to(dt), "down": (torch.randn(E, F) / 10).to(dt)}
+    part.bind({k: v.cuda() for k, v in w.items()}, ops)
+    h = torch.randn(T, E).to(dt)
+    resid = torch.randn(T, E)
+    x = resid.clone().cuda()
+    part.forward(_ctx(ops, None, [(0, 0, T)]), h.cuda(), accumulate_into=x)
+    ops.settle(x)
+    ref = resid.double() + plain.gated_mlp(h.double(), {k: v.double() for k, v in w.items()})
+    assert_close(x, ref, dtype, "gated feed-forward part")
+    with pytest.raises(ValueError, match="activation"):
+        build_part("feed_forward", PartSpec("gated_dense", {"width": 8, "inner": 8, "activation": "relu"}))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,K,D,pairing,theta,window,scale", [(4, 2, 16, "interleaved", 1e4, None, None),
+                                                             (3, 1, 32, "half", 5e5, 6, 0.3),
+                                                             (6, 3, 48, "half", 1e4, None, None)])
+def test_attention_mixer_part_in_steps(dtype, H, K, D, pairing, theta, window, scale):
+    """The mixer alone over a cache: two sequences, a prompt chunk each, then single tokens."""
+    from rbitnet_b200.parts import build_part, PartSpec
+    from rbitnet_b200.cache import SequenceCache
+    ops = _ops(dtype)
+    dt = DTYPES[dtype]
+    E = H * D
+    params = {"width": E, "n_heads": H, "n_kv_heads": K, "head_dim": D, "window": window, "scale": scale,
+              "position": {"kind": "rotary", "params": {"head_dim": D, "theta": theta, "pairing": pairing}}}
+    part = build_part("mixer", PartSpec("attention", params))
+    w = {"q": (torch.randn(H * D, E) * 3 / math.sqrt(E)).to(dt), "k": (torch.randn(K * D, E) * 3 / math.sqrt(E)).to(dt),
+         "v": (torch.randn(K * D, E) / math.sqrt(E)).to(dt), "o": (torch.randn(E, H * D) / math.sqrt(E)).to(dt)}
+    part.bind({k: v.cuda() for k, v in w.items()}, ops)
+    cache = SequenceCache({0: part.cache_need()}, {}, {}, max_tokens=512, max_seq=256, dtype=dt, device=ops.device)
+    lens = [70, 13]
+    hs = [torch.randn(n, E).to(dt) for n in lens]
+    slots = [cache.alloc() for _ in lens]
+    outs = [[] for _ in lens]
+
+    def run(chunks):
+        for s, _, n in chunks:
+            cache.reserve(s, n)
+        cache.upload_tables()
+        ctx = _ctx(ops, cache, chunks)
+        h = torch.cat([hs[slots.index(s)][st:st + n] for s, st, n in chunks]).cuda()
+        x = torch.zeros(h.shape[0], E, device="cuda")
+        part.forward(ctx, h, 0, accumulate_into=x)
+        ops.settle(x)
+        off = 0
+        for s, _, n in chunks:
+            outs[slots.index(s)].append(x[off:off + n].cpu())
+            off += n
+            cache.advance(s, n)
+
+    run([(slots[0], 0, 66), (slots[1], 0, 9)])
+    for k in range(4):
+        run([(slots[0], 66 + k, 1), (slots[1], 9 + k, 1)])
+    cfg = {"num_attention_heads": H, "num_key_value_heads": K, "head_dim": D, "rope_theta": theta,
+           "rope_pairing": pairing, "sliding_window": window}
+    for i, n in enumerate(lens):
+        if scale is None:
+            ref, _ = plain.attention_mixer(hs[i].double(), {k: v.double() for k, v in w.items()}, cfg, torch.arange(n))
+        else:   # the plain mixer has the default scale; fold the ratio into q
+            w2 = {k: v.double() for k, v in w.items()}
+            w2["q"] = w2["q"] * (scale * math.sqrt(D))
+            ref, _ = plain.attention_mixer(hs[i].double(), w2, cfg, torch.arange(n))
+        assert_close(torch.cat(outs[i]), ref, dtype, f"attention part, sequence {i}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_part(dtype):
+    """One pre-norm block of tiny A alone on one whole sequence."""
+    from rbitnet_b200.config import config_from_dict
+    from rbitnet_b200.config.registry import get_architecture
+    from rbitnet_b200.parts import build_block
+    from rbitnet_b200.cache import SequenceCache
+    from rbitnet_b200.weights import random_tensors
+    from helpers import sharpen
+    ops = _ops(dtype)
+    dt = DTYPES[dtype]
+    cfg = config_from_dict(TINY_A)
+    spec = get_architecture(cfg.architecture).build_spec(cfg)
+    tensors = {k: v.to(dt) for k, v in sharpen(random_tensors(spec, 3), 4.0).items()}
+    blk = build_block(spec.layers[1])
+    for role, part in blk.parts().items():
+        part.bind({k: tensors[spec.layers[1].names[f"{role}.{k}"]].cuda() for k in part.weight_shapes()}, ops)
+    cache = SequenceCache({0: blk.mixer.cache_need()}, {}, {}, max_tokens=128, max_seq=128, dtype=dt, device=ops.device)
+    s = cache.alloc()
+    T = 37
+    cache.reserve(s, T)
+    cache.upload_tables()
+    x0 = torch.randn(T, cfg.hidden_size)
+    x = x0.clone().cuda()
+    blk.run(_ctx(ops, cache, [(s, 0, T)]), x, 0)
+    ops.settle(x)
+    ref, _ = plain.block(x0.double(), plain.layer_weights({k: v for k, v in tensors.items()}, 1, torch.float64),
+                         plain.normalise_config(TINY_A), torch.arange(T))
+    assert_close(x, ref, dtype, "pre-norm block")
+
+
+# --------------------------------------------------------------------------- the order of layers is data
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_with_a_layer_twice_and_a_shared_cache(tmp_path, dtype):
+    """A test architecture made of Llama's parts whose schedule runs layer 0, layer 1, layer 0 again
+    (its own cache), then layer 1 reading the keys and values that the FIRST run of layer 1 wrote."""
+    from rbitnet_b200 import Engine, StepEntry
+    from rbitnet_b200.config import LlamaConfig, register_architecture, unregister_architecture
+    from rbitnet_b200.models.llama import build_llama_spec
+    from rbitnet_b200.parts import ScheduleEntry
+
+    class LoopedConfig(LlamaConfig):
+        architecture: ClassVar[str] = "LoopedTestLM"
+
+    def build(cfg):
+        spec = build_llama_spec(cfg)
+        spec.schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, reads_cache_of=1)]
+        return spec
+
+    register_architecture("LoopedTestLM", LoopedConfig, build, replace=True)
+    try:
+        cfgd = dict(TINY_A, architectures=["LoopedTestLM"])
+        folder = make_model_dir(tmp_path / "m", cfgd, 4, store=dtype)
+        pc, pt = plain.load_folder(folder)
+        eng = Engine.load_path(folder, dtype=dtype, max_tokens=1024)
+        assert len(eng.cache.groups) == 1 and len(eng.cache.groups[0].entries) == 3     # three caches, one reader
+        sched = [(0, None), (1, None), (0, None), (1, 1)]
+        ps = prompts([40, 7, 100], cfgd["vocab_size"], 30)
+        slots = [eng.new_sequence() for _ in ps]
+        lens = [25, 3, 90]
+        got = [[] for _ in ps]
+        out = eng.step([StepEntry(s, p[:n], list(range(n))) for s, p, n in zip(slots, ps, lens)])
+        off = 0
+        for i, n in enumerate(lens):
+            got[i].append(out[off:off + n])
+            off += n
+        for k in range(4):
+            out = eng.step([StepEntry(s, [p[n + k]], [0]) for s, p, n in zip(slots, ps, lens)])
+            for i in range(len(ps)):
+                got[i].append(out[i:i + 1])
+        for i, (p, n) in enumerate(zip(ps, lens)):
+            ref = plain.forward(pc, pt, p[:n + 4], torch.float64, schedule=sched)
+            assert_close(torch.cat(got[i]), ref, dtype, f"looped schedule, request {i}")
+        plain_default = plain.forward(pc, pt, ps[0][:29], torch.float64)
+        assert float((plain_default - plain.forward(pc, pt, ps[0][:29], torch.float64, schedule=sched)).abs().max()) > 1e-3
+    finally:
+        unregister_architecture("LoopedTestLM")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,window", [("A", 5), ("B", 64), ("B", 70)])
+def test_sliding_window_through_the_engine(tmp_path, dtype, name, window):
+    """config.json's sliding_window reaches the kernels: whole prompts, then tokens one by one across
+    the window's edge (and across a page's edge for 64 and 70)."""
+    from rbitnet_b200 import Engine, StepEntry
+    cfgd = dict({"A": TINY_A, "B": TINY_B}[name], sliding_window=window)
+    folder = make_model_dir(tmp_path / "m", cfgd, 5, store=dtype)
+    ref = PlainModel(folder)
+    eng = Engine.load_path(folder, dtype=dtype, max_tokens=1024)
+    n = min(cfgd["max_position_embeddings"], 2 * window + 30)
+    p = prompts([n], cfgd["vocab_size"], 31)[0]
+    full = plain.forward(dict(cfgd, sliding_window=None), ref.tensors, p, torch.float64)
+    assert float((full[-1] - ref.logits(p)[-1]).abs().max()) > 1e-4          # the window matters here
+    s = eng.new_sequence()
+    k = window + 3
+    outs = [eng.step([StepEntry(s, p[:k], list(range(k)))])]
+    outs += [eng.step([StepEntry(s, [t], [0])]) for t in p[k:]]
+    eng.end_sequence(s)
+    assert_close(torch.cat(outs), ref.logits(p), dtype, "windowed attention")
+
+
+# --------------------------------------------------------------------------- a toy mixer with state of its own
+def _toy_plain(cfg, tensors, tokens):
+    """Plain whole-sequence forward of the toy model below: layer 0 mixes with a decaying running
+    sum s_t = decay * s_{t-1} + h_t, y_t = W s_t; layer 1 is ordinary attention."""
+    c = plain.normalise_config(cfg)
+    t64 = {k: v.double() for k, v in tensors.items()}
+    ids = torch.as_tensor(tokens, dtype=torch.long)
+    x = t64["model.embed_tokens.weight"][ids]
+    pos = torch.arange(len(tokens))
+    h = plain.rmsnorm(x, t64["model.layers.0.input_layernorm.weight"], c["rms_norm_eps"])
+    s = torch.zeros(c["hidden_size"], dtype=torch.float64)
+    ys = []
+    for t in range(len(tokens)):
+        s = cfg["decay"] * s + h[t]
+        ys.append(t64["model.layers.0.mixer.weight"] @ s)
+    x = x + torch.stack(ys)
+    lw0 = {k: t64[f"model.layers.0.mlp.{k}_proj.weight"] for k in ("gate", "up", "down")}
+    x = x + plain.gated_mlp(plain.rmsnorm(x, t64["model.layers.0.post_attention_layernorm.weight"], c["rms_norm_eps"]), lw0)
+    x, _ = plain.block(x, plain.layer_weights(t64, 1, torch.float64), c, pos)
+    xn = plain.rmsnorm(x, t64["model.norm.weight"], c["rms_norm_eps"])
+    return xn @ t64["lm_head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path, dtype):
+    from rbitnet_b200 import Engine, StepEntry
+    from rbitnet_b200.config import LlamaConfig, register_architecture, unregister_architecture
+    from rbitnet_b200.models.llama import build_llama_spec
+    from rbitnet_b200.parts import Mixer, StateNeed, PartSpec, register_part, unregister_part
+    from rbitnet_b200.weights import random_tensors, write_safetensors
+
+    class DecayMixer(Mixer):
+        """y_t = W s_t with s_t = decay * s_{t-1} + h_t kept per sequence in the state area.
+        Written with torch on the device: a test part, not a kernel."""
+
+        def __init__(self, width, decay):
+            self.width, self.decay = width, decay
+
+        def weight_shapes(self):
+            return {"weight": ((self.width, self.width), "matrix")}
+
+        def state_need(self):
+            return StateNeed((self.width,), torch.float32)
+
+        def bind(self, weights, ops):
+            self.w = weights["weight"].to(torch.float32)
+
+        def forward(self, ctx, h, entry, accumulate_into):
+            state = ctx.state_view(entry)                      # [n_slots, width]
+            hf = h.to(torch.float32)
+            if ctx.meta.single_token:                          # device-only: works inside a captured step
+                slots = ctx.meta.tok_slot.long()
+                s = self.decay * state[slots] + hf
+                state[slots] = s
+                accumulate_into += s @ self.w.T
+                return
+            for c in ctx.meta.seqs:
+                s = state[c.slot].clone()
+                rows = []
+                for t in range(c.n_new):
+                    s = self.decay * s + hf[c.offset + t]
+                    rows.append(s)
+                state[c.slot] = s
+                accumulate_into[c.offset:c.offset + c.n_new] += torch.stack(rows) @ self.w.T
+
+    @dataclass
+    class ToyConfig(LlamaConfig):
+        architecture: ClassVar[str] = "ToyDecayLM"
+        decay: float = 0.5
+
+    def build(cfg):
+        spec = build_llama_spec(cfg)
+        spec.layers[0].mixer = PartSpec("toy_decay", {"width": cfg.hidden_size, "decay": cfg.decay})
+        names = {k: v for k, v in spec.layers[0].names.items() if not k.startswith("mixer.")}
+        names["mixer.weight"] = "model.layers.0.mixer.weight"
+        spec.layers[0].names = names
+        return spec
+
+    register_part("mixer", "toy_decay", DecayMixer, replace=True)
+    register_architecture("ToyDecayLM", ToyConfig, build, replace=True)
+    try:
+        cfgd = dict(TINY_B, architectures=["ToyDecayLM"], num_hidden_layers=2, decay=0.8)
+        folder = tmp_path / "toy"
+        folder.mkdir()
+        cfg = ToyConfig.from_dict(cfgd)
+        tensors = random_tensors(build(cfg), 6)
+        tensors["model.layers.0.mixer.weight"] *= 3
+        tensors = {k: v.to(DTYPES[dtype]) for k, v in tensors.items()}
+        (folder / "config.json").write_text(json.dumps(cfgd))
+        write_safetensors(folder / "model.safetensors", tensors)
+        eng = Engine.load_path(folder, dtype=dtype, max_tokens=1024)
+        assert list(eng.cache.states) == [0] and eng.cache.states[0].shape[1:] == (cfg.hidden_size,)
+        assert len(eng.cache.groups) == 1 and eng.cache.groups[0].entries == [1]      # only layer 1 caches keys
+        pc, pt = plain.load_folder(folder)
+        for round_ in range(2):                                 # the second round uses the slots again
+            ps = prompts([30, 5, 12], cfgd["vocab_size"], 40 + round_)
+            lens = [20, 1, 6]
+            slots = [eng.new_sequence() for _ in ps]
+            got = [[] for _ in ps]
+            out = eng.step([StepEntry(s, p[:n], list(range(n))) for s, p, n in zip(slots, ps, lens)])
+            off = 0
+            for i, n in enumerate(lens):
+                got[i].append(out[off:off + n])
+                off += n
+            for k in range(4):
+                out = eng.step([StepEntry(s, [p[n + k]], [0]) for s, p, n in zip(slots, ps, lens)])
+                for i in range(len(ps)):
+                    got[i].append(out[i:i + 1])
+            for i, (p, n) in enumerate(zip(ps, lens)):
+                assert_close(torch.cat(got[i]), _toy_plain(pc, pt, p[:n + 4]), dtype, f"toy model round {round_} request {i}")
+            for s in slots:
+                eng.end_sequence(s)
+        # generation (captured decode steps) runs the toy mixer too and keeps its state right
+        res = eng.generate([ps[0][:9], ps[2][:4]], max_tokens=5, temperature=0.0)
+        for p, r in zip([ps[0][:9], ps[2][:4]], res):
+            seq = list(p)
+            for t in r.tokens:
+                row = _toy_plain(pc, pt, seq)[-1]
+                tol = 2 * ((1e-5 + 1e-4 * float(row.abs().max())) if dtype == "float32" else 2e-2 * float(row.abs().max()))
+                assert float(row[t]) >= float(row.max()) - tol
+                seq.append(t)
+    finally:
+        unregister_architecture("ToyDecayLM")
+        unregister_part("mixer", "toy_decay")
