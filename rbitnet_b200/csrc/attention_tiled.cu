@@ -70,16 +70,16 @@ struct AttnParams {
 
 // Row stride of the shared tiles: D values plus 8 of padding, so that the eight 16-byte rows an
 // ldmatrix reads fall into different banks for every D that is a multiple of 16.
-template <int D> struct Smem {
+template <int D, bool DECODE> struct Smem {
   static constexpr int LD = D + 8;
-  static constexpr int Q_ELEMS = ROWS * LD;
+  static constexpr int Q_ELEMS = (DECODE ? 16 : ROWS) * LD;     // decode: one token's heads only
   static constexpr int KV_ELEMS = TILE_KEYS * LD;
   static constexpr size_t BYTES = (size_t)(Q_ELEMS + 4 * KV_ELEMS) * 2;
 };
 
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
-  using S = Smem<D>;
+  using S = Smem<D, DECODE>;
   constexpr int LD = S::LD;
   constexpr int NT = DECODE ? 2 : 8;          // 8-key column tiles of S per warp
   constexpr int DT = D / 8;                   // 8-wide column tiles of O
@@ -337,10 +337,10 @@ __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float
 template <int D, bool DECODE>
 int launch_one(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   auto kernel = attn_tiled_kernel<D, DECODE>;
-  size_t smem = Smem<D>::BYTES;
+  size_t smem = Smem<D, DECODE>::BYTES;
   if (DECODE) {
     const size_t merge = (size_t)(WARPS * 16 * D + 2 * WARPS * 16) * 4;
-    const size_t kv = (size_t)4 * Smem<D>::KV_ELEMS * 2;
+    const size_t kv = (size_t)4 * Smem<D, DECODE>::KV_ELEMS * 2;
     if (merge > kv) smem += merge - kv;
   }
   static bool configured = false;

@@ -55,28 +55,78 @@ RB_EXPORT int rb_embed(float* out, const void* table, int table_dtype, const int
 // in the sum of `n_partials` float32 slices [n_partials][T][E] (the pieces of a
 // matrix product that was split along its inner dimension) and the updated x is
 // written back, so the residual add and the norm read the row once.
-template <typename TO>
+template <typename TO> __device__ __forceinline__ void store4(TO* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<uint32_t*>(&lo);
+  v.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+// VEC: the width is a multiple of 4 and rows are read and written four values at a time.
+template <typename TO, bool VEC>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const float* __restrict__ w,
                                const float* __restrict__ partials, int n_partials, int64_t partial_stride,
                                int E, float eps) {
   __shared__ float scratch[33];
-  extern __shared__ float row[];  // E floats
+  extern __shared__ __align__(16) float row[];  // E floats
   const int t = blockIdx.x;
   float* xr = x + (int64_t)t * E;
   float ss = 0.f;
-  for (int j = threadIdx.x; j < E; j += blockDim.x) {
-    float v = xr[j];
-    if (partials) {
-      for (int p = 0; p < n_partials; ++p) v += partials[p * partial_stride + (int64_t)t * E + j];
-      xr[j] = v;
+  if (VEC) {
+    for (int j = threadIdx.x * 4; j < E; j += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + j);
+      if (n_partials > 0) {
+        for (int p = 0; p < n_partials; ++p) {
+          const float4 q = *reinterpret_cast<const float4*>(partials + p * partial_stride + (int64_t)t * E + j);
+          v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+        }
+        *reinterpret_cast<float4*>(xr + j) = v;
+      }
+      *reinterpret_cast<float4*>(row + j) = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    row[j] = v;
-    ss += v * v;
+  } else {
+    for (int j = threadIdx.x; j < E; j += blockDim.x) {
+      float v = xr[j];
+      if (n_partials > 0) {
+        for (int p = 0; p < n_partials; ++p) v += partials[p * partial_stride + (int64_t)t * E + j];
+        xr[j] = v;
+      }
+      row[j] = v;
+      ss += v * v;
+    }
   }
   ss = rb_block_sum(ss, scratch);
   const float r = 1.0f / sqrtf(ss / (float)E + eps);
   TO* o = out + (int64_t)t * E;
-  for (int j = threadIdx.x; j < E; j += blockDim.x) o[j] = rb_from_float<TO>(row[j] * w[j] * r);
+  if (VEC) {
+    for (int j = threadIdx.x * 4; j < E; j += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + j);
+      const float4 g = *reinterpret_cast<const float4*>(w + j);
+      store4<TO>(o + j, v.x * g.x * r, v.y * g.y * r, v.z * g.z * r, v.w * g.w * r);
+    }
+  } else {
+    for (int j = threadIdx.x; j < E; j += blockDim.x) o[j] = rb_from_float<TO>(row[j] * w[j] * r);
+  }
+}
+
+template <typename TO, bool VEC>
+static int launch_rmsnorm(TO* out, float* x, const float* w, const float* partials, int n_partials, int T, int E,
+                          float eps, cudaStream_t stream) {
+  const int per = VEC ? 4 : 1;
+  int threads = 128;
+  while (threads < 1024 && threads * per * 2 <= E) threads *= 2;     // about two loads per thread
+  const size_t smem = (size_t)E * sizeof(float);
+  if (smem > 48 * 1024)
+    RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  rmsnorm_kernel<TO, VEC><<<T, threads, smem, stream>>>(out, x, w, partials, n_partials, (int64_t)T * E, E, eps);
+  RB_CHECK_LAUNCH("rb_rmsnorm");
+  return 0;
 }
 
 RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, const float* partials,
@@ -85,23 +135,16 @@ RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, con
   RB_REQUIRE(T > 0 && E > 0, "rb_rmsnorm: bad sizes T=%d E=%d", T, E);
   RB_REQUIRE((size_t)E * 4 <= 200 * 1024, "rb_rmsnorm: width %d exceeds the %d floats one block can hold",
              E, 200 * 1024 / 4);
-  const int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
-  const size_t smem = (size_t)E * sizeof(float);
-  const int64_t pstride = (int64_t)T * E;
-  if (out_dtype == RB_F32) {
-    if (smem > 48 * 1024)
-      RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    rmsnorm_kernel<float><<<T, threads, smem, stream>>>((float*)out, x, w, partials, n_partials, pstride, E, eps);
-  } else if (out_dtype == RB_BF16) {
-    if (smem > 48 * 1024)
-      RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    rmsnorm_kernel<__nv_bfloat16><<<T, threads, smem, stream>>>((__nv_bfloat16*)out, x, w, partials, n_partials,
-                                                               pstride, E, eps);
-  } else {
-    RB_FAIL("rb_rmsnorm: unknown dtype %d", out_dtype);
-  }
-  RB_CHECK_LAUNCH("rb_rmsnorm");
-  return 0;
+  if (partials == nullptr) n_partials = 0;
+  const bool vec = E % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                   ((uintptr_t)out % 16 == 0) && ((uintptr_t)partials % 16 == 0);
+  if (out_dtype == RB_F32)
+    return vec ? launch_rmsnorm<float, true>((float*)out, x, w, partials, n_partials, T, E, eps, stream)
+               : launch_rmsnorm<float, false>((float*)out, x, w, partials, n_partials, T, E, eps, stream);
+  if (out_dtype == RB_BF16)
+    return vec ? launch_rmsnorm<__nv_bfloat16, true>((__nv_bfloat16*)out, x, w, partials, n_partials, T, E, eps, stream)
+               : launch_rmsnorm<__nv_bfloat16, false>((__nv_bfloat16*)out, x, w, partials, n_partials, T, E, eps, stream);
+  RB_FAIL("rb_rmsnorm: unknown dtype %d", out_dtype);
 }
 
 // ---------------------------------------------------------------- rotation + cache append
@@ -121,7 +164,7 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
                                      int n_slices, int64_t slice_stride,
                                      const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
-                                     int interleaved) {
+                                     int interleaved, int heads_per_block) {
   const int t = blockIdx.x;
   const int D = cache.head_dim, Kh = cache.n_kv_heads;
   const int pos = tok_pos[t];
@@ -134,14 +177,22 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
   };
   const int half = D / 2;
   const int n_rot_heads = H + (write_kv ? Kh : 0);
+  const int n_heads = n_rot_heads + (write_kv ? Kh : 0);        // rotated heads, then the v heads
+  const int h0 = blockIdx.y * heads_per_block, h1 = min(n_heads, h0 + heads_per_block);
   T* kdst = (T*)cache.k;
   T* vdst = (T*)cache.v;
-  // q and k heads: one thread per pair
-  for (int idx = threadIdx.x; idx < n_rot_heads * half; idx += blockDim.x) {
-    const int head = idx / half, i = idx % half;
+  // one thread per pair of values: a rotated pair of a q or k head, or two neighbours of a v head
+  for (int idx = threadIdx.x; idx < (h1 - h0) * half; idx += blockDim.x) {
+    const int head = h0 + idx / half, i = idx % half;
+    const int64_t src = (int64_t)head * D;  // q heads, k heads, v heads are contiguous in a row
+    if (head >= n_rot_heads) {
+      T* dst = vdst + rb_page_offset(cache, slot, pos, head - n_rot_heads);
+      dst[2 * i] = rb_from_float<T>(value(src + 2 * i));
+      dst[2 * i + 1] = rb_from_float<T>(value(src + 2 * i + 1));
+      continue;
+    }
     int a, b;
     if (interleaved) { a = 2 * i; b = 2 * i + 1; } else { a = i; b = i + half; }
-    const int64_t src = (int64_t)head * D;  // q heads, then k heads, are contiguous
     const float x0 = value(src + a);
     const float x1 = value(src + b);
     float sn, cs;
@@ -151,13 +202,6 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
     T* dst = head < H ? q_out + ((int64_t)t * H + head) * D : kdst + rb_page_offset(cache, slot, pos, head - H);
     dst[a] = rb_from_float<T>(y0);
     dst[b] = rb_from_float<T>(y1);
-  }
-  if (write_kv) {
-    const int64_t vsrc = (int64_t)(H + Kh) * D;
-    for (int idx = threadIdx.x; idx < Kh * D; idx += blockDim.x) {
-      const int kvh = idx / D, d = idx % D;
-      vdst[rb_page_offset(cache, slot, pos, kvh) + d] = rb_from_float<T>(value(vsrc + idx));
-    }
   }
 }
 
@@ -174,16 +218,22 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   RB_REQUIRE(n_slices >= 1, "rb_rotate_append: n_slices %d", n_slices);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
   const int threads = 256;
+  // few tokens: spread a token's heads over several blocks so that enough blocks run
+  const int n_heads = H + (write_kv ? 2 * Kh : 0);
+  int by = T >= 128 ? 1 : (128 + T - 1) / T;
+  if (by > n_heads) by = n_heads;
+  const int hpb = (n_heads + by - 1) / by;
+  const dim3 grid(T, (n_heads + hpb - 1) / hpb);
   if (dtype == RB_F32 && in_dtype == RB_F32)
-    rotate_append_kernel<float, float><<<T, threads, 0, stream>>>((float*)q_out, (const float*)qkv, qkv_stride,
-        n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
+    rotate_append_kernel<float, float><<<grid, threads, 0, stream>>>((float*)q_out, (const float*)qkv, qkv_stride,
+        n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else if (dtype == RB_BF16 && in_dtype == RB_BF16)
-    rotate_append_kernel<__nv_bfloat16, __nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)q_out,
+    rotate_append_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)q_out,
         (const __nv_bfloat16*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv,
-        interleaved);
+        interleaved, hpb);
   else if (dtype == RB_BF16 && in_dtype == RB_F32)
-    rotate_append_kernel<__nv_bfloat16, float><<<T, threads, 0, stream>>>((__nv_bfloat16*)q_out, (const float*)qkv,
-        qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
+    rotate_append_kernel<__nv_bfloat16, float><<<grid, threads, 0, stream>>>((__nv_bfloat16*)q_out, (const float*)qkv,
+        qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else
     RB_FAIL("rb_rotate_append: unsupported dtypes %d <- %d", dtype, in_dtype);
   RB_CHECK_LAUNCH("rb_rotate_append");

@@ -123,6 +123,12 @@ def library_path(verbose: bool = True, ptxas_info: bool = False) -> Path:
         tmp = out_dir / f".{name}.{os.getpid()}.tmp"
         _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *map(str, objs)], "link")
         os.replace(tmp, out_dir / name)
+        for old in out_dir.glob("librbitnet_b200_*.so"):      # builds of earlier sources
+            if old.name != name:
+                try:
+                    old.unlink()
+                except OSError:
+                    pass
     finally:
         done.set()
         shutil.rmtree(work, ignore_errors=True)

@@ -281,9 +281,9 @@ class CudaOps:
 
     @staticmethod
     def _decode_splits(batch: int, n_kv_heads: int, max_context: int) -> int:
-        """Parts a decode's keys are cut into so that about two CTAs per SM have work."""
+        """Parts a decode's keys are cut into so that about three CTAs per SM have work."""
         tiles = max(1, -(-max_context // 64))
-        return max(1, min(32, tiles, -(-296 // (batch * n_kv_heads))))
+        return max(1, min(32, tiles, -(-444 // (batch * n_kv_heads))))
 
     def _prefill_tiles(self, meta, tokens_per_tile: int):
         """Tiles of at most ``tokens_per_tile`` consecutive tokens of one sequence (device int32 arrays);
