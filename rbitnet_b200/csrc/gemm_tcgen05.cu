@@ -145,8 +145,19 @@ struct GemmParams {
   int K;
   int up_row0;        // EPI_GATED: first row of the up matrix inside W
   int kb_per_split;   // 64-wide k blocks per split
+  int n_t_tiles;      // token tiles
+  int splits;         // parts of K
+  int n_items;        // weight tiles * token tiles * splits
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// A CTA takes work items blockIdx.x, blockIdx.x + gridDim.x, ...; item = ((weight tile * token
+// tiles) + token tile) * splits + split, so CTAs that run together share tiles of W and X in L2.
+// When two accumulators fit in tensor memory they alternate, and the epilogue of one item runs
+// while the tensor cores work on the next.
 template <int BN, int STAGES, int EPI, typename OutT>
 __global__ void __launch_bounds__(192, 1)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
@@ -154,31 +165,32 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   constexpr int X_TILE_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = W_TILE_BYTES * (GATED ? 2 : 1) + X_TILE_BYTES;
   constexpr int ACC_COLS = BN * (GATED ? 2 : 1);
-  constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+  constexpr int NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;
+  constexpr int WANT_COLS = NBUF * ACC_COLS;
+  constexpr int TMEM_COLS = WANT_COLS <= 32 ? 32 : (WANT_COLS <= 64 ? 64 : (WANT_COLS <= 128 ? 128 : (WANT_COLS <= 256 ? 256 : 512)));
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
-  static_assert(ACC_COLS <= 512, "tensor memory has 512 columns");
+  static_assert(WANT_COLS <= 512, "tensor memory has 512 columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES];
   __shared__ uint64_t empty_bar[STAGES];
-  __shared__ uint64_t accum_bar;
+  __shared__ uint64_t accum_full[NBUF];
+  __shared__ uint64_t accum_empty[NBUF];
   __shared__ uint32_t tmem_holder;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM;          // first weight row of this CTA
-  const int t0 = blockIdx.y * BN;          // first token of this CTA
   const int nkb_total = (p.K + BK - 1) / BK;
-  const int kb_begin = blockIdx.z * p.kb_per_split;
-  const int kb_end = min(nkb_total, kb_begin + p.kb_per_split);
-  const int nkb = max(0, kb_end - kb_begin);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&accum_bar, 1);
+    for (int b = 0; b < NBUF; ++b) {
+      mbar_init(&accum_full[b], 1);
+      mbar_init(&accum_empty[b], 4);     // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -193,64 +205,97 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_holder;
 
+  // what an item covers
+  auto item_of = [&](int item, int& n0, int& t0, int& kb_begin, int& nkb, int& split) {
+    split = item % p.splits;
+    const int tile = item / p.splits;
+    n0 = (tile / p.n_t_tiles) * BM;
+    t0 = (tile % p.n_t_tiles) * BN;
+    kb_begin = split * p.kb_per_split;
+    nkb = max(0, min(nkb_total, kb_begin + p.kb_per_split) - kb_begin);
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % STAGES;
-        const uint32_t phase = (i / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[s], phase ^ 1, 1)) break;
-        uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        const int k = (kb_begin + i) * BK;
-        tma_load_2d(stage, &tmW, k, n0, &full_bar[s]);
-        if (GATED) tma_load_2d(stage + W_TILE_BYTES, &tmW, k, p.up_row0 + n0, &full_bar[s]);
-        tma_load_2d(stage + W_TILE_BYTES * (GATED ? 2 : 1), &tmX, k, t0, &full_bar[s]);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+        int n0, t0, kb_begin, nkb, split;
+        item_of(item, n0, t0, kb_begin, nkb, split);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          ok = mbar_wait(&empty_bar[s], phase ^ 1, 1);
+          if (!ok) break;
+          uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          const int k = (kb_begin + i) * BK;
+          tma_load_2d(stage, &tmW, k, n0, &full_bar[s]);
+          if (GATED) tma_load_2d(stage + W_TILE_BYTES, &tmW, k, p.up_row0 + n0, &full_bar[s]);
+          tma_load_2d(stage + W_TILE_BYTES * (GATED ? 2 : 1), &tmX, k, t0, &full_bar[s]);
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BN);
+      uint32_t it = 0, li = 0;
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % STAGES;
-        const uint32_t phase = (i / STAGES) & 1;
-        ok = mbar_wait(&full_bar[s], phase, 2);
+      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++li) {
+        int n0, t0, kb_begin, nkb, split;
+        item_of(item, n0, t0, kb_begin, nkb, split);
+        const int b = li % NBUF;
+        ok = mbar_wait(&accum_empty[b], ((li / NBUF) & 1) ^ 1, 4);    // the epilogue has drained this accumulator
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        const uint64_t dw = smem_desc_sw128(stage);
-        const uint64_t dx = smem_desc_sw128(stage + W_TILE_BYTES * (GATED ? 2 : 1));
+        const uint32_t acc_addr = tmem_base + (uint32_t)(b * ACC_COLS);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t phase = (it / STAGES) & 1;
+          ok = mbar_wait(&full_bar[s], phase, 2);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t dw = smem_desc_sw128(stage);
+          const uint64_t dx = smem_desc_sw128(stage + W_TILE_BYTES * (GATED ? 2 : 1));
 #pragma unroll
-        for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
-          const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
-          const uint64_t koff = (uint64_t)(k4 * UMMA_K * 2 >> 4);
-          umma_bf16(tmem_base, dw + koff, dx + koff, idesc, acc);
-          if (GATED) {
-            const uint64_t du = smem_desc_sw128(stage + W_TILE_BYTES);
-            umma_bf16(tmem_base + BN, du + koff, dx + koff, idesc, acc);
+          for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
+            const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
+            const uint64_t koff = (uint64_t)(k4 * UMMA_K * 2 >> 4);
+            umma_bf16(acc_addr, dw + koff, dx + koff, idesc, acc);
+            if (GATED) {
+              const uint64_t du = smem_desc_sw128(stage + W_TILE_BYTES);
+              umma_bf16(acc_addr + BN, du + koff, dx + koff, idesc, acc);
+            }
           }
+          tcgen05_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
         }
-        tcgen05_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
+        tcgen05_commit(&accum_full[b]);    // this item's accumulator is complete
       }
-      tcgen05_commit(&accum_bar);        // accumulators complete (or nothing was issued)
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;        // tensor-memory lanes 32*quarter .. +31 belong to this warp
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait(&accum_bar, 0, 3);
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    tcgen05_fence_after();
-    const int n = n0 + quarter * 32 + lane;           // output column = weight row
-    const bool n_ok = n < p.n_out;
-    if (ok) {
+    uint32_t li = 0;
+    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++li) {
+      int n0, t0, kb_begin, nkb, split;
+      item_of(item, n0, t0, kb_begin, nkb, split);
+      const int b = li % NBUF;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(&accum_full[b], (li / NBUF) & 1, 3);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int n = n0 + quarter * 32 + lane;           // output column = weight row
+      const bool n_ok = n < p.n_out;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
+        if (t0 + c >= p.n_tokens) break;
         uint32_t r[16], u[16];
         __syncwarp();
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * ACC_COLS + c);
         if (nkb > 0) {
           tmem_ld16(taddr, r);
           if (GATED) tmem_ld16(taddr + BN, u);
@@ -259,7 +304,6 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j) { r[j] = 0u; u[j] = 0u; }
         }
-        if (t0 + c >= p.n_tokens) break;
         // rows of this chunk that exist (none for a lane whose weight row is beyond the matrix);
         // no lane leaves the loop early: tcgen05.ld is executed by the whole warp
         const int t_left = n_ok ? p.n_tokens - (t0 + c) : 0;
@@ -273,7 +317,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int j = 0; j < 16; ++j)
             if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]);
         } else if (EPI == EPI_PARTIAL) {
-          float* dst = (float*)p.C + (int64_t)blockIdx.z * p.slice + (int64_t)(t0 + c) * p.ldc + n;
+          float* dst = (float*)p.C + (int64_t)split * p.slice + (int64_t)(t0 + c) * p.ldc + n;
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (j < t_left) dst[(int64_t)j * p.ldc] = __uint_as_float(r[j]);
@@ -287,6 +331,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
         }
       }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&accum_empty[b]);
     }
   }
   tcgen05_fence_before();
@@ -362,9 +410,18 @@ int get_map(CUtensorMap* out, const void* ptr, int rows, int cols, int64_t ld, i
   return 0;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES, int EPI, typename OutT>
-int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int n_w_tiles, int n_t_tiles,
-           int splits, cudaStream_t stream) {
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   constexpr int stage_bytes = W_TILE_BYTES * (EPI == EPI_GATED ? 2 : 1) + BN * BK * 2;
   constexpr int smem = STAGES * stage_bytes + 1024;
   static_assert(smem <= 227 * 1024, "shared memory");
@@ -374,22 +431,21 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, in
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  dim3 grid(n_w_tiles, n_t_tiles, splits);
+  const int grid = p.n_items < sm_count() ? p.n_items : sm_count();     // one CTA per SM, items in turn
   kernel<<<grid, 192, smem, stream>>>(tw, tx, p);
   RB_CHECK_LAUNCH("rb_gemm_tc");
   return 0;
 }
 
 template <int EPI, typename OutT>
-int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int n_w_tiles,
-             int n_t_tiles, int splits, cudaStream_t stream) {
+int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   constexpr bool G = EPI == EPI_GATED;
   switch (bn) {
-    case 16: return launch<16, G ? 5 : 10, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-    case 32: return launch<32, G ? 5 : 10, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-    case 64: return launch<64, G ? 5 : 8, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-    case 128: return launch<128, G ? 4 : 6, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-    case 256: return launch<256, G ? 3 : 4, EPI, OutT>(tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+    case 16: return launch<16, G ? 5 : 10, EPI, OutT>(tw, tx, p, stream);
+    case 32: return launch<32, G ? 5 : 10, EPI, OutT>(tw, tx, p, stream);
+    case 64: return launch<64, G ? 5 : 8, EPI, OutT>(tw, tx, p, stream);
+    case 128: return launch<128, G ? 4 : 6, EPI, OutT>(tw, tx, p, stream);
+    case 256: return launch<256, G ? 3 : 4, EPI, OutT>(tw, tx, p, stream);
   }
   RB_FAIL("rb_gemm_tc: no kernel for a token tile of %d", bn);
 }
@@ -427,6 +483,9 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
   int bn = token_tile;
   if (bn == 0) bn = n_tokens <= 16 ? 16 : n_tokens <= 32 ? 32 : n_tokens <= 64 ? 64 : n_tokens <= 128 ? 128 : 256;
+  // the gated product holds two accumulators per item: with a 128-token tile two items fit in
+  // tensor memory and the epilogue of one overlaps the products of the next
+  if (token_tile == 0 && epilogue == EPI_GATED && bn == 256) bn = 128;
   CUtensorMap tw, tx;
   if (get_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
   if (get_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
@@ -435,16 +494,13 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   p.up_row0 = up_row0; p.kb_per_split = (nkb + splits - 1) / splits;
   RB_REQUIRE((int64_t)(splits - 1) * p.kb_per_split < nkb, "rb_gemm_tc: a split of K would be empty");
   const int n_w_tiles = (n_out + BM - 1) / BM, n_t_tiles = (n_tokens + bn - 1) / bn;
-  RB_REQUIRE(n_t_tiles <= 65535 && splits <= 65535, "rb_gemm_tc: grid too large");
-  if (epilogue == EPI_STORE && c_dtype == RB_BF16)
-    return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-  if (epilogue == EPI_STORE && c_dtype == RB_F32)
-    return dispatch<EPI_STORE, float>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-  if (epilogue == EPI_ADD && c_dtype == RB_F32)
-    return dispatch<EPI_ADD, float>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-  if (epilogue == EPI_PARTIAL && c_dtype == RB_F32)
-    return dispatch<EPI_PARTIAL, float>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
-  if (epilogue == EPI_GATED && c_dtype == RB_BF16)
-    return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, p, n_w_tiles, n_t_tiles, splits, stream);
+  const long long items = (long long)n_w_tiles * n_t_tiles * splits;
+  RB_REQUIRE(items < (1ll << 30), "rb_gemm_tc: too many tiles");
+  p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
+  if (epilogue == EPI_STORE && c_dtype == RB_BF16) return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, stream);
+  if (epilogue == EPI_STORE && c_dtype == RB_F32) return dispatch<EPI_STORE, float>(bn, tw, tx, p, stream);
+  if (epilogue == EPI_ADD && c_dtype == RB_F32) return dispatch<EPI_ADD, float>(bn, tw, tx, p, stream);
+  if (epilogue == EPI_PARTIAL && c_dtype == RB_F32) return dispatch<EPI_PARTIAL, float>(bn, tw, tx, p, stream);
+  if (epilogue == EPI_GATED && c_dtype == RB_BF16) return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, p, stream);
   RB_FAIL("rb_gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, c_dtype);
 }
