@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(128) attn_simple_kernel(T* __restrict__ out, c
                                                          RbPagedLayer cache, const int* __restrict__ tok_pos,
                                                          const int* __restrict__ tok_slot, int n_tokens, int H,
                                                          float scale, int window) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * 4 + warp;
   if (w >= (int64_t)n_tokens * H) return;
@@ -74,7 +76,7 @@ int launch(T* out, const T* q, RbPagedLayer c, const int* tok_pos, const int* to
   const int blocks = (int)((warps + 3) / 4);
   const int epl = (c.head_dim + 31) / 32;
 #define CASE(E) \
-  case E: attn_simple_kernel<T, E><<<blocks, 128, 0, stream>>>(out, q, c, tok_pos, tok_slot, n_tokens, H, scale, window); break;
+  case E: RB_LAUNCH("attn_simple_kernel", (attn_simple_kernel<T, E>), blocks, 128, 0, stream, out, q, c, tok_pos, tok_slot, n_tokens, H, scale, window); break;
   switch (epl) {
     CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8)
     default: RB_FAIL("rb_attention_simple: head_dim %d exceeds 256", c.head_dim);

@@ -79,6 +79,8 @@ template <int D, bool DECODE> struct Smem {
 
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   using S = Smem<D, DECODE>;
   constexpr int LD = S::LD;
   constexpr int NT = DECODE ? 2 : 8;          // 8-key column tiles of S per warp
@@ -319,6 +321,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
 // Merges the partials of a split decode in split order.
 __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, int n_splits, int D) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   const int64_t th = blockIdx.x;   // token * H + head
   float m = -INFINITY;
   for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(th * n_splits + s) * 2]);
@@ -348,7 +352,7 @@ int launch_one(const AttnParams& p, dim3 grid, cudaStream_t stream) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = true;
   }
-  kernel<<<grid, WARPS * 32, smem, stream>>>(p);
+  RB_LAUNCH("kernel", (kernel), grid, WARPS * 32, smem, stream, p);
   RB_CHECK_LAUNCH("rb_attention_tiled");
   return 0;
 }
@@ -418,7 +422,7 @@ RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k,
   p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
   if (launch_d<true>(D, p, dim3(B, Kh, n_splits), stream) != 0) return -1;
   if (n_splits > 1) {
-    attn_combine_kernel<<<B * H, D >= 128 ? 128 : 64, 0, stream>>>((__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
+    RB_LAUNCH("attn_combine_kernel", (attn_combine_kernel), B * H, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
     RB_CHECK_LAUNCH("rb_attention_combine");
   }
   return 0;

@@ -4,6 +4,7 @@
 #include "rb_common.cuh"
 
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 static thread_local char g_error[512];
@@ -17,6 +18,15 @@ void rb_set_error(const char* fmt, ...) {
 
 RB_EXPORT const char* rb_last_error() { return g_error; }
 
+bool rb_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("RBITNET_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
 RB_EXPORT int rb_abi_version() { return 1; }
 
 // ---------------------------------------------------------------- embedding
@@ -26,6 +36,8 @@ RB_EXPORT int rb_abi_version() { return 1; }
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
                              const int* __restrict__ ids, int E, int V) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -40,9 +52,9 @@ RB_EXPORT int rb_embed(float* out, const void* table, int table_dtype, const int
   RB_REQUIRE(T > 0 && E > 0 && V > 0, "rb_embed: bad sizes T=%d E=%d V=%d", T, E, V);
   const int threads = E >= 1024 ? 256 : 128;
   if (table_dtype == RB_F32)
-    embed_kernel<float><<<T, threads, 0, stream>>>(out, (const float*)table, ids, E, V);
+    RB_LAUNCH("embed_kernel", (embed_kernel<float>), T, threads, 0, stream, out, (const float*)table, ids, E, V);
   else if (table_dtype == RB_BF16)
-    embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, E, V);
+    RB_LAUNCH("embed_kernel", (embed_kernel<__nv_bfloat16>), T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, E, V);
   else
     RB_FAIL("rb_embed: unknown dtype %d", table_dtype);
   RB_CHECK_LAUNCH("rb_embed");
@@ -72,6 +84,8 @@ template <typename TO, bool VEC>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const float* __restrict__ w,
                                const float* __restrict__ partials, int n_partials, int64_t partial_stride,
                                int E, float eps) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   __shared__ float scratch[33];
   extern __shared__ __align__(16) float row[];  // E floats
   const int t = blockIdx.x;
@@ -115,6 +129,81 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
   }
 }
 
+// Rows of up to 4*NV*blockDim values (a multiple of 4) kept in registers: every load of a row
+// is in flight before the first is used, and nothing goes through shared memory.
+template <typename TO, int NV>
+__global__ void rmsnorm_reg_kernel(TO* __restrict__ out, float* __restrict__ x, const float* __restrict__ w,
+                                   const float* __restrict__ partials, int n_partials, int64_t partial_stride,
+                                   int E, float eps) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  float* xr = x + (int64_t)t * E;
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (threadIdx.x + i * blockDim.x) * 4;
+    v[i] = j < E ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (n_partials > 0) {
+    const float* pr = partials + (int64_t)t * E;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int j = (threadIdx.x + i * blockDim.x) * 4;
+      if (j < E) {
+        // slices are added in slice order; four loads at a time are in flight
+        int p = 0;
+        for (; p + 4 <= n_partials; p += 4) {
+          const float4 q0 = *reinterpret_cast<const float4*>(pr + (p + 0) * partial_stride + j);
+          const float4 q1 = *reinterpret_cast<const float4*>(pr + (p + 1) * partial_stride + j);
+          const float4 q2 = *reinterpret_cast<const float4*>(pr + (p + 2) * partial_stride + j);
+          const float4 q3 = *reinterpret_cast<const float4*>(pr + (p + 3) * partial_stride + j);
+          v[i].x = (((v[i].x + q0.x) + q1.x) + q2.x) + q3.x;
+          v[i].y = (((v[i].y + q0.y) + q1.y) + q2.y) + q3.y;
+          v[i].z = (((v[i].z + q0.z) + q1.z) + q2.z) + q3.z;
+          v[i].w = (((v[i].w + q0.w) + q1.w) + q2.w) + q3.w;
+        }
+        for (; p < n_partials; ++p) {
+          const float4 q = *reinterpret_cast<const float4*>(pr + p * partial_stride + j);
+          v[i].x += q.x; v[i].y += q.y; v[i].z += q.z; v[i].w += q.w;
+        }
+        *reinterpret_cast<float4*>(xr + j) = v[i];
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  ss = rb_block_sum(ss, scratch);
+  const float r = 1.0f / sqrtf(ss / (float)E + eps);
+  TO* o = out + (int64_t)t * E;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (threadIdx.x + i * blockDim.x) * 4;
+    if (j < E) {
+      const float4 g = *reinterpret_cast<const float4*>(w + j);
+      store4<TO>(o + j, v[i].x * g.x * r, v[i].y * g.y * r, v[i].z * g.z * r, v[i].w * g.w * r);
+    }
+  }
+}
+
+template <typename TO>
+static int launch_rmsnorm_reg(TO* out, float* x, const float* w, const float* partials, int n_partials, int T, int E,
+                              float eps, cudaStream_t stream) {
+  const int threads = E <= 1024 ? 128 : (E <= 4096 ? 256 : 1024);
+  const int nv = (E / 4 + threads - 1) / threads;
+  const int64_t ps = (int64_t)T * E;
+  switch (nv) {
+    case 1: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 1>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
+    case 2: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 2>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
+    case 3: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 3>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
+    default: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 4>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
+  }
+  RB_CHECK_LAUNCH("rb_rmsnorm");
+  return 0;
+}
+
 template <typename TO, bool VEC>
 static int launch_rmsnorm(TO* out, float* x, const float* w, const float* partials, int n_partials, int T, int E,
                           float eps, cudaStream_t stream) {
@@ -124,7 +213,7 @@ static int launch_rmsnorm(TO* out, float* x, const float* w, const float* partia
   const size_t smem = (size_t)E * sizeof(float);
   if (smem > 48 * 1024)
     RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  rmsnorm_kernel<TO, VEC><<<T, threads, smem, stream>>>(out, x, w, partials, n_partials, (int64_t)T * E, E, eps);
+  RB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<TO, VEC>), T, threads, smem, stream, out, x, w, partials, n_partials, (int64_t)T * E, E, eps);
   RB_CHECK_LAUNCH("rb_rmsnorm");
   return 0;
 }
@@ -138,6 +227,12 @@ RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, con
   if (partials == nullptr) n_partials = 0;
   const bool vec = E % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                    ((uintptr_t)out % 16 == 0) && ((uintptr_t)partials % 16 == 0);
+  if (vec && E <= 16384) {
+    if (out_dtype == RB_F32)
+      return launch_rmsnorm_reg<float>((float*)out, x, w, partials, n_partials, T, E, eps, stream);
+    if (out_dtype == RB_BF16)
+      return launch_rmsnorm_reg<__nv_bfloat16>((__nv_bfloat16*)out, x, w, partials, n_partials, T, E, eps, stream);
+  }
   if (out_dtype == RB_F32)
     return vec ? launch_rmsnorm<float, true>((float*)out, x, w, partials, n_partials, T, E, eps, stream)
                : launch_rmsnorm<float, false>((float*)out, x, w, partials, n_partials, T, E, eps, stream);
@@ -165,6 +260,8 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
                                      const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
                                      int interleaved, int heads_per_block) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   const int t = blockIdx.x;
   const int D = cache.head_dim, Kh = cache.n_kv_heads;
   const int pos = tok_pos[t];
@@ -172,6 +269,7 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
   const TI* row = qkv + (int64_t)t * qkv_stride;
   auto value = [&](int64_t i) {
     float v = rb_to_float<TI>(row[i]);
+#pragma unroll 4
     for (int s = 1; s < n_slices; ++s) v += rb_to_float<TI>(row[s * slice_stride + i]);
     return v;
   };
@@ -225,15 +323,11 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
   if (dtype == RB_F32 && in_dtype == RB_F32)
-    rotate_append_kernel<float, float><<<grid, threads, 0, stream>>>((float*)q_out, (const float*)qkv, qkv_stride,
-        n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<float, float>), grid, threads, 0, stream, (float*)q_out, (const float*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else if (dtype == RB_BF16 && in_dtype == RB_BF16)
-    rotate_append_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>((__nv_bfloat16*)q_out,
-        (const __nv_bfloat16*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv,
-        interleaved, hpb);
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16, __nv_bfloat16>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else if (dtype == RB_BF16 && in_dtype == RB_F32)
-    rotate_append_kernel<__nv_bfloat16, float><<<grid, threads, 0, stream>>>((__nv_bfloat16*)q_out, (const float*)qkv,
-        qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16, float>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const float*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else
     RB_FAIL("rb_rotate_append: unsupported dtypes %d <- %d", dtype, in_dtype);
   RB_CHECK_LAUNCH("rb_rotate_append");
@@ -243,6 +337,8 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
 // x[i] += sum over slices of partials[s][i], in slice order (float32).
 __global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partials, int n_partials,
                                     int64_t n) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     float v = x[i];
     for (int p = 0; p < n_partials; ++p) v += partials[p * n + i];
@@ -253,7 +349,7 @@ __global__ void add_partials_kernel(float* __restrict__ x, const float* __restri
 RB_EXPORT int rb_add_partials(float* x, const float* partials, int n_partials, int64_t n, cudaStream_t stream) {
   if (n == 0 || n_partials == 0) return 0;
   const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  add_partials_kernel<<<blocks, 256, 0, stream>>>(x, partials, n_partials, n);
+  RB_LAUNCH("add_partials_kernel", (add_partials_kernel), blocks, 256, 0, stream, x, partials, n_partials, n);
   RB_CHECK_LAUNCH("rb_add_partials");
   return 0;
 }
@@ -263,6 +359,8 @@ RB_EXPORT int rb_add_partials(float* x, const float* partials, int n_partials, i
 // crates/bitnet-core/src/llama/model.rs:116-120, 297-302
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int F) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / F;
     const int j = (int)(i % F);
@@ -278,10 +376,9 @@ RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int T, int 
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
   if (dtype == RB_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)gate_up, n, F);
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F);
   else if (dtype == RB_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out,
-                                                                  (const __nv_bfloat16*)gate_up, n, F);
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, F);
   else
     RB_FAIL("rb_silu_mul: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_silu_mul");
@@ -291,6 +388,8 @@ RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int T, int 
 // ---------------------------------------------------------------- row gather (float32 residual rows)
 __global__ void gather_rows_kernel(float* __restrict__ out, const float* __restrict__ x,
                                    const int* __restrict__ rows, int E) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   const int r = blockIdx.x;
   const float* src = x + (int64_t)rows[r] * E;
   float* dst = out + (int64_t)r * E;
@@ -299,7 +398,7 @@ __global__ void gather_rows_kernel(float* __restrict__ out, const float* __restr
 
 RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R, int E, cudaStream_t stream) {
   if (R == 0) return 0;
-  gather_rows_kernel<<<R, 256, 0, stream>>>(out, x, rows, E);
+  RB_LAUNCH("gather_rows_kernel", (gather_rows_kernel), R, 256, 0, stream, out, x, rows, E);
   RB_CHECK_LAUNCH("rb_gather_rows");
   return 0;
 }
@@ -309,6 +408,8 @@ RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R,
 // position moves on by one, so that steps can follow one another without the host.
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ tok_pos,
                                       const int* __restrict__ sampled, int B) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < B) {
     token_ids[i] = sampled[i];
@@ -318,7 +419,7 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restri
 
 RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled, int B, cudaStream_t stream) {
   if (B == 0) return 0;
-  decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(token_ids, tok_pos, sampled, B);
+  RB_LAUNCH("decode_advance_kernel", (decode_advance_kernel), (B + 127) / 128, 128, 0, stream, token_ids, tok_pos, sampled, B);
   RB_CHECK_LAUNCH("rb_decode_advance");
   return 0;
 }

@@ -18,6 +18,8 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, in
                                                          const TA* __restrict__ A, int64_t lda,
                                                          const TA* __restrict__ W, int64_t ldw, int M, int N,
                                                          int K, int accumulate) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   __shared__ float As[BK][BM + 1];
   __shared__ float Ws[BK][BN + 1];
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -77,8 +79,9 @@ RB_EXPORT int rb_gemm_simple(void* C, int64_t ldc, int c_dtype, const void* A, i
   RB_REQUIRE(M > 0 && N > 0 && K > 0, "rb_gemm_simple: bad sizes M=%d N=%d K=%d", M, N, K);
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   RB_REQUIRE(grid.y <= 65535, "rb_gemm_simple: M=%d too large for one launch", M);
-#define LAUNCH(TA, TC) \
-  gemm_simple_kernel<TA, TC><<<grid, 256, 0, stream>>>((TC*)C, ldc, (const TA*)A, lda, (const TA*)W, ldw, M, N, K, accumulate)
+#define LAUNCH(TA, TC)                                                                                     \
+  RB_LAUNCH("gemm_simple_kernel", (gemm_simple_kernel<TA, TC>), grid, 256, 0, stream, (TC*)C, ldc, (const TA*)A, \
+            lda, (const TA*)W, ldw, M, N, K, accumulate)
   if (a_dtype == RB_F32 && c_dtype == RB_F32) LAUNCH(float, float);
   else if (a_dtype == RB_BF16 && c_dtype == RB_F32) LAUNCH(__nv_bfloat16, float);
   else if (a_dtype == RB_BF16 && c_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

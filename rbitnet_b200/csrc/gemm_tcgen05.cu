@@ -148,18 +148,30 @@ struct GemmParams {
   int n_t_tiles;      // token tiles
   int splits;         // parts of K
   int n_items;        // weight tiles * token tiles * splits
+  int cluster;        // 1: the splits of a tile form a thread-block cluster and are summed through shared memory
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 // A CTA takes work items blockIdx.x, blockIdx.x + gridDim.x, ...; item = ((weight tile * token
 // tiles) + token tile) * splits + split, so CTAs that run together share tiles of W and X in L2.
 // When two accumulators fit in tensor memory they alternate, and the epilogue of one item runs
 // while the tensor cores work on the next.
-template <int BN, int STAGES, int EPI, typename OutT>
-__global__ void __launch_bounds__(192, 1)
+// MINB: CTAs that share an SM (2 for the small token tiles of a decode step: twice as many, smaller
+// items stream W together and finish together, which evens out an item count that does not
+// divide by the number of SMs).
+template <int BN, int STAGES, int EPI, typename OutT, int MINB>
+__global__ void __launch_bounds__(192, MINB)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
   constexpr bool GATED = EPI == EPI_GATED;
   constexpr int X_TILE_BYTES = BN * BK * 2;
@@ -179,8 +191,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __shared__ uint64_t accum_empty[NBUF];
   __shared__ uint32_t tmem_holder;
 
+  rb_pdl_launch_dependents();     // the next kernel may be set up while this one runs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nkb_total = (p.K + BK - 1) / BK;
+  // cluster mode: grid (splits, tiles), one item per CTA, blockIdx.x is the split and the cluster rank
+  const int first_item = blockIdx.y * p.splits + blockIdx.x;
+  const int item_stride = p.cluster ? p.n_items : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -204,6 +220,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_holder;
+  // barriers and tensor memory are ready; from here on global memory is touched, so everything
+  // earlier in the stream has to be complete
+  rb_pdl_wait();
 
   // what an item covers
   auto item_of = [&](int item, int& n0, int& t0, int& kb_begin, int& nkb, int& split) {
@@ -220,7 +239,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x) {
+      for (int item = first_item; item < p.n_items && ok; item += item_stride) {
         int n0, t0, kb_begin, nkb, split;
         item_of(item, n0, t0, kb_begin, nkb, split);
         for (int i = 0; i < nkb; ++i, ++it) {
@@ -243,7 +262,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       constexpr uint32_t idesc = make_idesc(BN);
       uint32_t it = 0, li = 0;
       bool ok = true;
-      for (int item = blockIdx.x; item < p.n_items && ok; item += gridDim.x, ++li) {
+      for (int item = first_item; item < p.n_items && ok; item += item_stride, ++li) {
         int n0, t0, kb_begin, nkb, split;
         item_of(item, n0, t0, kb_begin, nkb, split);
         const int b = li % NBUF;
@@ -279,7 +298,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;        // tensor-memory lanes 32*quarter .. +31 belong to this warp
     uint32_t li = 0;
-    for (int item = blockIdx.x; item < p.n_items; item += gridDim.x, ++li) {
+    for (int item = first_item; item < p.n_items; item += item_stride, ++li) {
       int n0, t0, kb_begin, nkb, split;
       item_of(item, n0, t0, kb_begin, nkb, split);
       const int b = li % NBUF;
@@ -290,6 +309,27 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tcgen05_fence_after();
       const int n = n0 + quarter * 32 + lane;           // output column = weight row
       const bool n_ok = n < p.n_out;
+      if (p.cluster) {
+        // this split's accumulator goes to shared memory (the stage ring is idle now: every MMA
+        // that read it has completed); rank 0 adds the splits up after the cluster barrier below
+        float* red = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (t0 + c >= p.n_tokens) break;
+          uint32_t r[16];
+          __syncwarp();
+          if (nkb > 0) {
+            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * ACC_COLS + c), r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) red[(c + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+        }
+        break;        // one item per CTA in this mode
+      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         if (t0 + c >= p.n_tokens) break;
@@ -336,6 +376,60 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&accum_empty[b]);
     }
+  }
+  if (p.cluster) {
+    // every thread of every CTA of the cluster arrives here, also after a wait that gave up
+    static_assert(EPI == EPI_GATED || BN * BM * 4 <= STAGES * STAGE_BYTES, "the ring holds one accumulator");
+    __syncwarp();
+    cluster_sync_all();
+    if (EPI != EPI_GATED && warp >= 2 && first_item < p.n_items) {
+      // every CTA of the cluster adds up a share of the token columns (column c belongs to rank
+      // c mod splits), reading all parts of a column in split order through distributed shared memory
+      int n0, t0, kb_begin, nkb, split;
+      item_of(first_item, n0, t0, kb_begin, nkb, split);
+      const int quarter = warp & 3;
+      const int n = n0 + quarter * 32 + lane;
+      const int my = (int)cluster_rank();
+      const uint32_t red = smem_u32(smem) + (uint32_t)(quarter * 32 + lane) * 4;
+      uint32_t remote[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[r]) : "r"(red), "r"((uint32_t)(r < p.splits ? r : 0)));
+      if (n < p.n_out) {
+        for (int cb = 0; cb < BN; cb += 2 * p.splits) {
+          int col[2];
+          bool ok[2];
+          float old[2], part[2][8];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            col[h] = cb + h * p.splits + my;
+            ok[h] = col[h] < BN && t0 + col[h] < p.n_tokens;
+            old[h] = 0.f;
+            if (EPI == EPI_ADD && ok[h]) old[h] = ((const float*)p.C)[(int64_t)(t0 + col[h]) * p.ldc + n];
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {      // all loads first, then the sums in split order
+              part[h][r] = 0.f;
+              if (ok[h] && r < p.splits)
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[h][r]) : "r"(remote[r] + (uint32_t)(col[h] * BM) * 4));
+            }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (!ok[h]) continue;
+            float v = part[h][0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) v += part[h][r];
+            const int64_t at = (int64_t)(t0 + col[h]) * p.ldc + n;
+            if (EPI == EPI_ADD) ((float*)p.C)[at] = old[h] + v;
+            else store_out<OutT>((OutT*)p.C + at, v);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cluster_sync_all();        // nobody's shared memory goes away while rank 0 reads it
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -420,19 +514,39 @@ int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, int EPI, typename OutT>
+template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   constexpr int stage_bytes = W_TILE_BYTES * (EPI == EPI_GATED ? 2 : 1) + BN * BK * 2;
   constexpr int smem = STAGES * stage_bytes + 1024;
-  static_assert(smem <= 227 * 1024, "shared memory");
-  auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT>;
+  static_assert(smem * MINB <= 227 * 1024, "shared memory");
+  auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT, MINB>;
   static bool configured = false;
   if (!configured) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  const int grid = p.n_items < sm_count() ? p.n_items : sm_count();     // one CTA per SM, items in turn
-  kernel<<<grid, 192, smem, stream>>>(tw, tx, p);
+  if (p.cluster) {
+    // grid (splits, tiles): the CTAs of one tile are one cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.splits, p.n_items / p.splits, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = rb_pdl_enabled() ? 2 : 1;
+    RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p));
+    return 0;
+  }
+  const int slots = sm_count() * MINB;
+  const int grid = p.n_items < slots ? p.n_items : slots;     // resident CTAs take items in turn
+  RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, p);
   RB_CHECK_LAUNCH("rb_gemm_tc");
   return 0;
 }
@@ -441,11 +555,11 @@ template <int EPI, typename OutT>
 int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   constexpr bool G = EPI == EPI_GATED;
   switch (bn) {
-    case 16: return launch<16, G ? 5 : 10, EPI, OutT>(tw, tx, p, stream);
-    case 32: return launch<32, G ? 5 : 10, EPI, OutT>(tw, tx, p, stream);
-    case 64: return launch<64, G ? 5 : 8, EPI, OutT>(tw, tx, p, stream);
-    case 128: return launch<128, G ? 4 : 6, EPI, OutT>(tw, tx, p, stream);
-    case 256: return launch<256, G ? 3 : 4, EPI, OutT>(tw, tx, p, stream);
+    case 16: return launch<16, 5, EPI, OutT, G ? 1 : 2>(tw, tx, p, stream);
+    case 32: return launch<32, 5, EPI, OutT, G ? 1 : 2>(tw, tx, p, stream);
+    case 64: return launch<64, G ? 5 : 4, EPI, OutT, G ? 1 : 2>(tw, tx, p, stream);
+    case 128: return launch<128, G ? 4 : 6, EPI, OutT, 1>(tw, tx, p, stream);
+    case 256: return launch<256, G ? 3 : 4, EPI, OutT, 1>(tw, tx, p, stream);
   }
   RB_FAIL("rb_gemm_tc: no kernel for a token tile of %d", bn);
 }
@@ -466,7 +580,9 @@ RB_EXPORT int rb_read_error_flag(int* value, int reset) {
 
 // C (+)= X W^T on the tensor cores.
 //   epilogue 0: C[tokens, n_out] = product, c_dtype float32 or bfloat16
-//   epilogue 1: C (float32) += product                       (splits must be 1)
+//   epilogue 1: C (float32) += product
+//   (epilogues 0 and 1 with 2..8 splits: the CTAs of a tile form a cluster and the first adds
+//    the parts up through distributed shared memory, in split order; token tile <= 64)
 //   epilogue 2: C is [splits][tokens][ldc] float32 slices; slice z holds the product over its part of K
 //   epilogue 3: W = [gate ; up] with up starting at row up_row0; C[tokens, n_out] = silu(gate)*up
 // Requirements (refused otherwise): bfloat16 X and W, K a multiple of 8, row strides multiples of 8
@@ -478,7 +594,8 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
   RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
   RB_REQUIRE(splits >= 1, "rb_gemm_tc: splits %d", splits);
-  RB_REQUIRE(epilogue == EPI_PARTIAL || splits == 1, "rb_gemm_tc: only the slice epilogue can split K");
+  RB_REQUIRE(epilogue != EPI_GATED || splits == 1, "rb_gemm_tc: the gated product cannot split K");
+  RB_REQUIRE(epilogue == EPI_PARTIAL || splits <= 8, "rb_gemm_tc: at most 8 splits are summed on the device (%d asked)", splits);
   const int nkb = (K + BK - 1) / BK;
   RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
   int bn = token_tile;
@@ -497,6 +614,8 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   const long long items = (long long)n_w_tiles * n_t_tiles * splits;
   RB_REQUIRE(items < (1ll << 30), "rb_gemm_tc: too many tiles");
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
+  p.cluster = (splits > 1 && epilogue != EPI_PARTIAL) ? 1 : 0;
+  RB_REQUIRE(!p.cluster || bn <= 64, "rb_gemm_tc: K is split only for token tiles of at most 64");
   if (epilogue == EPI_STORE && c_dtype == RB_BF16) return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, stream);
   if (epilogue == EPI_STORE && c_dtype == RB_F32) return dispatch<EPI_STORE, float>(bn, tw, tx, p, stream);
   if (epilogue == EPI_ADD && c_dtype == RB_F32) return dispatch<EPI_ADD, float>(bn, tw, tx, p, stream);

@@ -39,6 +39,40 @@ void rb_set_error(const char* fmt, ...);
     if (e__ != cudaSuccess) RB_FAIL("%s failed: %s", #call, cudaGetErrorString(e__)); \
   } while (0)
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of the library is launched with the attribute that lets it start while the
+// kernel before it in the stream is still running.  A kernel therefore calls rb_pdl_wait()
+// before its first access to global memory (after the wait, everything earlier in the stream
+// has completed and is visible), and rb_pdl_launch_dependents() as early as it can, so that
+// the next kernel's launch and set-up overlap this kernel's work.  Inside a captured graph the
+// same launches become programmatic edges.
+__device__ __forceinline__ void rb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void rb_pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool rb_pdl_enabled();   // RBITNET_PDL=0 in the environment turns the launch attribute off
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t rb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = rb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define RB_LAUNCH(name, kernel, grid, block, smem, stream, ...)                              \
+  do {                                                                                       \
+    cudaError_t e__ = rb_launch(kernel, grid, block, smem, stream, __VA_ARGS__);             \
+    if (e__ != cudaSuccess) RB_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
 // ---------------------------------------------------------------- scalar conversions
 template <typename T> __device__ __forceinline__ float rb_to_float(T v);
 template <> __device__ __forceinline__ float rb_to_float<float>(float v) { return v; }

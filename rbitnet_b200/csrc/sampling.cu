@@ -26,6 +26,8 @@ __device__ __forceinline__ float clean(float v) { return v != v ? -INFINITY : v;
 __global__ void __launch_bounds__(THREADS) sample_stats_kernel(float* __restrict__ stats,
                                                               const float* __restrict__ logits, int64_t row_stride,
                                                               int V, int chunk, const float* __restrict__ temperature) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   __shared__ float scratch[33];
   __shared__ int s_arg;
   const int r = blockIdx.x, c = blockIdx.y, n_chunks = gridDim.y;
@@ -60,6 +62,8 @@ __global__ void __launch_bounds__(THREADS) sample_pick_kernel(int* __restrict__ 
                                                              int V, int chunk, int n_chunks,
                                                              const float* __restrict__ temperature,
                                                              const float* __restrict__ uniform) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
   __shared__ float part[THREADS];
   __shared__ float s_m, s_before, s_target;
   __shared__ int s_chunk, s_pick;
@@ -157,10 +161,9 @@ RB_EXPORT int rb_sample(int* out, const float* logits, int64_t row_stride, int R
   RB_REQUIRE(stats != nullptr, "rb_sample: no scratch");
   const int n_chunks = rb_sample_chunks(V);
   const int chunk = (V + n_chunks - 1) / n_chunks;
-  sample_stats_kernel<<<dim3(R, n_chunks), THREADS, 0, stream>>>(stats, logits, row_stride, V, chunk, temperature);
+  RB_LAUNCH("sample_stats_kernel", (sample_stats_kernel), dim3(R, n_chunks), THREADS, 0, stream, stats, logits, row_stride, V, chunk, temperature);
   RB_CHECK_LAUNCH("rb_sample (stats)");
-  sample_pick_kernel<<<R, THREADS, 0, stream>>>(out, stats, logits, row_stride, V, chunk, n_chunks, temperature,
-                                                uniform);
+  RB_LAUNCH("sample_pick_kernel", (sample_pick_kernel), R, THREADS, 0, stream, out, stats, logits, row_stride, V, chunk, n_chunks, temperature, uniform);
   RB_CHECK_LAUNCH("rb_sample (pick)");
   return 0;
 }

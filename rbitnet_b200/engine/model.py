@@ -77,13 +77,9 @@ class Model:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
-        if hasattr(ops, "begin_step"):
-            ops.begin_step()
         x = ops.embed(meta.token_ids, self.embedding)            # float32 residual stream [T, E]
         for e, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].run(ctx, x, e)
-        if hasattr(ops, "settle"):
-            ops.settle(x)             # a product still waiting to be added to the residual stream
         if meta.n_want == 0:
             return None
         rows = ops.gather_rows(x, meta.want_rows)

@@ -42,14 +42,6 @@ class GateUpWeight:
     n_in: int
 
 
-@dataclass
-class SplitProduct:
-    """A product whose inner dimension was cut into parts: float32 slices [parts, T, out] that
-    the consumer adds up in slice order (``rotate_append`` does; ``CudaOps.settle_product`` makes
-    an ordinary tensor of it)."""
-    slices: torch.Tensor
-
-
 class CudaOps:
     def __init__(self, dtype=torch.bfloat16, device="cuda:0", verbose_build: bool = True):
         if dtype not in _CODE:
@@ -64,8 +56,6 @@ class CudaOps:
             raise KernelError(f"device {self.device} has compute capability {major}.{minor}; "
                               "the kernels are built for sm_100a only")
         self.lib = load(verbose=verbose_build)
-        #: float32 slices waiting to be added to a residual tensor, by the tensor's address
-        self._pending = {}
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -116,53 +106,31 @@ class CudaOps:
         self._check(x, torch.float32, "rmsnorm input")
         T, E = x.shape
         out = torch.empty((T, E), dtype=out_dtype or self.dtype, device=self.device)
-        if partials is None:
-            partials = self._pending.pop(x.data_ptr(), None)      # fold a split product on the way
-        else:
-            self.settle(x)
         n_part = 0 if partials is None else partials.shape[0]
         self.lib.call("rb_rmsnorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), _ptr(partials), n_part,
                       T, E, float(eps), self._stream())
         return out
 
     def linear(self, x: torch.Tensor, weight: LinearWeight, out_dtype=None,
-               accumulate_into: Optional[torch.Tensor] = None, allow_split: bool = False,
-               deferred_ok: bool = False):
+               accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x[T, in] * W[out, in]^T.  With ``accumulate_into`` (float32 [T, out]) the
-        product is added to it in float32 and it is returned.  With ``allow_split`` the
-        result may come back as a ``SplitProduct`` (for a consumer that adds the slices).
-        With ``deferred_ok`` the sum into ``accumulate_into`` may be left as slices that
-        ``rmsnorm``, ``gather_rows`` or ``settle`` on that tensor fold in; a caller that reads
-        the tensor any other way must call ``settle`` first."""
+        product is added to it in float32 and it is returned."""
         self._check(x, self.dtype, "linear input")
         T, K = x.shape
         if K != weight.n_in:
             raise KernelError(f"linear: input width {K} does not match the weight's {weight.n_in}")
         N = weight.n_out
-        tc = self._tensor_core_ok(x, weight.w)
-        may_split = allow_split if accumulate_into is None else deferred_ok
-        splits = self._k_splits(T, N, K) if tc and may_split else 1
-        if splits > 1:
-            # few weight tiles and few tokens: cut K so that every SM streams a part of the matrix;
-            # each part writes its own float32 slice, added up by the consumer in slice order
-            slices = torch.empty((splits, T, N), dtype=torch.float32, device=self.device)
-            self.lib.call("rb_gemm_tc", _ptr(slices), N, F32, _ptr(x), x.stride(0), T, _ptr(weight.w),
-                          weight.w.stride(0), N, N, K, 2, 0, splits, 0, self._stream())
-            if accumulate_into is not None:
-                self._check(accumulate_into, torch.float32, "linear accumulate_into")
-                self.settle(accumulate_into)
-                self._pending[accumulate_into.data_ptr()] = slices
-                return accumulate_into
-            return SplitProduct(slices)
         if accumulate_into is not None:
             out, acc = accumulate_into, 1
             self._check(out, torch.float32, "linear accumulate_into")
-            self.settle(out)
         else:
             out, acc = torch.empty((T, N), dtype=out_dtype or self.dtype, device=self.device), 0
-        if tc:
+        if self._tensor_core_ok(x, weight.w):
+            # few tokens and few weight tiles: K is cut into parts so that every SM streams a piece
+            # of W; the parts of a tile are one thread-block cluster and are summed on chip
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0), T,
-                          _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, 1, 0, self._stream())
+                          _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, self._k_splits(T, N, K), 0,
+                          self._stream())
         else:
             self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
                           _ptr(weight.w), weight.w.stride(0), self.code, T, N, K, acc, self._stream())
@@ -171,30 +139,15 @@ class CudaOps:
     @staticmethod
     def _k_splits(T: int, N: int, K: int) -> int:
         """Parts to cut the inner dimension into: only for at most 64 tokens (the product is then
-        bound by reading W) and only when the 128-row tiles of W are fewer than the 148 SMs."""
+        bound by reading W) and only when the 128-row tiles of W are fewer than the CTAs that run
+        together (two per SM); at most 8, the size of a cluster."""
         if T > 64:
             return 1
         tiles = -(-N // 128)
         blocks = -(-K // 64)
-        want = max(1, min(148 // tiles, blocks // 4))
+        want = max(1, min(8, 148 // tiles, blocks // 4))
         per = -(-blocks // want)
         return -(-blocks // per)          # no part may be empty
-
-    def begin_step(self) -> None:
-        """Forgets slices left over from a step that did not finish."""
-        self._pending.clear()
-
-    def settle(self, x: torch.Tensor) -> None:
-        """Adds any slices still waiting for the residual tensor ``x`` into it."""
-        slices = self._pending.pop(x.data_ptr(), None)
-        if slices is not None:
-            self.lib.call("rb_add_partials", _ptr(x), _ptr(slices), slices.shape[0], x.numel(), self._stream())
-
-    def settle_product(self, y) -> torch.Tensor:
-        """An ordinary tensor in the compute dtype from the result of ``linear(allow_split=True)``."""
-        if isinstance(y, SplitProduct):
-            return y.slices.sum(dim=0).to(self.dtype)
-        return y
 
     def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         """The tcgen05 product takes bfloat16 operands whose rows TMA can address: inner size and
@@ -221,13 +174,8 @@ class CudaOps:
     def rotate_append(self, qkv: torch.Tensor, rotary, meta, view, n_heads: int) -> torch.Tensor:
         """Rotates q (and k) by position, appends k and v to the cache; returns q [T, H, D]."""
         D, Kh = view.head_dim, view.n_kv_heads
-        if isinstance(qkv, SplitProduct):
-            sl = qkv.slices
-            n_slices, T, width = sl.shape
-            src, stride, slice_stride, in_code = sl, sl.stride(1), sl.stride(0), F32
-        else:
-            T, width = qkv.shape
-            src, stride, n_slices, slice_stride, in_code = qkv, qkv.stride(0), 1, 0, self.code
+        T, width = qkv.shape
+        src, stride, n_slices, slice_stride, in_code = qkv, qkv.stride(0), 1, 0, self.code
         if rotary is None:
             inv_freq, interleaved, rot_dim = self._zeros_freq(D), False, D
         else:
@@ -301,7 +249,6 @@ class CudaOps:
         return meta.extra[key]
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
-        self.settle(x)
         R, E = rows.shape[0], x.shape[1]
         out = torch.empty((R, E), dtype=torch.float32, device=self.device)
         self.lib.call("rb_gather_rows", _ptr(out), _ptr(x), _ptr(rows), R, E, self._stream())

@@ -51,9 +51,6 @@ class Part:
 
 class Norm(Part):
     role = "norm"
-    #: True if ``forward`` reads x only through ``ctx.ops.rmsnorm`` (which folds in the slices a
-    #: split product may have left for x).  Otherwise the block settles x before the norm runs.
-    folds_split_products = False
 
     def forward(self, ctx, x: torch.Tensor, partials=None) -> torch.Tensor:
         raise NotImplementedError

@@ -17,15 +17,10 @@ class PreNormBlock:
         return {"mixer": self.mixer, "feed_forward": self.feed_forward,
                 "mixer_norm": self.mixer_norm, "ffn_norm": self.ffn_norm}
 
-    def _norm(self, norm, ctx, x):
-        if not norm.folds_split_products and hasattr(ctx.ops, "settle"):
-            ctx.ops.settle(x)
-        return norm.forward(ctx, x)
-
     def run(self, ctx, x, entry: int) -> None:
-        h = self._norm(self.mixer_norm, ctx, x)
+        h = self.mixer_norm.forward(ctx, x)
         self.mixer.forward(ctx, h, entry, accumulate_into=x)
-        h = self._norm(self.ffn_norm, ctx, x)
+        h = self.ffn_norm.forward(ctx, x)
         self.feed_forward.forward(ctx, h, accumulate_into=x)
 
 

@@ -24,7 +24,7 @@ class GatedDense(FeedForward):
 
     def forward(self, ctx, h, accumulate_into):
         t = ctx.ops.gated_linear(h, self.w_gate_up)        # silu(gate h) * (up h)
-        ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into, deferred_ok=True)
+        ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into)
 
 
 register_part("feed_forward", "gated_dense", GatedDense)

@@ -9,8 +9,6 @@ from .registry import register_part
 
 
 class RMSNorm(Norm):
-    folds_split_products = True
-
     def __init__(self, width: int, eps: float):
         self.width, self.eps = int(width), float(eps)
         self.weight = None

@@ -44,7 +44,7 @@ def test_embed(ops32, ops16, V, E, T):
     assert torch.equal(ops16.embed(ids, tb), tb[ids.long()].float())
 
 
-@pytest.mark.parametrize("E,T,eps", [(48, 3, 1e-5), (272, 17, 1e-6), (4096, 5, 1e-5), (5000, 2, 1e-3)])
+@pytest.mark.parametrize("E,T,eps", [(48, 3, 1e-5), (272, 17, 1e-6), (4096, 5, 1e-5), (5000, 2, 1e-3), (50, 3, 1e-5), (18000, 2, 1e-5)])
 def test_rmsnorm(ops32, ops16, E, T, eps):
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(T, E, device="cuda", generator=g) * 3
@@ -324,54 +324,62 @@ def test_gather_rows(ops32):
     assert torch.equal(ops32.gather_rows(x, rows), x[rows.long()])
 
 
-@pytest.mark.parametrize("T,N,K", [(1, 256, 4096), (8, 100, 1032), (64, 4096, 1024), (33, 520, 2048)])
-def test_split_product_slices_add_up(ops16, T, N, K):
-    """Few tokens and few weight tiles: the inner dimension is cut into parts.  The slices are
-    folded by the consumer: the next norm (residual case) or the rotation (q, k, v case)."""
+@pytest.mark.parametrize("T,N,K", [(1, 256, 4096), (8, 100, 1032), (64, 4096, 1024), (33, 520, 2048), (5, 6144, 4096)])
+def test_product_split_along_the_inner_dimension(ops16, T, N, K):
+    """Few tokens and few weight tiles: the inner dimension is cut into parts whose CTAs form a
+    cluster; the first of them adds the parts up on chip, in a fixed order."""
     g = torch.Generator(device="cuda").manual_seed(14)
     x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
     w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
     lw = ops16.prepare_linear([w])
-    assert ops16._k_splits(T, N, K) > 1
+    assert 1 < ops16._k_splits(T, N, K) <= 8
     ref = x.double() @ w.double().T
-    y = ops16.linear(x, lw, allow_split=True)
-    from rbitnet_b200.kernels.ops import SplitProduct
-    assert isinstance(y, SplitProduct) and y.slices.shape[0] == ops16._k_splits(T, N, K)
-    assert _rel(y.slices.sum(0), ref) < 2e-5
-    # residual case: the slices wait, and the norm folds them while it reads the row
+    y = ops16.linear(x, lw, out_dtype=F32)
+    assert _rel(y, ref) < 2e-5
+    assert torch.equal(y, ops16.linear(x, lw, out_dtype=F32))          # the same bits every time
+    assert _rel(ops16.linear(x, lw), ref) < 5e-3
     acc = torch.randn(T, N, device="cuda", generator=g)
     want = acc.double() + ref
-    ops16.linear(x, lw, accumulate_into=acc, deferred_ok=True)
-    assert ops16._pending
-    wn = torch.ones(N, device="cuda")
-    h = ops16.rmsnorm(acc, wn, 1e-5, out_dtype=F32)
+    ops16.linear(x, lw, accumulate_into=acc)
     assert _rel(acc, want) < 2e-5
-    assert _rel(h, want / torch.sqrt((want ** 2).mean(-1, keepdim=True) + 1e-5)) < 2e-5
-    # ... or any other reader settles them first
-    acc2 = torch.randn(T, N, device="cuda", generator=g)
-    want2 = acc2.double() + ref
-    ops16.linear(x, lw, accumulate_into=acc2, deferred_ok=True)
-    rows = torch.arange(T, dtype=torch.int32, device="cuda")
-    assert _rel(ops16.gather_rows(acc2, rows), want2) < 2e-5
-    assert not ops16._pending
     ops16.check_errors()
 
 
-def test_rotation_reads_split_slices(ops16):
+def test_slices_of_a_split_product_can_be_written_and_folded(ops16):
+    """The product can also leave its parts as float32 slices; the norm folds slices in slice order
+    while it reads a row, and the rotation kernel reads slices directly."""
+    from ctypes import c_void_p
     from rbitnet_b200.cache import CacheLayerView
-    from rbitnet_b200.kernels.ops import SplitProduct
+    g = torch.Generator(device="cuda").manual_seed(15)
+    T, N, K, S = 8, 512, 2048, 4
+    x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    slices = torch.zeros(S, T, N, device="cuda")
+    P = lambda t: c_void_p(t.data_ptr())
+    st = c_void_p(torch.cuda.current_stream().cuda_stream)
+    ops16.lib.call("rb_gemm_tc", P(slices), N, 0, P(x), K, T, P(w), K, N, N, K, 2, 0, S, 0, st)
+    ref = x.double() @ w.double().T
+    assert _rel(slices.sum(0), ref) < 2e-5 and float(slices[S - 1].abs().max()) > 0
+    acc = torch.randn(T, N, device="cuda", generator=g)
+    want = acc.double() + ref
+    h = ops16.rmsnorm(acc, torch.ones(N, device="cuda"), 1e-5, partials=slices, out_dtype=F32)
+    assert _rel(acc, want) < 2e-5
+    assert _rel(h, want / torch.sqrt((want ** 2).mean(-1, keepdim=True) + 1e-5)) < 2e-5
+    # rotation from slices equals rotation from their (once more rounded) sum
     H, Kh, D, page = 4, 2, 32, 64
     rows = [(0, 3), (1, 70), (0, 4)]
-    g = torch.Generator(device="cuda").manual_seed(15)
-    slices = torch.randn(3, len(rows), (H + 2 * Kh) * D, device="cuda", generator=g)
-    whole = slices.sum(0).to(BF16)
+    sl = torch.randn(3, len(rows), (H + 2 * Kh) * D, device="cuda", generator=g)
+    whole = sl.sum(0).to(BF16)
     inv = (1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(D // 2, dtype=torch.float32) / D)).cuda()
+    meta = _meta(rows)
     outs = []
-    for src in (SplitProduct(slices), whole):
+    for src, in_code, n_sl, sl_stride, stride in ((sl, 0, 3, sl.stride(0), sl.stride(1)), (whole, 1, 1, 0, whole.stride(0))):
         k = torch.zeros(4, Kh, page, D, device="cuda", dtype=BF16)
         v = torch.zeros_like(k)
         table = torch.tensor([[0, 1], [2, 3]], dtype=torch.int32, device="cuda")
-        view = CacheLayerView(k, v, table, 2, page, Kh, D, True, 0)
-        outs.append((ops16.rotate_append(src, (inv, False, D), _meta(rows), view, H), k, v))
-    for a, b in zip(outs[0], outs[1]):
-        assert _rel(a, b.double()) < 8e-3      # the same up to the one extra rounding of `whole`
+        q = torch.empty(len(rows), H, D, device="cuda", dtype=BF16)
+        ops16.lib.call("rb_rotate_append", P(q), P(src), stride, 1, P(inv), P(meta.tok_pos), P(meta.tok_slot), P(k), P(v),
+                       P(table), 2, page, len(rows), H, Kh, D, 1, D, 0, in_code, n_sl, sl_stride, st)
+        outs.append((q, k, v))
+    for a_, b_ in zip(outs[0], outs[1]):
+        assert _rel(a_, b_.double()) < 8e-3

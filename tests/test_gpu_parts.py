@@ -65,7 +65,6 @@ def test_feed_forward_part(dtype):
     resid = torch.randn(T, E)
     x = resid.clone().cuda()
     part.forward(_ctx(ops, None, [(0, 0, T)]), h.cuda(), accumulate_into=x)
-    ops.settle(x)
     ref = resid.double() + plain.gated_mlp(h.double(), {k: v.double() for k, v in w.items()})
     assert_close(x, ref, dtype, "gated feed-forward part")
     with pytest.raises(ValueError, match="activation"):
@@ -105,7 +104,6 @@ def test_attention_mixer_part_in_steps(dtype, H, K, D, pairing, theta, window, s
         h = torch.cat([hs[slots.index(s)][st:st + n] for s, st, n in chunks]).cuda()
         x = torch.zeros(h.shape[0], E, device="cuda")
         part.forward(ctx, h, 0, accumulate_into=x)
-        ops.settle(x)
         off = 0
         for s, _, n in chunks:
             outs[slots.index(s)].append(x[off:off + n].cpu())
@@ -153,7 +151,6 @@ def test_block_part(dtype):
     x0 = torch.randn(T, cfg.hidden_size)
     x = x0.clone().cuda()
     blk.run(_ctx(ops, cache, [(s, 0, T)]), x, 0)
-    ops.settle(x)
     ref, _ = plain.block(x0.double(), plain.layer_weights({k: v for k, v in tensors.items()}, 1, torch.float64),
                          plain.normalise_config(TINY_A), torch.arange(T))
     assert_close(x, ref, dtype, "pre-norm block")

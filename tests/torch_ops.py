@@ -55,7 +55,7 @@ class TorchOps:
         s = (x * x).sum(-1, keepdim=True) / x.shape[-1]
         return (x * w * (1.0 / torch.sqrt(s + eps))).to(out_dtype or self.dtype)
 
-    def linear(self, x, weight, out_dtype=None, accumulate_into=None, allow_split=False, deferred_ok=False):
+    def linear(self, x, weight, out_dtype=None, accumulate_into=None):
         y = x.to(torch.float32) @ weight.w.to(torch.float32).T
         if accumulate_into is not None:
             accumulate_into += y
