@@ -220,9 +220,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_holder;
-  // barriers and tensor memory are ready; from here on global memory is touched, so everything
-  // earlier in the stream has to be complete
-  rb_pdl_wait();
+  // Barriers and tensor memory are ready.  Whoever touches memory that an earlier kernel may
+  // still be writing or reading calls rb_pdl_wait() first: the loader before it loads X, the
+  // epilogue warps before they touch C.  W is never written, so its first tiles are requested
+  // before the wait and stream in while the kernel before this one finishes.
 
   // what an item covers
   auto item_of = [&](int item, int& n0, int& t0, int& kb_begin, int& nkb, int& split) {
@@ -239,10 +240,31 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      // the first item's first stages: W before the wait, X after it
+      int early = 0;
+      if (first_item < p.n_items) {
+        int n0, t0, kb_begin, nkb, split;
+        item_of(first_item, n0, t0, kb_begin, nkb, split);
+        early = min(nkb, STAGES);
+        for (int i = 0; i < early; ++i) {
+          uint8_t* stage = smem + (size_t)i * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+          const int k = (kb_begin + i) * BK;
+          tma_load_2d(stage, &tmW, k, n0, &full_bar[i]);
+          if (GATED) tma_load_2d(stage + W_TILE_BYTES, &tmW, k, p.up_row0 + n0, &full_bar[i]);
+        }
+        rb_pdl_wait();
+        for (int i = 0; i < early; ++i) {
+          uint8_t* stage = smem + (size_t)i * STAGE_BYTES;
+          tma_load_2d(stage + W_TILE_BYTES * (GATED ? 2 : 1), &tmX, (kb_begin + i) * BK, t0, &full_bar[i]);
+        }
+      }
       for (int item = first_item; item < p.n_items && ok; item += item_stride) {
         int n0, t0, kb_begin, nkb, split;
         item_of(item, n0, t0, kb_begin, nkb, split);
-        for (int i = 0; i < nkb; ++i, ++it) {
+        int i = 0;
+        if (item == first_item) { i = early; it = early; }
+        for (; i < nkb; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
           ok = mbar_wait(&empty_bar[s], phase ^ 1, 1);
@@ -297,6 +319,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;        // tensor-memory lanes 32*quarter .. +31 belong to this warp
+    rb_pdl_wait();                       // before C is read or written
     uint32_t li = 0;
     for (int item = first_item; item < p.n_items; item += item_stride, ++li) {
       int n0, t0, kb_begin, nkb, split;
