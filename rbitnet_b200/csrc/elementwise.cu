@@ -357,31 +357,33 @@ RB_EXPORT int rb_add_partials(float* x, const float* partials, int n_partials, i
 // ---------------------------------------------------------------- SiLU(gate) * up
 // out[t, j] = silu(gu[t, j]) * gu[t, F + j], silu(v) = v / (1 + exp(-v)), in float32.
 // crates/bitnet-core/src/llama/model.rs:116-120, 297-302
-template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int F) {
+template <typename T, typename TI>
+__global__ void silu_mul_kernel(T* __restrict__ out, const TI* __restrict__ gu, int64_t n, int F) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / F;
     const int j = (int)(i % F);
-    const float g = rb_to_float<T>(gu[t * 2 * F + j]);
-    const float u = rb_to_float<T>(gu[t * 2 * F + F + j]);
+    const float g = rb_to_float<TI>(gu[t * 2 * F + j]);
+    const float u = rb_to_float<TI>(gu[t * 2 * F + F + j]);
     out[i] = rb_from_float<T>(g / (1.0f + expf(-g)) * u);
   }
 }
 
-RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int T, int F, cudaStream_t stream) {
+// in_dtype: dtype of gate_up (the output dtype, or RB_F32 for a bfloat16 output).
+RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int in_dtype, int T, int F, cudaStream_t stream) {
   if (T == 0) return 0;
   const int64_t n = (int64_t)T * F;
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
-  if (dtype == RB_F32)
-    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F);
-  else if (dtype == RB_BF16)
-    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, F);
+  if (dtype == RB_F32 && in_dtype == RB_F32)
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<float, float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F);
+  else if (dtype == RB_BF16 && in_dtype == RB_BF16)
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, F);
+  else if (dtype == RB_BF16 && in_dtype == RB_F32)
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16, float>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const float*)gate_up, n, F);
   else
-    RB_FAIL("rb_silu_mul: unknown dtype %d", dtype);
-  RB_CHECK_LAUNCH("rb_silu_mul");
+    RB_FAIL("rb_silu_mul: unsupported dtypes %d <- %d", dtype, in_dtype);
   return 0;
 }
 

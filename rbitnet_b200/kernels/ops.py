@@ -145,7 +145,9 @@ class CudaOps:
             return 1
         tiles = -(-N // 128)
         blocks = -(-K // 64)
-        want = max(1, min(8, 148 // tiles, blocks // 4))
+        want = 1
+        while want * 2 <= min(8, 296 // tiles, blocks // 4):      # 1, 2, 4 or 8: the sizes clusters schedule well
+            want *= 2
         per = -(-blocks // want)
         return -(-blocks // per)          # no part may be empty
 
@@ -161,6 +163,15 @@ class CudaOps:
         """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype."""
         T = x.shape[0]
         out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
+        if self._tensor_core_ok(x, weight.w) and T <= 64:
+            # few tokens: the product is bound by reading W, and twice as many plain tiles keep more
+            # SMs streaming than the two-accumulator tiles; gate and up stay float32 until activated
+            gu = torch.empty((T, 2 * weight.inner), dtype=torch.float32, device=self.device)
+            self.lib.call("rb_gemm_tc", _ptr(gu), gu.stride(0), F32, _ptr(x), x.stride(0), T, _ptr(weight.w),
+                          weight.w.stride(0), 2 * weight.inner, 2 * weight.inner, weight.n_in, 0, 0, 1, 0,
+                          self._stream())
+            self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, F32, T, weight.inner, self._stream())
+            return out
         if self._tensor_core_ok(x, weight.w):
             # two accumulators per tile; the activation and the product happen on the way out
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), T,
@@ -168,7 +179,7 @@ class CudaOps:
                           3, weight.inner, 1, 0, self._stream())
             return out
         gu = self.linear(x, LinearWeight(weight.w, 2 * weight.inner, weight.n_in))
-        self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, T, weight.inner, self._stream())
+        self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, self.code, T, weight.inner, self._stream())
         return out
 
     def rotate_append(self, qkv: torch.Tensor, rotary, meta, view, n_heads: int) -> torch.Tensor:
@@ -229,9 +240,18 @@ class CudaOps:
 
     @staticmethod
     def _decode_splits(batch: int, n_kv_heads: int, max_context: int) -> int:
-        """Parts a decode's keys are cut into so that about three CTAs per SM have work."""
+        """Parts a decode's keys are cut into.  About three CTAs of the decode kernel fit an SM; the
+        number of parts is the one (up to 16) that fills whole waves of those 444 places best,
+        since a last wave with a few CTAs costs as much as a full one."""
         tiles = max(1, -(-max_context // 64))
-        return max(1, min(32, tiles, -(-444 // (batch * n_kv_heads))))
+        places = 444
+        best, best_eff = 1, 0.0
+        for s in range(1, min(16, tiles) + 1):
+            ctas = batch * n_kv_heads * s
+            eff = ctas / (-(-ctas // places) * places)
+            if eff > best_eff + 0.02:
+                best, best_eff = s, eff
+        return best
 
     def _prefill_tiles(self, meta, tokens_per_tile: int):
         """Tiles of at most ``tokens_per_tile`` consecutive tokens of one sequence (device int32 arrays);
