@@ -245,9 +245,12 @@ class CudaOps:
         since a last wave with a few CTAs costs as much as a full one."""
         tiles = max(1, -(-max_context // 64))
         places = 444
+        pairs = batch * n_kv_heads
+        if pairs <= places:                      # one wave: as many parts as fit it
+            return max(1, min(16, tiles, places // pairs))
         best, best_eff = 1, 0.0
         for s in range(1, min(16, tiles) + 1):
-            ctas = batch * n_kv_heads * s
+            ctas = pairs * s
             eff = ctas / (-(-ctas // places) * places)
             if eff > best_eff + 0.02:
                 best, best_eff = s, eff
