@@ -303,6 +303,73 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
   }
 }
 
+// Many tokens, bfloat16 in and out, head_dim a multiple of 16: one block per token.  A thread owns
+// eight rotation pairs (the same eight in every head), computes their sines and cosines once,
+// and walks over the heads with 16-byte loads and stores; values are copied 16 bytes at a time.
+__global__ void __launch_bounds__(256) rotate_append_rows_kernel(
+    __nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride,
+    const float* __restrict__ inv_freq, const int* __restrict__ tok_pos, const int* __restrict__ tok_slot,
+    RbPagedLayer cache, int H, int write_kv, int interleaved) {
+  rb_pdl_launch_dependents();
+  rb_pdl_wait();
+  const int t = blockIdx.x;
+  const int D = cache.head_dim, Kh = cache.n_kv_heads;
+  const int pos = tok_pos[t], slot = tok_slot[t];
+  const __nv_bfloat16* row = qkv + (int64_t)t * qkv_stride;
+  const int groups = D / 16;                       // groups of eight pairs per head
+  const int lanes = blockDim.x / groups;           // threads that share a group walk different heads
+  const int grp = threadIdx.x % groups, lane = threadIdx.x / groups;
+  const int n_rot = H + (write_kv ? Kh : 0);
+  __nv_bfloat16* kdst = (__nv_bfloat16*)cache.k;
+  __nv_bfloat16* vdst = (__nv_bfloat16*)cache.v;
+  if (lane < lanes) {
+    float sn[8], cs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sincosf((float)pos * inv_freq[grp * 8 + j], &sn[j], &cs[j]);
+    // element offsets of the two 16-byte pieces this thread rotates in every head
+    const int off_a = interleaved ? grp * 16 : grp * 8;
+    const int off_b = interleaved ? grp * 16 + 8 : D / 2 + grp * 8;
+    for (int head = lane; head < n_rot; head += lanes) {
+      const __nv_bfloat16* src = row + (int64_t)head * D;
+      uint4 va = *reinterpret_cast<const uint4*>(src + off_a);
+      uint4 vb = *reinterpret_cast<const uint4*>(src + off_b);
+      __nv_bfloat16* ea = reinterpret_cast<__nv_bfloat16*>(&va);
+      __nv_bfloat16* eb = reinterpret_cast<__nv_bfloat16*>(&vb);
+      if (interleaved) {
+        // pairs (2i, 2i+1): pairs 0..3 lie in va, 4..7 in vb
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          __nv_bfloat16* e = j < 4 ? ea : eb;
+          const int o = (j & 3) * 2;
+          const float x0 = __bfloat162float(e[o]), x1 = __bfloat162float(e[o + 1]);
+          e[o] = __float2bfloat16_rn(x0 * cs[j] - x1 * sn[j]);
+          e[o + 1] = __float2bfloat16_rn(x0 * sn[j] + x1 * cs[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float x0 = __bfloat162float(ea[j]), x1 = __bfloat162float(eb[j]);
+          ea[j] = __float2bfloat16_rn(x0 * cs[j] - x1 * sn[j]);
+          eb[j] = __float2bfloat16_rn(x0 * sn[j] + x1 * cs[j]);
+        }
+      }
+      __nv_bfloat16* dst = head < H ? q_out + ((int64_t)t * H + head) * D
+                                    : kdst + rb_page_offset(cache, slot, pos, head - H);
+      *reinterpret_cast<uint4*>(dst + off_a) = va;
+      *reinterpret_cast<uint4*>(dst + off_b) = vb;
+    }
+  }
+  if (write_kv) {
+    const __nv_bfloat16* vsrc = row + (int64_t)(H + Kh) * D;
+    const int per_head = D / 8;
+    for (int idx = threadIdx.x; idx < Kh * per_head; idx += blockDim.x) {
+      const int kvh = idx / per_head, c = idx % per_head;
+      *reinterpret_cast<uint4*>(vdst + rb_page_offset(cache, slot, pos, kvh) + c * 8) =
+          *reinterpret_cast<const uint4*>(vsrc + (int64_t)kvh * D + c * 8);
+    }
+  }
+}
+
 // in_dtype: dtype of qkv (the compute dtype, or RB_F32 slices for a bfloat16 cache); n_slices >= 1.
 RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride, int dtype,
                                const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
@@ -322,6 +389,13 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   if (by > n_heads) by = n_heads;
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
+  if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 128 && D % 16 == 0 && D <= 256 * 16 &&
+      qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+      ((uintptr_t)cache_k % 16 == 0) && ((uintptr_t)cache_v % 16 == 0)) {
+    RB_LAUNCH("rotate_append_rows_kernel", (rotate_append_rows_kernel), T, 256, 0, stream, (__nv_bfloat16*)q_out,
+              (const __nv_bfloat16*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
+    return 0;
+  }
   if (dtype == RB_F32 && in_dtype == RB_F32)
     RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<float, float>), grid, threads, 0, stream, (float*)q_out, (const float*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else if (dtype == RB_BF16 && in_dtype == RB_BF16)

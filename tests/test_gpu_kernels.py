@@ -383,3 +383,26 @@ def test_slices_of_a_split_product_can_be_written_and_folded(ops16):
         outs.append((q, k, v))
     for a_, b_ in zip(outs[0], outs[1]):
         assert _rel(a_, b_.double()) < 8e-3
+
+
+@pytest.mark.parametrize("H,Kh,D,interleaved", [(4, 2, 16, True), (3, 1, 48, False), (8, 2, 128, False), (2, 2, 256, True)])
+def test_rotation_of_many_tokens(ops16, H, Kh, D, interleaved):
+    """The many-token form of the rotation (one block per token, 16-byte accesses) against the
+    few-token form on the same rows."""
+    from rbitnet_b200.cache import CacheLayerView
+    page, max_pages, n_slots, T = 64, 4, 2, 200
+    rows = [(0, p) for p in range(130)] + [(1, p) for p in range(17, 17 + T - 130)]
+    g = torch.Generator(device="cuda").manual_seed(16)
+    qkv = torch.randn(T, (H + 2 * Kh) * D, device="cuda", generator=g).to(BF16)
+    inv = (1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(D // 2, dtype=torch.float32) / D)).cuda()
+    table = torch.randperm(n_slots * max_pages).to(torch.int32).reshape(n_slots, max_pages).cuda()
+    res = []
+    for chunk in (T, 100):      # 200 rows at once (many-token kernel), or in two steps of 100 (few-token kernel)
+        k = torch.zeros(n_slots * max_pages, Kh, page, D, device="cuda", dtype=BF16)
+        v = torch.zeros_like(k)
+        view = CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0)
+        qs = [ops16.rotate_append(qkv[i:i + chunk], (inv, interleaved, D), _meta(rows[i:i + chunk]), view, H)
+              for i in range(0, T, chunk)]
+        res.append((torch.cat(qs), k, v))
+    for a, b in zip(res[0], res[1]):
+        assert torch.equal(a, b)
