@@ -1,0 +1,341 @@
+// Prefill attention on the 5th-generation tensor cores: S = Q K^T and O += P V are tcgen05.mma
+// with the accumulators in tensor memory; keys and values come from the paged cache by TMA.
+//
+// One CTA works for ONE kv head of ONE sequence on a tile of 128 rows; a row is a (token, query
+// head) pair of the heads that share the kv head (row r -> token r / G, head kvh*G + r % G), so
+// the G heads of a group reuse every key and value tile.  Keys and values arrive in tiles of 64
+// positions (one page, or an aligned part of a page): [64, D] per kv head, two stages.
+//
+// Roles (192 threads): warp 0 loads K and V tiles with TMA; warp 1 owns tensor memory and issues
+// the MMAs; warps 2..5 are the softmax: thread = one row.  Per key tile:
+//   MMA:      S[128, 64] = Q[128, D] K[64, D]^T                     (bfloat16 in, float32 in TMEM)
+//   softmax:  read the row of S, mask by position (causal, window), running max and sum in
+//             float32, rescale the row of O in tensor memory when the max moved, round P to
+//             bfloat16 into shared memory (the A operand of the next MMA)
+//   MMA:      O[128, D] += P[128, 64] V[64, D]
+// The score is (q.k)*scale with the scale folded into the exponent (base 2).
+// crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound, P V), :102-114 (softmax).
+//
+// All operands are K-major with the 128-byte swizzle except V, whose tile [keys, D] has D
+// contiguous: it is the MN-major B operand of O += P V.  Every mbarrier wait is bounded.
+#include "rb_tcgen05.cuh"
+
+namespace {
+
+constexpr int ROWS = 128;          // rows of a CTA (UMMA M)
+constexpr int TILE_KEYS = 64;      // keys per tile (UMMA N of S, K of P V)
+constexpr int KV_STAGES = 2;
+
+struct TcAttnParams {
+  const __nv_bfloat16* q;   // [T, H, D]
+  __nv_bfloat16* out;       // [T, H*D]
+  const int* page_table;
+  int max_pages, page_size, n_kv_heads;
+  const int* tok_pos;
+  const int* tok_slot;
+  const int* tile_tok0;
+  const int* tile_ntok;
+  int n_tiles;
+  int H, G;
+  float scale_log2;
+  int window;
+};
+
+// byte offset of element (row, col) in a K-major tile of 64 columns with the 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
+  return (uint32_t)(row * 128 + ((((col >> 3) ^ (row & 7))) << 4) + (col & 7) * 2);
+}
+
+// MN-major operand (the contiguous dimension is M or N), 128-byte swizzle: 64 contiguous elements
+// per row of 128 bytes, eight K rows per group of 1024 bytes; `lbo` is the distance between
+// 64-element blocks along M/N.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)(lbo_bytes >> 4) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int D>
+struct TcSmem {
+  static constexpr int DB = D / 64;                         // 64-column blocks of a head
+  static constexpr int Q_BYTES = ROWS * 128 * DB;           // DB blocks of [128 rows][128 bytes]
+  static constexpr int KV_TILE_BYTES = TILE_KEYS * 128 * DB;
+  static constexpr int P_BYTES = ROWS * 128;
+  static constexpr int OFF_K = Q_BYTES;
+  static constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
+  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int BYTES = OFF_BAR + 128;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TcAttnParams p) {
+  using S = TcSmem<D>;
+  constexpr int DB = S::DB;
+  constexpr int O_COL = TILE_KEYS;                          // tensor memory: S in columns [0,64), O in [64, 64+D)
+  constexpr int TMEM_COLS = (TILE_KEYS + D) <= 128 ? 128 : 256;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
+  uint64_t* kv_full = bars;                  // [2]
+  uint64_t* kv_empty = bars + 2;             // [2]
+  uint64_t* s_full = bars + 4;
+  uint64_t* p_full = bars + 5;
+  uint64_t* o_full = bars + 6;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 7);
+
+  rb_pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = p.n_tiles - 1 - (int)blockIdx.x;         // late tiles see the most keys: start them first
+  const int kvh = blockIdx.y;
+  const int G = p.G, H = p.H;
+
+  if (threadIdx.x == 0) {
+    if ((smem_u32(smem) & 1023u) != 0) atomicCAS(&g_error_flag, 0, 9);
+    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  rb_pdl_wait();                                           // q and the cache come from earlier kernels
+
+  const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+  const int slot = p.tok_slot[tok0], pos0 = p.tok_pos[tok0];
+  const int n_rows = ntok * G;
+  const int key_hi = pos0 + ntok - 1;
+  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int kt_begin = key_lo / TILE_KEYS, kt_end = key_hi / TILE_KEYS + 1;
+
+  // ---- Q rows into shared memory, swizzled as the K-major A operand (rows beyond n_rows are zero)
+  for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += blockDim.x) {
+    const int r = idx / (D / 8), c8 = idx % (D / 8);       // 8 values = 16 bytes
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows) {
+      const int tok = tok0 + r / G, head = kvh * G + r % G;
+      v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + c8 * 8);
+    }
+    const int blk = c8 / 8, col = (c8 % 8) * 8;
+    *reinterpret_cast<uint4*>(smem + blk * (ROWS * 128) + sw128_offset(r, col)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA loader
+    if (lane == 0) {
+      for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
+        const int s = j % KV_STAGES;
+        if (!mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, 5)) break;
+        const int key0 = kt * TILE_KEYS;
+        const int page = p.page_table[(int64_t)slot * p.max_pages + key0 / p.page_size];
+        const int row = (page * p.n_kv_heads + kvh) * p.page_size + key0 % p.page_size;
+        mbar_expect_tx(&kv_full[s], 2 * S::KV_TILE_BYTES);
+#pragma unroll
+        for (int b = 0; b < DB; ++b) {
+          tma_load_2d(smem + S::OFF_K + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmK, b * 64, row, &kv_full[s]);
+          tma_load_2d(smem + S::OFF_V + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmV, b * 64, row, &kv_full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_mn(ROWS, TILE_KEYS, 0, 0);   // Q (K-major) x K (K-major)
+      constexpr uint32_t idesc_o = make_idesc_mn(ROWS, 64, 0, 1);          // P (K-major) x V (N contiguous), 64 columns of D at a time
+      const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + S::OFF_P);
+      bool ok = true;
+      for (int kt = kt_begin, j = 0; kt < kt_end && ok; ++kt, ++j) {
+        const int s = j % KV_STAGES;
+        ok = mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, 6);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t k_addr = smem_u32(smem + S::OFF_K + s * S::KV_TILE_BYTES);
+        const uint32_t v_addr = smem_u32(smem + S::OFF_V + s * S::KV_TILE_BYTES);
+#pragma unroll
+        for (int b = 0; b < DB; ++b)
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint64_t koff = (uint64_t)(k4 * 32 >> 4);
+            umma_bf16(tmem_base, smem_desc_sw128(q_addr + b * (ROWS * 128)) + koff,
+                      smem_desc_sw128(k_addr + b * (TILE_KEYS * 128)) + koff, idesc_s, (b > 0 || k4 > 0) ? 1u : 0u);
+          }
+        tcgen05_commit(s_full);                              // S of this tile (and all earlier MMAs) complete
+        ok = mbar_wait(p_full, j & 1, 7);                    // P of this tile is in shared memory
+        if (!ok) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int k16 = 0; k16 < TILE_KEYS / 16; ++k16)
+#pragma unroll
+          for (int b = 0; b < DB; ++b) {
+            // A: 16 keys of P = 32 bytes along K; B: 16 key rows of V (2048 bytes), 64 columns of block b
+            umma_bf16(tmem_base + O_COL + b * 64, smem_desc_sw128(p_addr) + (uint64_t)(k16 * 32 >> 4),
+                      smem_desc_sw128_mn(v_addr + b * (TILE_KEYS * 128) + k16 * 2048, TILE_KEYS * 128), idesc_o,
+                      (j > 0 || k16 > 0) ? 1u : 0u);
+          }
+        tcgen05_commit(&kv_empty[s]);                        // the stage is free when these MMAs have read it
+      }
+      tcgen05_commit(o_full);
+    }
+  } else {
+    // ------------------------------------------------------------ softmax and output (warps 2..5)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;                       // this thread's row = tensor-memory lane
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const bool row_ok = r < n_rows;
+    const int row_pos = pos0 + r / G;
+    const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
+      if (lane == 0) ok = mbar_wait(s_full, j & 1, 8);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      tcgen05_fence_after();
+      float sv[TILE_KEYS];
+#pragma unroll
+      for (int c = 0; c < TILE_KEYS; c += 16) tmem_ld16(lane_addr + c, reinterpret_cast<uint32_t*>(sv + c));
+      tmem_ld_wait();
+      const int key_base = kt * TILE_KEYS;
+      float m_new = m_run;
+#pragma unroll
+      for (int c = 0; c < TILE_KEYS; ++c) {
+        const int key = key_base + c;
+        const bool allowed = row_ok && key <= row_pos && key >= row_lo;
+        sv[c] = allowed ? sv[c] * p.scale_log2 : -INFINITY;
+        m_new = fmaxf(m_new, sv[c]);
+      }
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = exp2f(m_run - m_use);               // exp2(-inf) = 0 before the first allowed key
+      // the row of O is rescaled when the running max moved (decided per warp: the tensor-memory
+      // instructions are executed by whole warps)
+      const bool moved = j > 0 && m_new > m_run;
+      if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll 1
+        for (int c = 0; c < D; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(lane_addr + O_COL + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st16(lane_addr + O_COL + c, o);
+        }
+        tmem_st_wait();
+      }
+      m_run = m_new;
+      l_run *= corr;
+      // P = exp2(S - m), rounded to bfloat16 into the swizzled A-operand tile
+      uint8_t* prow = smem + S::OFF_P;
+#pragma unroll
+      for (int c8 = 0; c8 < TILE_KEYS / 8; ++c8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float p0 = exp2f(sv[c8 * 8 + 2 * i] - m_use), p1 = exp2f(sv[c8 * 8 + 2 * i + 1] - m_use);
+          l_run += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(prow + sw128_offset(r, c8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- output: O / l
+    if (ok) {
+      if (lane == 0) ok = mbar_wait(o_full, 0, 10);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+    }
+    if (ok) {
+      tcgen05_fence_after();
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      const int tok = tok0 + r / G, head = kvh * G + r % G;
+      __nv_bfloat16* dst = p.out + ((int64_t)tok * H + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 16) {
+        uint32_t o[16];
+        __syncwarp();
+        tmem_ld16(lane_addr + O_COL + c, o);
+        tmem_ld_wait();
+        if (row_ok) {
+          uint32_t w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+template <int D>
+int launch_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& p, int Kh, cudaStream_t stream) {
+  auto kernel = attn_tc_kernel<D>;
+  constexpr int smem = TcSmem<D>::BYTES;
+  static bool configured = false;
+  if (!configured) {
+    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  RB_LAUNCH("rb_attention_prefill_tc", (kernel), dim3(p.n_tiles, Kh), 192, smem, stream, tk, tv, p);
+  return 0;
+}
+
+}  // namespace
+
+int rb_attention_tc_error_flag(int* value, int reset) { return rb_file_error_flag(value, reset); }
+
+// Whether the tensor-memory prefill kernel takes these sizes.
+RB_EXPORT int rb_attention_prefill_tc_supports(int H, int Kh, int D, int page_size) {
+  if (Kh <= 0 || H % Kh) return 0;
+  const int G = H / Kh;
+  return (D == 64 || D == 128) && page_size % TILE_KEYS == 0 && G <= ROWS;
+}
+
+// Prefill over the paged cache: tile i covers tile_ntok[i] <= 128/G tokens of one sequence starting
+// at batch row tile_tok0[i].  cache_k / cache_v: [n_pages, Kh, page_size, D] bfloat16.
+RB_EXPORT int rb_attention_prefill_tc(void* out, const void* q, const void* cache_k, const void* cache_v,
+                                      long long n_pages, const int* page_table, int max_pages, int page_size,
+                                      const int* tok_pos, const int* tok_slot, const int* tile_tok0,
+                                      const int* tile_ntok, int n_tiles, int H, int Kh, int D, float scale,
+                                      int window, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  RB_REQUIRE(rb_attention_prefill_tc_supports(H, Kh, D, page_size),
+             "rb_attention_prefill_tc: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
+  CUtensorMap tk, tv;
+  const long long rows = n_pages * Kh * page_size;
+  if (rb_get_tensor_map(&tk, cache_k, rows, D, D, TILE_KEYS) != 0) return -1;
+  if (rb_get_tensor_map(&tv, cache_v, rows, D, D, TILE_KEYS) != 0) return -1;
+  TcAttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+  p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size; p.n_kv_heads = Kh;
+  p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.tile_tok0 = tile_tok0; p.tile_ntok = tile_ntok; p.n_tiles = n_tiles;
+  p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  if (D == 64) return launch_tc<64>(tk, tv, p, Kh, stream);
+  return launch_tc<128>(tk, tv, p, Kh, stream);
+}

@@ -20,9 +20,8 @@
 // Every wait on an mbarrier is bounded: after about two seconds the waiting thread records an
 // error code in a device word and the CTA leaves through the common exit, freeing its tensor
 // memory.  The host reads the word with rb_read_error_flag().
-#include "rb_common.cuh"
+#include "rb_tcgen05.cuh"
 
-#include <cuda.h>
 #include <mutex>
 #include <unordered_map>
 #include <string>
@@ -36,99 +35,7 @@ constexpr int W_TILE_BYTES = BM * BK * 2;
 
 enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_GATED = 3 };
 
-__device__ int g_error_flag = 0;
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false (and the error word set) after ~2 s.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 1024; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > 2000000000ull) {
-      atomicCAS(&g_error_flag, 0, code);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);   // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused with a swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset: next 8-row group
-  d |= (uint64_t)1 << 46;                    // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;                    // 128-byte swizzle
-  return d;
-}
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-  return (1u << 4)                     // accumulator float32
-         | (1u << 7) | (1u << 10)      // A and B bfloat16
-         | ((uint32_t)(n >> 3) << 17)  // N
-         | ((uint32_t)(BM >> 4) << 24);  // M
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__host__ __device__ constexpr uint32_t make_idesc(int n) { return make_idesc_mn(BM, n, 0, 0); }
 
 template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
@@ -150,10 +57,6 @@ struct GemmParams {
   int n_items;        // weight tiles * token tiles * splits
   int cluster;        // 1: the splits of a tile form a thread-block cluster and are summed through shared memory
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -480,7 +383,7 @@ EncodeTiledFn encode_fn() {
 }
 
 struct MapKey {
-  const void* ptr; int rows, cols; int64_t ld; int box_rows;
+  const void* ptr; long long rows; int cols; int64_t ld; int box_rows;
   bool operator==(const MapKey& o) const {
     return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
   }
@@ -499,7 +402,9 @@ struct MapKeyHash {
 // Tensor map of a row-major bfloat16 matrix [rows, cols] (cols contiguous), box [box_rows, 64],
 // 128-byte swizzle, zero fill outside.  Maps are cached by their arguments: they are pure
 // functions of them.
-int get_map(CUtensorMap* out, const void* ptr, int rows, int cols, int64_t ld, int box_rows) {
+}  // namespace
+
+int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   MapKey key{ptr, rows, cols, ld, box_rows};
@@ -519,13 +424,15 @@ int get_map(CUtensorMap* out, const void* ptr, int rows, int cols, int64_t ld, i
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  RB_REQUIRE(r == CUDA_SUCCESS, "rb_gemm: cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %lld)", (int)r,
+  RB_REQUIRE(r == CUDA_SUCCESS, "rb_gemm: cuTensorMapEncodeTiled failed with %d (rows %lld cols %d ld %lld)", (int)r,
              rows, cols, (long long)ld);
   std::lock_guard<std::mutex> g(mu);
   if (cache.size() > 4096) cache.clear();
   cache[key] = *out;
   return 0;
 }
+
+namespace {
 
 int sm_count() {
   static int n = 0;
@@ -590,14 +497,13 @@ int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmPar
 }  // namespace
 
 // The device word that a kernel sets when one of its bounded waits ran out (0: none).
+int rb_attention_tc_error_flag(int* value, int reset);   // attention_tcgen05.cu
+
 RB_EXPORT int rb_read_error_flag(int* value, int reset) {
-  int v = 0;
-  RB_CUDA(cudaMemcpyFromSymbol(&v, g_error_flag, sizeof(int)));
-  if (reset && v != 0) {
-    int z = 0;
-    RB_CUDA(cudaMemcpyToSymbol(g_error_flag, &z, sizeof(int)));
-  }
-  *value = v;
+  int a = 0, b = 0;
+  if (rb_file_error_flag(&a, reset) != 0) return -1;
+  if (rb_attention_tc_error_flag(&b, reset) != 0) return -1;
+  *value = a != 0 ? a : b;
   return 0;
 }
 
@@ -627,8 +533,8 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   // tensor memory and the epilogue of one overlaps the products of the next
   if (token_tile == 0 && epilogue == EPI_GATED && bn == 256) bn = 128;
   CUtensorMap tw, tx;
-  if (get_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
-  if (get_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
+  if (rb_get_tensor_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
+  if (rb_get_tensor_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
   GemmParams p;
   p.C = C; p.ldc = ldc; p.slice = (int64_t)n_tokens * ldc; p.n_tokens = n_tokens; p.n_out = n_out; p.K = K;
   p.up_row0 = up_row0; p.kb_per_split = (nkb + splits - 1) / splits;

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "rb_decode_advance": [P, P, P, I, P],
     "rb_attention_prefill": [P, P, P, P, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
+    "rb_attention_prefill_tc": [P, P, P, P, L, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode_static": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, I, P],
 }
 
@@ -48,6 +49,7 @@ class KernelLibrary:
         for name, argtypes in _SIGNATURES.items():
             self.declare(name, argtypes)
         self.declare("rb_attention_tiled_supports", [I, I, I, I, I])
+        self.declare("rb_attention_prefill_tc_supports", [I, I, I, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

@@ -56,6 +56,8 @@ class CudaOps:
             raise KernelError(f"device {self.device} has compute capability {major}.{minor}; "
                               "the kernels are built for sm_100a only")
         self.lib = load(verbose=verbose_build)
+        #: prefill attention of head sizes 64 and 128 runs on tcgen05 (else on the mma.sync kernel)
+        self.prefill_on_tcgen05 = True
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -225,6 +227,13 @@ class CudaOps:
                           _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
                           _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, _ptr(part_o), _ptr(part_ml),
                           n_splits, self._stream(), launches=2 if n_splits > 1 else 1)
+        elif self.dtype == torch.bfloat16 and self.prefill_on_tcgen05 and \
+                self.lib.raw("rb_attention_prefill_tc_supports")(H, Kh, D, view.page_size):
+            tok0, ntok, n_tiles = self._prefill_tiles(meta, 128 // (H // Kh))
+            self.lib.call("rb_attention_prefill_tc", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
+                          view.k.shape[0], _ptr(view.page_table), view.max_pages, view.page_size,
+                          _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(tok0), _ptr(ntok), n_tiles, H, Kh, D,
+                          float(scale), win, self._stream())
         elif self.dtype == torch.bfloat16 and \
                 self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 0):
             tok0, ntok, n_tiles = self._prefill_tiles(meta, 64 // (H // Kh))
