@@ -10,7 +10,7 @@
 // the MMAs; warps 2..5 are the softmax: thread = one row.  Per key tile:
 //   MMA:      S[128, 64] = Q[128, D] K[64, D]^T                     (bfloat16 in, float32 in TMEM)
 //   softmax:  read the row of S, mask by position (causal, window), running max and sum in
-//             float32, rescale the row of O in tensor memory when the max moved, round P to
+//             float32, rescale the row of O in tensor memory when the max grew much, round P to
 //             bfloat16 into shared memory (the A operand of the next MMA)
 //   MMA:      O[128, D] += P[128, 64] V[64, D]
 // The score is (q.k)*scale with the scale folded into the exponent (base 2).
@@ -46,6 +46,13 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
   return (uint32_t)(row * 128 + ((((col >> 3) ^ (row & 7))) << 4) + (col & 7) * 2);
 }
 
+// 2^x for x <= 0 (and -inf -> 0) with the hardware approximation (relative error about 2^-22)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // MN-major operand (the contiguous dimension is M or N), 128-byte swizzle: 64 contiguous elements
 // per row of 128 bytes, eight K rows per group of 1024 bytes; `lbo` is the distance between
 // 64-element blocks along M/N.
@@ -73,7 +80,7 @@ struct TcSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TcAttnParams p) {
   using S = TcSmem<D>;
   constexpr int DB = S::DB;
@@ -211,20 +218,34 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       for (int c = 0; c < TILE_KEYS; c += 16) tmem_ld16(lane_addr + c, reinterpret_cast<uint32_t*>(sv + c));
       tmem_ld_wait();
       const int key_base = kt * TILE_KEYS;
+      // a tile that every row of the CTA sees whole needs no mask (all tiles but those on the
+      // diagonal and at the window's edge)
+      const bool whole = key_base + TILE_KEYS - 1 <= pos0 &&
+                         (p.window <= 0 || key_base >= max(0, key_hi - p.window + 1));
       float m_new = m_run;
+      if (whole) {
+        float t = sv[0];
 #pragma unroll
-      for (int c = 0; c < TILE_KEYS; ++c) {
-        const int key = key_base + c;
-        const bool allowed = row_ok && key <= row_pos && key >= row_lo;
-        sv[c] = allowed ? sv[c] * p.scale_log2 : -INFINITY;
-        m_new = fmaxf(m_new, sv[c]);
+        for (int c = 1; c < TILE_KEYS; ++c) t = fmaxf(t, sv[c]);
+        m_new = fmaxf(m_new, t * p.scale_log2);           // the scale is positive
+      } else {
+#pragma unroll
+        for (int c = 0; c < TILE_KEYS; ++c) {
+          const int key = key_base + c;
+          const bool allowed = row_ok && key <= row_pos && key >= row_lo;
+          sv[c] = allowed ? sv[c] : -INFINITY;
+          m_new = fmaxf(m_new, sv[c] * p.scale_log2);
+        }
       }
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = exp2f(m_run - m_use);               // exp2(-inf) = 0 before the first allowed key
-      // the row of O is rescaled when the running max moved (decided per warp: the tensor-memory
-      // instructions are executed by whole warps)
-      const bool moved = j > 0 && m_new > m_run;
-      if (__any_sync(0xffffffffu, moved)) {
+      // The exponent's reference m_run follows the true running max lazily: it moves only when the
+      // max has grown by more than 8 (a factor 256 in P, harmless in bfloat16 and float32), so the
+      // row of O in tensor memory is rescaled rarely.  l and O use the same reference, so O / l is exact.
+      const bool moved = m_new > m_run + 8.0f || (m_run == -INFINITY && m_new > -INFINITY);
+      const float m_next = moved ? m_new : m_run;
+      const float m_use = m_next == -INFINITY ? 0.f : m_next;
+      const float corr = moved ? exp2f(m_run - m_use) : 1.0f;      // exp2(-inf) = 0 before the first allowed key
+      // decided per warp: the tensor-memory instructions are executed by whole warps
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
         for (int c = 0; c < D; c += 16) {
           uint32_t o[16];
@@ -236,21 +257,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         }
         tmem_st_wait();
       }
-      m_run = m_new;
+      m_run = m_next;
       l_run *= corr;
       // P = exp2(S - m), rounded to bfloat16 into the swizzled A-operand tile
-      uint8_t* prow = smem + S::OFF_P;
+      uint8_t* prow = smem + S::OFF_P + r * 128;
+      const float neg_m = -m_use;
 #pragma unroll
       for (int c8 = 0; c8 < TILE_KEYS / 8; ++c8) {
         uint32_t w[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float p0 = exp2f(sv[c8 * 8 + 2 * i] - m_use), p1 = exp2f(sv[c8 * 8 + 2 * i + 1] - m_use);
+          // p = 2^(s*scale - m): one multiply-add and one exponential; 2^(-inf) = 0 for masked keys
+          const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * i], p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * i + 1], p.scale_log2, neg_m));
           l_run += p0 + p1;
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           w[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(prow + sw128_offset(r, c8 * 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tcgen05_fence_before();
