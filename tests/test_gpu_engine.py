@@ -176,3 +176,56 @@ def test_greedy_generation_through_the_entry_point(engines, name, dtype):
     if dtype == "float32":
         for p, r in zip(ps, res):
             assert r.tokens == plain.generate_greedy(ref.cfg, ref.tensors, p, 10, stop)
+
+
+# Mid-size configurations: head sizes 64 and 128 and widths of several tiles, so that the engine runs
+# the tensor-core product over many tiles, the tcgen05 prefill attention and the split decode kernels
+# (the tiny configurations have head sizes 16 and 32, which take the other attention kernels).
+MID = {
+    "M64": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=512, num_attention_heads=8,
+                num_key_value_heads=2, head_dim=64, intermediate_size=1432, vocab_size=1000, rope_theta=10000.0,
+                rms_norm_eps=1e-5, max_position_embeddings=1024, tie_word_embeddings=False, rope_pairing="half"),
+    "M128": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=768, num_attention_heads=6,
+                 num_key_value_heads=3, head_dim=128, intermediate_size=1048, vocab_size=777, rope_theta=500000.0,
+                 rms_norm_eps=1e-6, max_position_embeddings=1024, tie_word_embeddings=True,
+                 rope_pairing="interleaved"),
+}
+
+
+@pytest.mark.parametrize("name", list(MID))
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mid_size_prefill_chunks_and_decode(tmp_path, name, dtype):
+    """Unequal prompts (one long enough for many key tiles) in one step, a second chunk for one of them,
+    then tokens one by one for all; against the plain model."""
+    from rbitnet_b200 import Engine, StepEntry
+    cfg = MID[name]
+    folder = make_model_dir(tmp_path / "m", cfg, 11, store=dtype, factor=2.0)   # scores spread with a deviation of about one
+    ref = PlainModel(folder)
+    eng = Engine.load_path(folder, dtype=dtype, max_tokens=4096)
+    V = cfg["vocab_size"]
+    ps = prompts([700, 130, 37], V, seed=41)
+    first = [520, 126, 33]
+    slots = [eng.new_sequence() for _ in ps]
+    got = [[] for _ in ps]
+    out = eng.step([StepEntry(s, p[:n], [0, n // 2, n - 1]) for s, p, n in zip(slots, ps, first)])
+    for i in range(3):
+        got[i].append((out[3 * i:3 * i + 3], [0, first[i] // 2, first[i] - 1]))
+    out = eng.step([StepEntry(slots[0], ps[0][520:696], [0, 175])])            # a later chunk of the long prompt
+    got[0].append((out, [520, 695]))
+    for k in range(4):
+        out = eng.step([StepEntry(s, [p[len(p) - 4 + k]], [0]) for s, p in zip(slots, ps)])
+        for i, p in enumerate(ps):
+            got[i].append((out[i:i + 1], [len(p) - 4 + k]))
+    for i, p in enumerate(ps):
+        want = ref.logits(p)
+        for rows, places in got[i]:
+            assert_close(rows, want[places], dtype, f"{name} request {i} places {places}")
+    for s in slots:
+        eng.end_sequence(s)
+    res = eng.generate([ps[1][:100], ps[2]], max_tokens=6, temperature=0.0)
+    for p, r in zip([ps[1][:100], ps[2]], res):
+        full = ref.logits(list(p) + r.tokens)
+        for i, t in enumerate(r.tokens):
+            row = full[len(p) - 1 + i]
+            atol, rtol = (1e-5, 1e-4) if dtype == "float32" else (0.0, 2e-2)
+            assert float(row[t]) >= float(row.max()) - 2 * (atol + rtol * float(row.abs().max()))
