@@ -389,7 +389,7 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   if (by > n_heads) by = n_heads;
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
-  if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 128 && D % 16 == 0 && D <= 256 * 16 &&
+  if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 32 && D % 16 == 0 && D <= 256 * 16 &&
       qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)cache_k % 16 == 0) && ((uintptr_t)cache_v % 16 == 0)) {
     RB_LAUNCH("rotate_append_rows_kernel", (rotate_append_rows_kernel), T, 256, 0, stream, (__nv_bfloat16*)q_out,

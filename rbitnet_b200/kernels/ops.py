@@ -270,6 +270,12 @@ class CudaOps:
         made once per step and kept on the step's meta."""
         import numpy as np
         key = ("attention_tiles", tokens_per_tile)
+        if key not in meta.extra and meta.single_token:
+            # one token per sequence: a tile per row, made on the device (this also runs while a
+            # decode step is being captured, where a copy from the host is not allowed)
+            n = meta.n_tokens
+            meta.extra[key] = (torch.arange(n, dtype=torch.int32, device=self.device),
+                               torch.ones(n, dtype=torch.int32, device=self.device), n)
         if key not in meta.extra:
             tok0, ntok = [], []
             for c in meta.seqs:

@@ -350,3 +350,40 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path, dt
     finally:
         unregister_architecture("ToyDecayLM")
         unregister_part("mixer", "toy_decay")
+
+
+@pytest.mark.parametrize("head_dim,theta", [(16, 10000.0), (48, 500000.0), (128, 1e6)])
+def test_position_encoding_part(head_dim, theta):
+    """The rotary part's inverse frequencies are the reference's 1/theta^(2i/D) in float32
+    (crates/bitnet-core/src/llama/model.rs:126-127); 'none' gives no rotation."""
+    from rbitnet_b200.parts import build_part, PartSpec
+    ops = _ops("float32")
+    for pairing in ("half", "interleaved"):
+        part = build_part("position", PartSpec("rotary", {"head_dim": head_dim, "theta": theta, "pairing": pairing}))
+        part.bind({}, ops)
+        inv, interleaved, rot = part.rotary()
+        assert interleaved == (pairing == "interleaved") and rot == head_dim
+        pos = torch.tensor([1000])
+        want = plain.rope_angles(pos, head_dim, theta)[0] / 1000.0
+        assert torch.allclose(inv.cpu(), want, rtol=1e-6, atol=0)
+    assert build_part("position", PartSpec("none", {})).rotary() is None
+    with pytest.raises(ValueError, match="even"):
+        build_part("position", PartSpec("rotary", {"head_dim": 15, "theta": 1e4}))
+
+
+def test_decode_with_more_than_16_heads_per_kv_head_through_captured_steps(tmp_path):
+    """Multi-query attention with 20 query heads on one kv head: the decode step takes the prefill
+    kernels (the split decode kernel holds at most 16 heads per group), also when captured."""
+    from rbitnet_b200 import Engine
+    cfg = dict(TINY_B, num_attention_heads=20, num_key_value_heads=1, head_dim=64, hidden_size=1280,
+               intermediate_size=520, num_hidden_layers=1)
+    folder = make_model_dir(tmp_path / "m", cfg, 8, store="bfloat16", factor=1.0)
+    ref = PlainModel(folder)
+    eng = Engine.load_path(folder, dtype="bfloat16", max_tokens=1024)
+    ps = prompts([70, 3], cfg["vocab_size"], 70)
+    res = eng.generate(ps, max_tokens=4, temperature=0.0)
+    for p, r in zip(ps, res):
+        full = ref.logits(list(p) + r.tokens)
+        for i, t in enumerate(r.tokens):
+            row = full[len(p) - 1 + i]
+            assert float(row[t]) >= float(row.max()) - 4e-2 * float(row.abs().max())
