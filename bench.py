@@ -191,6 +191,49 @@ def prefill_flops(cfg, layers, tokens):
     return layers * (per_layer + attn) + 2 * E * V
 
 
+# The other generation workloads of BASELINE.json (configs[3] and configs[4]), run through Engine.generate.
+WORKLOADS = {
+    "llama2_7b_unequal": dict(
+        model=dict(architectures=["LlamaForCausalLM"], num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+                   num_key_value_heads=32, head_dim=128, intermediate_size=11008, vocab_size=32000, rope_theta=10000.0,
+                   rms_norm_eps=1e-5, max_position_embeddings=4096),
+        prompts=16, len_lo=64, len_hi=2048, max_tokens=256, temperature=0.0),
+    "tinyllama_b64_sampling": dict(
+        model=dict(architectures=["LlamaForCausalLM"], num_hidden_layers=22, hidden_size=2048, num_attention_heads=32,
+                   num_key_value_heads=4, head_dim=64, intermediate_size=5632, vocab_size=32000, rope_theta=10000.0,
+                   rms_norm_eps=1e-5, max_position_embeddings=2048),
+        prompts=64, len_lo=512, len_hi=512, max_tokens=1024, temperature=0.8),
+}
+
+
+def run_workload(name):
+    """End-to-end generation (host token ids in, generated ids out) of one of WORKLOADS; one short line."""
+    import torch
+    from rbitnet_b200 import Engine
+    w = WORKLOADS[name]
+    cfg = w["model"]
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(w["len_lo"], w["len_hi"] + 1, (w["prompts"],), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    cache_tokens = sum(-(-(n + w["max_tokens"]) // 64) * 64 for n in lens) + 4096
+    eng = Engine.from_random(cfg, seed=1, dtype="bfloat16", max_tokens=cache_tokens,
+                             max_seq=cfg["max_position_embeddings"], max_batch=64)
+    times = []
+    for _ in range(2):                     # the first run also captures the decode steps
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = eng.generate(prompts, max_tokens=w["max_tokens"], temperature=w["temperature"], seed=3, stop_ids=[])
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    new = sum(len(r.tokens) for r in res)
+    print(json.dumps({"workload": name, "layers": cfg["num_hidden_layers"], "prompts": len(prompts),
+                      "prompt_tokens": sum(lens), "new_tokens": new, "seconds": round(times[1], 3),
+                      "first_run_seconds": round(times[0], 3), "new_tokens_per_s": round(new / times[1], 1),
+                      "steps": eng.last_stats["steps"], "temperature": w["temperature"], "dtype": "bf16",
+                      "data": "synthetic (random weights and token ids)"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -202,6 +245,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1/64 points")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="'prefill': only the 2,048-token prefill, one short line (for profiling)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="run one of the other generation workloads end to end instead (one short line)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -212,6 +257,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload:
+        return run_workload(args.workload)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
 
     import torch

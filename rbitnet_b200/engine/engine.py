@@ -83,6 +83,7 @@ class Engine:
         self.use_graphs = use_graphs and ops is None
         self._graphs = {}
         self._graph_pool = None
+        self._pad_slot = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -142,6 +143,10 @@ class Engine:
                 f"cache={self.cache.bytes() / 2**20:.1f}MiB")
 
     # ------------------------------------------------------------------ stepping
+    def live_sequences(self) -> List[int]:
+        """Slots held by callers (the engine's own padding sequence is not counted)."""
+        return [s for s in self.cache.book.live() if s != self._pad_slot]
+
     def new_sequence(self) -> int:
         return self.cache.alloc()
 
@@ -161,20 +166,57 @@ class Engine:
             self._graphs[batch] = g
         return g
 
+    @staticmethod
+    def _graph_batch(n: int) -> int:
+        """Batch sizes that get a captured step of their own: 1, 2, 4, then multiples of 8."""
+        return n if n <= 2 else (4 if n <= 4 else -(-n // 8) * 8)
+
+    def _padding_slot(self) -> Optional[int]:
+        """A sequence of its own for the rows that fill a captured step up to its batch size: they
+        rewrite position 0 of this slot and their results are dropped, so they change nothing."""
+        if self._pad_slot is None:
+            try:
+                slot = self.cache.alloc()
+            except Exception:
+                return None
+            try:
+                self.cache.reserve(slot, 1)
+            except Exception:
+                self.cache.free(slot)
+                return None
+            self._pad_slot = slot
+        return self._pad_slot
+
     def _decode_step(self, feed, temperatures, uniforms) -> List[int]:
         slots = [s for s, _ in feed]
         positions = [self.cache.length(s) for s in slots]
         for s in slots:
             self.cache.reserve(s, 1)
+        n = len(feed)
+        tokens = [t[0] for _, t in feed]
+        temperatures, uniforms = list(temperatures), list(uniforms)
+        batch = self._graph_batch(n)
+        run_slots = list(slots)
+        if batch > n:
+            pad = self._padding_slot()
+            if pad is None:
+                batch = n                      # no room for a padding sequence: a step of the exact size
+            else:
+                extra = batch - n
+                run_slots += [pad] * extra
+                tokens += [0] * extra
+                positions = positions + [0] * extra
+                temperatures += [0.0] * extra
+                uniforms += [0.0] * extra
         self.cache.upload_tables()
-        g = self.decode_graph(len(feed))
-        g.stage(slots, [t[0] for _, t in feed], positions, temperatures, uniforms)
+        g = self.decode_graph(batch)
+        g.stage(run_slots, tokens, positions, temperatures, uniforms)
         if g.graph is None:
             g.capture(pool=self._graph_pool)
             if self._graph_pool is None:
                 self._graph_pool = g.graph.pool()
         g.replay()
-        ids = g.read()
+        ids = g.read()[:n]
         for s in slots:
             self.cache.advance(s, 1)
         return ids

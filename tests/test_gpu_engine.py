@@ -158,7 +158,7 @@ def test_greedy_generation_through_the_entry_point(engines, name, dtype):
     ps = prompts([4, 19, 1, 8, 30], V, seed=10)
     stop = [7]
     res = eng.generate(ps, max_tokens=10, temperature=0.0, stop_ids=stop, max_batch=3)
-    assert eng.cache.book.live() == []
+    assert eng.live_sequences() == []
     for p, r in zip(ps, res):
         # every emitted token must be the plain model's arg-max given the tokens before it
         # (within the dtype's tolerance at a near tie), and a stop token is never emitted
