@@ -84,16 +84,20 @@ __global__ void __launch_bounds__(192, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TcAttnParams p) {
   using S = TcSmem<D>;
   constexpr int DB = S::DB;
-  constexpr int O_COL = TILE_KEYS;                          // tensor memory: S in columns [0,64), O in [64, 64+D)
-  constexpr int TMEM_COLS = (TILE_KEYS + D) <= 128 ? 128 : 256;
+  constexpr int O_COL = 2 * TILE_KEYS;                      // tensor memory: two S buffers in columns [0,128), O in [128, 128+D)
+  constexpr int TMEM_COLS = 256;
+  static_assert(2 * TILE_KEYS + D <= 256, "tensor memory columns");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
-  uint64_t* kv_full = bars;                  // [2]
-  uint64_t* kv_empty = bars + 2;             // [2]
-  uint64_t* s_full = bars + 4;
-  uint64_t* p_full = bars + 5;
-  uint64_t* o_full = bars + 6;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 7);
+  uint64_t* k_full = bars;                   // [2] keys of a tile have landed
+  uint64_t* k_empty = bars + 2;              // [2] S of that tile is complete: the key stage is free
+  uint64_t* v_full = bars + 4;               // [2]
+  uint64_t* v_empty = bars + 6;              // [2] P V of that tile is complete
+  uint64_t* s_full = bars + 8;               // [2] one per S buffer
+  uint64_t* p_full = bars + 10;              // P of a tile is in shared memory (one arrival per softmax warp)
+  uint64_t* pv_done = bars + 11;             // P V of a tile is complete: O is consistent, the P buffer is free
+  uint64_t* o_full = bars + 12;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
 
   rb_pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -103,9 +107,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     if ((smem_u32(smem) & 1023u) != 0) atomicCAS(&g_error_flag, 0, 9);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+    }
     mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -147,16 +155,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (lane == 0) {
       for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
         const int s = j % KV_STAGES;
-        if (!mbar_wait(&kv_empty[s], ((j / KV_STAGES) & 1) ^ 1, 5)) break;
+        const uint32_t ph = ((j / KV_STAGES) & 1) ^ 1;
         const int key0 = kt * TILE_KEYS;
         const int page = p.page_table[(int64_t)slot * p.max_pages + key0 / p.page_size];
         const int row = (page * p.n_kv_heads + kvh) * p.page_size + key0 % p.page_size;
-        mbar_expect_tx(&kv_full[s], 2 * S::KV_TILE_BYTES);
+        if (!mbar_wait(&k_empty[s], ph, 5)) break;
+        mbar_expect_tx(&k_full[s], S::KV_TILE_BYTES);
 #pragma unroll
-        for (int b = 0; b < DB; ++b) {
-          tma_load_2d(smem + S::OFF_K + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmK, b * 64, row, &kv_full[s]);
-          tma_load_2d(smem + S::OFF_V + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmV, b * 64, row, &kv_full[s]);
-        }
+        for (int b = 0; b < DB; ++b)
+          tma_load_2d(smem + S::OFF_K + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmK, b * 64, row, &k_full[s]);
+        if (!mbar_wait(&v_empty[s], ph, 5)) break;
+        mbar_expect_tx(&v_full[s], S::KV_TILE_BYTES);
+#pragma unroll
+        for (int b = 0; b < DB; ++b)
+          tma_load_2d(smem + S::OFF_V + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmV, b * 64, row, &v_full[s]);
       }
     }
   } else if (warp == 1) {
@@ -166,25 +178,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       constexpr uint32_t idesc_o = make_idesc_mn(ROWS, 64, 0, 1);          // P (K-major) x V (N contiguous), 64 columns of D at a time
       const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + S::OFF_P);
       bool ok = true;
-      for (int kt = kt_begin, j = 0; kt < kt_end && ok; ++kt, ++j) {
+      const int n_tiles = kt_end - kt_begin;
+      // S of tile j goes to S buffer j & 1.  S(j+1) is issued before P V (j), so the tensor cores
+      // work on the next tile's scores while the softmax of this tile runs.
+      auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES;
-        ok = mbar_wait(&kv_full[s], (j / KV_STAGES) & 1, 6);
-        if (!ok) break;
+        if (!mbar_wait(&k_full[s], (j / KV_STAGES) & 1, 6)) return false;
         tcgen05_fence_after();
         const uint32_t k_addr = smem_u32(smem + S::OFF_K + s * S::KV_TILE_BYTES);
-        const uint32_t v_addr = smem_u32(smem + S::OFF_V + s * S::KV_TILE_BYTES);
 #pragma unroll
         for (int b = 0; b < DB; ++b)
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             const uint64_t koff = (uint64_t)(k4 * 32 >> 4);
-            umma_bf16(tmem_base, smem_desc_sw128(q_addr + b * (ROWS * 128)) + koff,
+            umma_bf16(tmem_base + (uint32_t)((j & 1) * TILE_KEYS), smem_desc_sw128(q_addr + b * (ROWS * 128)) + koff,
                       smem_desc_sw128(k_addr + b * (TILE_KEYS * 128)) + koff, idesc_s, (b > 0 || k4 > 0) ? 1u : 0u);
           }
-        tcgen05_commit(s_full);                              // S of this tile (and all earlier MMAs) complete
+        tcgen05_commit(&s_full[j & 1]);
+        tcgen05_commit(&k_empty[s]);
+        return true;
+      };
+      if (n_tiles > 0) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);
+        if (!ok) break;
+        const int s = j % KV_STAGES;
         ok = mbar_wait(p_full, j & 1, 7);                    // P of this tile is in shared memory
         if (!ok) break;
+        ok = mbar_wait(&v_full[s], (j / KV_STAGES) & 1, 6);
+        if (!ok) break;
         tcgen05_fence_after();
+        const uint32_t v_addr = smem_u32(smem + S::OFF_V + s * S::KV_TILE_BYTES);
 #pragma unroll
         for (int k16 = 0; k16 < TILE_KEYS / 16; ++k16)
 #pragma unroll
@@ -194,7 +218,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                       smem_desc_sw128_mn(v_addr + b * (TILE_KEYS * 128) + k16 * 2048, TILE_KEYS * 128), idesc_o,
                       (j > 0 || k16 > 0) ? 1u : 0u);
           }
-        tcgen05_commit(&kv_empty[s]);                        // the stage is free when these MMAs have read it
+        tcgen05_commit(&v_empty[s]);
+        tcgen05_commit(pv_done);
       }
       tcgen05_commit(o_full);
     }
@@ -209,13 +234,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
-      if (lane == 0) ok = mbar_wait(s_full, j & 1, 8);
+      if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, 8);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tcgen05_fence_after();
       float sv[TILE_KEYS];
+      const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * TILE_KEYS);
 #pragma unroll
-      for (int c = 0; c < TILE_KEYS; c += 16) tmem_ld16(lane_addr + c, reinterpret_cast<uint32_t*>(sv + c));
+      for (int c = 0; c < TILE_KEYS; c += 16) tmem_ld16(s_addr + c, reinterpret_cast<uint32_t*>(sv + c));
       tmem_ld_wait();
       const int key_base = kt * TILE_KEYS;
       // a tile that every row of the CTA sees whole needs no mask (all tiles but those on the
@@ -244,38 +270,48 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const float m_next = moved ? m_new : m_run;
       const float m_use = m_next == -INFINITY ? 0.f : m_next;
       const float corr = moved ? exp2f(m_run - m_use) : 1.0f;      // exp2(-inf) = 0 before the first allowed key
-      // decided per warp: the tensor-memory instructions are executed by whole warps
-      if (j > 0 && __any_sync(0xffffffffu, moved)) {
-#pragma unroll 1
-        for (int c = 0; c < D; c += 16) {
-          uint32_t o[16];
-          tmem_ld16(lane_addr + O_COL + c, o);
-          tmem_ld_wait();
+      // P = 2^(S*scale - m), rounded to bfloat16, kept in registers until the P buffer is free
+      uint32_t pw[TILE_KEYS / 2];
+      {
+        const float neg_m = -m_use;
+        float sum = 0.f;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-          tmem_st16(lane_addr + O_COL + c, o);
+        for (int i = 0; i < TILE_KEYS / 2; ++i) {
+          // one multiply-add and one exponential per value; 2^(-inf) = 0 for masked keys
+          const float p0 = fast_exp2(fmaf(sv[2 * i], p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(sv[2 * i + 1], p.scale_log2, neg_m));
+          sum += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          pw[i] = *reinterpret_cast<uint32_t*>(&h);
         }
-        tmem_st_wait();
+        l_run = l_run * corr + sum;
       }
       m_run = m_next;
-      l_run *= corr;
-      // P = exp2(S - m), rounded to bfloat16 into the swizzled A-operand tile
-      uint8_t* prow = smem + S::OFF_P + r * 128;
-      const float neg_m = -m_use;
+      // P V of the tile before must be complete before O is rescaled and before P is overwritten
+      if (j > 0) {
+        if (lane == 0) ok = mbar_wait(pv_done, (j - 1) & 1, 11);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        tcgen05_fence_after();
+        // decided per warp: the tensor-memory instructions are executed by whole warps
+        if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 16) {
+            uint32_t o[16];
+            tmem_ld16(lane_addr + O_COL + c, o);
+            tmem_ld_wait();
 #pragma unroll
-      for (int c8 = 0; c8 < TILE_KEYS / 8; ++c8) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          // p = 2^(s*scale - m): one multiply-add and one exponential; 2^(-inf) = 0 for masked keys
-          const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * i], p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * i + 1], p.scale_log2, neg_m));
-          l_run += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          w[i] = *reinterpret_cast<uint32_t*>(&h);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st16(lane_addr + O_COL + c, o);
+          }
+          tmem_st_wait();
         }
-        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      uint8_t* prow = smem + S::OFF_P + r * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < TILE_KEYS / 8; ++c8)
+        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) =
+            make_uint4(pw[4 * c8], pw[4 * c8 + 1], pw[4 * c8 + 2], pw[4 * c8 + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tcgen05_fence_before();
       __syncwarp();
