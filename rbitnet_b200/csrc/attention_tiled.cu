@@ -80,7 +80,9 @@ template <int D, bool DECODE> struct Smem {
 template <int D, bool DECODE>
 __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
   rb_pdl_launch_dependents();
-  rb_pdl_wait();
+  // The step's positions, slots and page tables were written before the step began, so they are
+  // read at once; rb_pdl_wait() comes before the first access to what the kernel before this
+  // one wrote (q, and the newest position's keys and values).
   using S = Smem<D, DECODE>;
   constexpr int LD = S::LD;
   constexpr int NT = DECODE ? 2 : 8;          // 8-key column tiles of S per warp
@@ -108,18 +110,6 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
     kt_end = min(kt_end, kt_begin + per);
   }
 
-  // ---- Q rows into shared memory (rows beyond n_rows are zero)
-  for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += WARPS * 32) {
-    const int r = idx / (D / 8), c = idx % (D / 8);
-    if (DECODE && r >= 16) break;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < n_rows) {
-      const int tok = tok0 + r / G, head = kvh * G + r % G;
-      v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + c * 8);
-    }
-    *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
-  }
-
   const __nv_bfloat16* Kbase = reinterpret_cast<const __nv_bfloat16*>(p.cache.k);
   const __nv_bfloat16* Vbase = reinterpret_cast<const __nv_bfloat16*>(p.cache.v);
   auto load_tile = [&](int kt, int buf) {
@@ -136,6 +126,27 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
       cp_async16(vd + r * LD + c * 8, vsrc + r * D + c * 8);
     }
   };
+
+  // Decode: every tile but the one that holds the newest position was written by earlier steps,
+  // so this CTA's first tile can be on its way before the wait.
+  const bool early = DECODE && kt_begin < kt_end && kt_begin != pos0 / TILE_KEYS;
+  if (early) {
+    load_tile(kt_begin, 0);
+    cp_async_commit();
+  }
+  rb_pdl_wait();
+
+  // ---- Q rows into shared memory (rows beyond n_rows are zero)
+  for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += WARPS * 32) {
+    const int r = idx / (D / 8), c = idx % (D / 8);
+    if (DECODE && r >= 16) break;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < n_rows) {
+      const int tok = tok0 + r / G, head = kvh * G + r % G;
+      v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + c * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + r * LD + c * 8) = v;
+  }
 
   // ---- per-warp state
   const int rb = DECODE ? 0 : warp * 16;          // first row of this warp
@@ -155,7 +166,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
   }
 
-  if (kt_begin < kt_end) {
+  if (!early && kt_begin < kt_end) {
     load_tile(kt_begin, 0);
     cp_async_commit();
   }

@@ -136,11 +136,16 @@ __global__ void rmsnorm_reg_kernel(TO* __restrict__ out, float* __restrict__ x, 
                                    const float* __restrict__ partials, int n_partials, int64_t partial_stride,
                                    int E, float eps) {
   rb_pdl_launch_dependents();
-  rb_pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   float* xr = x + (int64_t)t * E;
-  float4 v[NV];
+  float4 v[NV], g[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {       // the norm's weights do not depend on the kernel before
+    const int j = (threadIdx.x + i * blockDim.x) * 4;
+    g[i] = j < E ? *reinterpret_cast<const float4*>(w + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  rb_pdl_wait();
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int j = (threadIdx.x + i * blockDim.x) * 4;
@@ -181,10 +186,7 @@ __global__ void rmsnorm_reg_kernel(TO* __restrict__ out, float* __restrict__ x, 
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int j = (threadIdx.x + i * blockDim.x) * 4;
-    if (j < E) {
-      const float4 g = *reinterpret_cast<const float4*>(w + j);
-      store4<TO>(o + j, v[i].x * g.x * r, v[i].y * g.y * r, v[i].z * g.z * r, v[i].w * g.w * r);
-    }
+    if (j < E) store4<TO>(o + j, v[i].x * g[i].x * r, v[i].y * g[i].y * r, v[i].z * g[i].z * r, v[i].w * g[i].w * r);
   }
 }
 
@@ -261,11 +263,11 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
                                      const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
                                      int interleaved, int heads_per_block) {
   rb_pdl_launch_dependents();
-  rb_pdl_wait();
   const int t = blockIdx.x;
   const int D = cache.head_dim, Kh = cache.n_kv_heads;
   const int pos = tok_pos[t];
   const int slot = tok_slot[t];
+  rb_pdl_wait();     // positions and slots were written before the step began; qkv comes from the kernel before
   const TI* row = qkv + (int64_t)t * qkv_stride;
   auto value = [&](int64_t i) {
     float v = rb_to_float<TI>(row[i]);
