@@ -74,7 +74,10 @@ template <int D, bool DECODE> struct Smem {
   static constexpr int LD = D + 8;
   static constexpr int Q_ELEMS = (DECODE ? 16 : ROWS) * LD;     // decode: one token's heads only
   static constexpr int KV_ELEMS = TILE_KEYS * LD;
-  static constexpr size_t BYTES = (size_t)(Q_ELEMS + 4 * KV_ELEMS) * 2;
+  // two stages of keys and values: one tile on its way while one is used.  (Three stages for
+  // decode, with two CTAs per SM instead of three, measured the same at batch 8 and worse at 64.)
+  static constexpr int STAGES = 2;
+  static constexpr size_t BYTES = (size_t)(Q_ELEMS + 2 * STAGES * KV_ELEMS) * 2;
 };
 
 template <int D, bool DECODE>
@@ -89,8 +92,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
   constexpr int DT = D / 8;                   // 8-wide column tiles of O
   extern __shared__ __align__(16) uint8_t smem_bytes[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
-  __nv_bfloat16* sK = sQ + S::Q_ELEMS;        // [2][64][LD]
-  __nv_bfloat16* sV = sK + 2 * S::KV_ELEMS;   // [2][64][LD]
+  __nv_bfloat16* sK = sQ + S::Q_ELEMS;        // [stages][64][LD]
+  constexpr int NS = S::STAGES;
+  __nv_bfloat16* sV = sK + NS * S::KV_ELEMS;  // [NS][64][LD] after the [NS][64][LD] of the keys
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
@@ -129,10 +133,19 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
 
   // Decode: every tile but the one that holds the newest position was written by earlier steps,
   // so this CTA's first tile can be on its way before the wait.
-  const bool early = DECODE && kt_begin < kt_end && kt_begin != pos0 / TILE_KEYS;
-  if (early) {
-    load_tile(kt_begin, 0);
-    cp_async_commit();
+  // Tiles are requested NS - 1 ahead; one commit group per tile (possibly empty), so that waiting
+  // for all but the newest NS - 2 groups means the current tile has landed.
+  const int newest = pos0 / TILE_KEYS;
+  int n_early = 0;                     // tiles requested before the wait
+  if (DECODE) {
+    for (int i = 0; i < NS - 1; ++i) {
+      const int kt = kt_begin + i;
+      if (kt < kt_end && kt != newest && n_early == i) {
+        load_tile(kt, i);
+        cp_async_commit();
+        n_early = i + 1;
+      }
+    }
   }
   rb_pdl_wait();
 
@@ -166,19 +179,15 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
   }
 
-  if (!early && kt_begin < kt_end) {
-    load_tile(kt_begin, 0);
+  for (int i = n_early; i < NS - 1; ++i) {        // the rest of the first NS - 1 tiles
+    if (kt_begin + i < kt_end) load_tile(kt_begin + i, i);
     cp_async_commit();
   }
   for (int kt = kt_begin; kt < kt_end; ++kt) {
-    const int buf = (kt - kt_begin) & 1;
-    if (kt + 1 < kt_end) {
-      load_tile(kt + 1, buf ^ 1);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
+    const int buf = (kt - kt_begin) % NS;
+    if (kt + NS - 1 < kt_end) load_tile(kt + NS - 1, (kt - kt_begin + NS - 1) % NS);
+    cp_async_commit();
+    cp_async_wait<NS - 1>();             // all but the newest NS - 1 groups: tile kt has landed
     __syncthreads();
     const __nv_bfloat16* tK = sK + buf * S::KV_ELEMS;
     const __nv_bfloat16* tV = sV + buf * S::KV_ELEMS;
@@ -355,7 +364,7 @@ int launch_one(const AttnParams& p, dim3 grid, cudaStream_t stream) {
   size_t smem = Smem<D, DECODE>::BYTES;
   if (DECODE) {
     const size_t merge = (size_t)(WARPS * 16 * D + 2 * WARPS * 16) * 4;
-    const size_t kv = (size_t)4 * Smem<D, DECODE>::KV_ELEMS * 2;
+    const size_t kv = (size_t)2 * Smem<D, DECODE>::STAGES * Smem<D, DECODE>::KV_ELEMS * 2;
     if (merge > kv) smem += merge - kv;
   }
   static bool configured = false;
