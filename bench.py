@@ -234,6 +234,39 @@ def run_workload(name):
     return 0
 
 
+def print_timeline(engine, batch, context):
+    """When each kernel of one captured decode step really ran (CUPTI records through torch.profiler,
+    no replay, no serialisation): with programmatic dependent launch a kernel starts early and
+    waits, so the useful figure per kernel is how long after the previous kernel's end it ended."""
+    import torch
+    from torch.profiler import profile, ProfilerActivity
+    slots = fill_cache(engine, batch, context, 64)
+    g = engine.decode_graph(batch)
+    g.stage(slots, [1] * batch, [context] * batch, [0.0] * batch, [0.5] * batch)
+    if g.graph is None:
+        g.capture(pool=engine._graph_pool)
+    g.stage(slots, [1] * batch, [context] * batch, [0.0] * batch, [0.5] * batch)
+    for _ in range(5):
+        g.replay()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                key=lambda e: e.time_range.start)
+    last = ev[-(len(ev) // 3):]
+    t0, prev_end = last[0].time_range.start, last[0].time_range.start
+    print(f"{'start':>9} {'end':>9} {'after prev end':>15}  kernel   (microseconds from the step's first kernel)")
+    for e in last:
+        end = e.time_range.end
+        print(f"{e.time_range.start - t0:9.1f} {end - t0:9.1f} {end - max(prev_end, t0):15.1f}  {e.name[:80]}")
+        prev_end = max(prev_end, end)
+    print(f"step: {prev_end - t0:.1f} us, {len(last)} kernels")
+    for s_ in slots:
+        engine.end_sequence(s_)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -245,6 +278,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1/64 points")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="'prefill': only the 2,048-token prefill, one short line (for profiling)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print when each kernel of one decode step ran inside the captured graph, and exit")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the other generation workloads end to end instead (one short line)")
     args = ap.parse_args()
@@ -275,6 +310,9 @@ def main():
     torch.cuda.synchronize()
     build_s = time.time() - t_build
 
+    if args.timeline:
+        print_timeline(engine, args.batch, PROMPT_LEN)
+        return 0
     if args.phase == "prefill":
         pf_ms = time_prefill(engine, PROMPT_LEN, reps=max(1, min(3, steps)))
         print(json.dumps({"phase": "prefill", "tokens": PROMPT_LEN, "layers": args.layers, "ms": round(pf_ms, 3),
