@@ -3,17 +3,20 @@
 //
 // One CTA works for ONE kv head of ONE sequence on a tile of 128 rows; a row is a (token, query
 // head) pair of the heads that share the kv head (row r -> token r / G, head kvh*G + r % G), so
-// the G heads of a group reuse every key and value tile.  Keys and values arrive in tiles of 64
-// positions (one page, or an aligned part of a page): [64, D] per kv head, two stages.
+// the G heads of a group reuse every key and value tile.  Keys and values arrive in tiles of 128
+// positions (two 64-position pieces, each one page or an aligned part of a page), two stages each.
+// The instructions are as wide as the head allows (N = 128 keys for S, N = D for O): narrow
+// tcgen05.mma run far below the tensor cores' rate.
 //
-// Roles (192 threads): warp 0 loads K and V tiles with TMA; warp 1 owns tensor memory and issues
-// the MMAs; warps 2..5 are the softmax: thread = one row.  Per key tile:
-//   MMA:      S[128, 64] = Q[128, D] K[64, D]^T                     (bfloat16 in, float32 in TMEM)
+// Roles (320 threads): warp 0 loads K and V tiles with TMA; warp 1 owns tensor memory and issues
+// the MMAs; warps 2..9 are the softmax, two threads per row (64 keys each).  Per key tile:
+//   MMA:      S[128, 128] = Q[128, D] K[128, D]^T                   (bfloat16 in, float32 in TMEM)
 //   softmax:  read the row of S, mask by position (causal, window), running max and sum in
 //             float32, rescale the row of O in tensor memory when the max grew much, round P to
 //             bfloat16 into shared memory (the A operand of the next MMA)
-//   MMA:      O[128, D] += P[128, 64] V[64, D]
-// The score is (q.k)*scale with the scale folded into the exponent (base 2).
+//   MMA:      O[128, D] += P[128, 128] V[128, D]
+// S has two buffers: S of the next tile is issued before P V of this one, so the tensor cores work
+// while the softmax runs.  The score is (q.k)*scale with the scale folded into the exponent (base 2).
 // crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound, P V), :102-114 (softmax).
 //
 // All operands are K-major with the 128-byte swizzle except V, whose tile [keys, D] has D
@@ -23,7 +26,9 @@
 namespace {
 
 constexpr int ROWS = 128;          // rows of a CTA (UMMA M)
-constexpr int TILE_KEYS = 64;      // keys per tile (UMMA N of S, K of P V)
+constexpr int TILE_KEYS = 128;     // keys per tile (UMMA N of S, K of P V)
+constexpr int PIECE = 64;          // positions per TMA piece of a tile (a page, or an aligned part of one)
+constexpr int THREADS = 320;       // loader warp, MMA warp, eight softmax warps
 constexpr int KV_STAGES = 2;
 
 struct TcAttnParams {
@@ -69,24 +74,26 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t 
 template <int D>
 struct TcSmem {
   static constexpr int DB = D / 64;                         // 64-column blocks of a head
-  static constexpr int Q_BYTES = ROWS * 128 * DB;           // DB blocks of [128 rows][128 bytes]
-  static constexpr int KV_TILE_BYTES = TILE_KEYS * 128 * DB;
-  static constexpr int P_BYTES = ROWS * 128;
+  static constexpr int BLOCK = ROWS * 128;                  // a block of [128 rows][128 bytes]
+  static constexpr int Q_BYTES = BLOCK * DB;
+  static constexpr int KV_TILE_BYTES = BLOCK * DB;          // 128 keys, DB blocks
+  static constexpr int P_BYTES = BLOCK * (TILE_KEYS / 64);  // 128 rows, two blocks of 64 keys
   static constexpr int OFF_K = Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
   static constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_MAX = OFF_P + P_BYTES;           // float [2 tiles][2 halves][128 rows]
+  static constexpr int OFF_BAR = OFF_MAX + 2 * 2 * ROWS * 4;
   static constexpr int BYTES = OFF_BAR + 128;
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TcAttnParams p) {
   using S = TcSmem<D>;
   constexpr int DB = S::DB;
-  constexpr int O_COL = 2 * TILE_KEYS;                      // tensor memory: two S buffers in columns [0,128), O in [128, 128+D)
-  constexpr int TMEM_COLS = 256;
-  static_assert(2 * TILE_KEYS + D <= 256, "tensor memory columns");
+  constexpr int O_COL = 2 * TILE_KEYS;                      // tensor memory: two S buffers in columns [0,256), O in [256, 256+D)
+  constexpr int TMEM_COLS = 512;
+  static_assert(2 * TILE_KEYS + D <= 512, "tensor memory columns");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
   uint64_t* k_full = bars;                   // [2] keys of a tile have landed
@@ -98,6 +105,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   uint64_t* pv_done = bars + 11;             // P V of a tile is complete: O is consistent, the P buffer is free
   uint64_t* o_full = bars + 12;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
+  float* row_max = reinterpret_cast<float*>(smem + S::OFF_MAX);
 
   rb_pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,7 +120,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
     }
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
     mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -124,14 +132,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  rb_pdl_wait();                                           // q and the cache come from earlier kernels
-
-  const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+  const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];      // fixed before the step began
   const int slot = p.tok_slot[tok0], pos0 = p.tok_pos[tok0];
   const int n_rows = ntok * G;
   const int key_hi = pos0 + ntok - 1;
   const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int kt_begin = key_lo / TILE_KEYS, kt_end = key_hi / TILE_KEYS + 1;
+  rb_pdl_wait();                                           // q and the cache come from earlier kernels
 
   // ---- Q rows into shared memory, swizzled as the K-major A operand (rows beyond n_rows are zero)
   for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += blockDim.x) {
@@ -142,7 +149,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + c8 * 8);
     }
     const int blk = c8 / 8, col = (c8 % 8) * 8;
-    *reinterpret_cast<uint4*>(smem + blk * (ROWS * 128) + sw128_offset(r, col)) = v;
+    *reinterpret_cast<uint4*>(smem + blk * S::BLOCK + sw128_offset(r, col)) = v;
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tcgen05_fence_before();
@@ -156,26 +163,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = ((j / KV_STAGES) & 1) ^ 1;
-        const int key0 = kt * TILE_KEYS;
-        const int page = p.page_table[(int64_t)slot * p.max_pages + key0 / p.page_size];
-        const int row = (page * p.n_kv_heads + kvh) * p.page_size + key0 % p.page_size;
+        int row[TILE_KEYS / PIECE];
+#pragma unroll
+        for (int h = 0; h < TILE_KEYS / PIECE; ++h) {      // a tile is two pieces of 64 positions
+          const int key0 = kt * TILE_KEYS + h * PIECE;
+          const int pi = min(key0 / p.page_size, p.max_pages - 1);       // past the sequence: any page, masked later
+          const int page = p.page_table[(int64_t)slot * p.max_pages + pi];
+          row[h] = (page * p.n_kv_heads + kvh) * p.page_size + key0 % p.page_size;
+        }
         if (!mbar_wait(&k_empty[s], ph, 5)) break;
         mbar_expect_tx(&k_full[s], S::KV_TILE_BYTES);
 #pragma unroll
         for (int b = 0; b < DB; ++b)
-          tma_load_2d(smem + S::OFF_K + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmK, b * 64, row, &k_full[s]);
+#pragma unroll
+          for (int h = 0; h < TILE_KEYS / PIECE; ++h)
+            tma_load_2d(smem + S::OFF_K + s * S::KV_TILE_BYTES + b * S::BLOCK + h * (PIECE * 128), &tmK, b * 64, row[h], &k_full[s]);
         if (!mbar_wait(&v_empty[s], ph, 5)) break;
         mbar_expect_tx(&v_full[s], S::KV_TILE_BYTES);
 #pragma unroll
         for (int b = 0; b < DB; ++b)
-          tma_load_2d(smem + S::OFF_V + s * S::KV_TILE_BYTES + b * (TILE_KEYS * 128), &tmV, b * 64, row, &v_full[s]);
+#pragma unroll
+          for (int h = 0; h < TILE_KEYS / PIECE; ++h)
+            tma_load_2d(smem + S::OFF_V + s * S::KV_TILE_BYTES + b * S::BLOCK + h * (PIECE * 128), &tmV, b * 64, row[h], &v_full[s]);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_mn(ROWS, TILE_KEYS, 0, 0);   // Q (K-major) x K (K-major)
-      constexpr uint32_t idesc_o = make_idesc_mn(ROWS, 64, 0, 1);          // P (K-major) x V (N contiguous), 64 columns of D at a time
+      constexpr uint32_t idesc_o = make_idesc_mn(ROWS, D, 0, 1);           // P (K-major) x V (D contiguous)
       const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + S::OFF_P);
       bool ok = true;
       const int n_tiles = kt_end - kt_begin;
@@ -191,8 +207,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             const uint64_t koff = (uint64_t)(k4 * 32 >> 4);
-            umma_bf16(tmem_base + (uint32_t)((j & 1) * TILE_KEYS), smem_desc_sw128(q_addr + b * (ROWS * 128)) + koff,
-                      smem_desc_sw128(k_addr + b * (TILE_KEYS * 128)) + koff, idesc_s, (b > 0 || k4 > 0) ? 1u : 0u);
+            umma_bf16(tmem_base + (uint32_t)((j & 1) * TILE_KEYS), smem_desc_sw128(q_addr + b * S::BLOCK) + koff,
+                      smem_desc_sw128(k_addr + b * S::BLOCK) + koff, idesc_s, (b > 0 || k4 > 0) ? 1u : 0u);
           }
         tcgen05_commit(&s_full[j & 1]);
         tcgen05_commit(&k_empty[s]);
@@ -210,59 +226,69 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         tcgen05_fence_after();
         const uint32_t v_addr = smem_u32(smem + S::OFF_V + s * S::KV_TILE_BYTES);
 #pragma unroll
-        for (int k16 = 0; k16 < TILE_KEYS / 16; ++k16)
-#pragma unroll
-          for (int b = 0; b < DB; ++b) {
-            // A: 16 keys of P = 32 bytes along K; B: 16 key rows of V (2048 bytes), 64 columns of block b
-            umma_bf16(tmem_base + O_COL + b * 64, smem_desc_sw128(p_addr) + (uint64_t)(k16 * 32 >> 4),
-                      smem_desc_sw128_mn(v_addr + b * (TILE_KEYS * 128) + k16 * 2048, TILE_KEYS * 128), idesc_o,
-                      (j > 0 || k16 > 0) ? 1u : 0u);
-          }
+        for (int k16 = 0; k16 < TILE_KEYS / 16; ++k16) {
+          // A: 16 keys of P = 32 bytes along K inside the 64-key block k16 / 4;
+          // B: 16 key rows of V (2048 bytes further per step), all D columns: 64-column blocks S::BLOCK apart
+          umma_bf16(tmem_base + O_COL, smem_desc_sw128(p_addr + (k16 / 4) * S::BLOCK) + (uint64_t)((k16 % 4) * 32 >> 4),
+                    smem_desc_sw128_mn(v_addr + k16 * 2048, S::BLOCK), idesc_o, (j > 0 || k16 > 0) ? 1u : 0u);
+        }
         tcgen05_commit(&v_empty[s]);
         tcgen05_commit(pv_done);
       }
       tcgen05_commit(o_full);
     }
   } else {
-    // ------------------------------------------------------------ softmax and output (warps 2..5)
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;                       // this thread's row = tensor-memory lane
+    // ------------------------------------------------------------ softmax and output (warps 2..9)
+    // Two threads per row: thread (quarter, lane, half) owns row quarter*32 + lane, the 64 keys
+    // `half` of every tile and the columns [half*D/2, (half+1)*D/2) of O.  A wait that gives up sets
+    // `failed`; the threads then stop waiting but keep the same control flow, so that the named
+    // barrier below is always reached by all 256 of them.
+    const int quarter = warp & 3;                            // the tensor-memory lanes a warp may touch: warp % 4
+    const int half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const bool row_ok = r < n_rows;
     const int row_pos = pos0 + r / G;
     const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
+    constexpr int HK = TILE_KEYS / 2;                        // keys per thread and tile
+    constexpr int HD = D / 2;                                // columns of O per thread
     float m_run = -INFINITY, l_run = 0.f;
-    bool ok = true;
+    bool failed = false;
     for (int kt = kt_begin, j = 0; kt < kt_end; ++kt, ++j) {
-      if (lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, 8);
+      bool ok = !failed;
+      if (ok && lane == 0) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, 8);
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
+      failed |= !ok;
       tcgen05_fence_after();
-      float sv[TILE_KEYS];
-      const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * TILE_KEYS);
+      float sv[HK];
+      const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) * TILE_KEYS + half * HK);
 #pragma unroll
-      for (int c = 0; c < TILE_KEYS; c += 16) tmem_ld16(s_addr + c, reinterpret_cast<uint32_t*>(sv + c));
+      for (int c = 0; c < HK; c += 16) tmem_ld16(s_addr + c, reinterpret_cast<uint32_t*>(sv + c));
       tmem_ld_wait();
-      const int key_base = kt * TILE_KEYS;
+      const int key_base = kt * TILE_KEYS + half * HK;
       // a tile that every row of the CTA sees whole needs no mask (all tiles but those on the
       // diagonal and at the window's edge)
-      const bool whole = key_base + TILE_KEYS - 1 <= pos0 &&
-                         (p.window <= 0 || key_base >= max(0, key_hi - p.window + 1));
-      float m_new = m_run;
+      const bool whole = kt * TILE_KEYS + TILE_KEYS - 1 <= pos0 &&
+                         (p.window <= 0 || kt * TILE_KEYS >= max(0, key_hi - p.window + 1));
+      float m_half = -INFINITY;
       if (whole) {
-        float t = sv[0];
 #pragma unroll
-        for (int c = 1; c < TILE_KEYS; ++c) t = fmaxf(t, sv[c]);
-        m_new = fmaxf(m_new, t * p.scale_log2);           // the scale is positive
+        for (int c = 0; c < HK; ++c) m_half = fmaxf(m_half, sv[c]);
+        m_half *= p.scale_log2;                              // the scale is positive
       } else {
 #pragma unroll
-        for (int c = 0; c < TILE_KEYS; ++c) {
+        for (int c = 0; c < HK; ++c) {
           const int key = key_base + c;
           const bool allowed = row_ok && key <= row_pos && key >= row_lo;
           sv[c] = allowed ? sv[c] : -INFINITY;
-          m_new = fmaxf(m_new, sv[c] * p.scale_log2);
+          m_half = fmaxf(m_half, sv[c] * p.scale_log2);
         }
       }
+      // the row's max over both halves
+      float* mx = row_max + (j & 1) * 2 * ROWS;
+      mx[half * ROWS + r] = m_half;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float m_new = fmaxf(m_run, fmaxf(m_half, mx[(half ^ 1) * ROWS + r]));
       // The exponent's reference m_run follows the true running max lazily: it moves only when the
       // max has grown by more than 8 (a factor 256 in P, harmless in bfloat16 and float32), so the
       // row of O in tensor memory is rescaled rarely.  l and O use the same reference, so O / l is exact.
@@ -271,12 +297,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       const float m_use = m_next == -INFINITY ? 0.f : m_next;
       const float corr = moved ? exp2f(m_run - m_use) : 1.0f;      // exp2(-inf) = 0 before the first allowed key
       // P = 2^(S*scale - m), rounded to bfloat16, kept in registers until the P buffer is free
-      uint32_t pw[TILE_KEYS / 2];
+      uint32_t pw[HK / 2];
       {
         const float neg_m = -m_use;
         float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < TILE_KEYS / 2; ++i) {
+        for (int i = 0; i < HK / 2; ++i) {
           // one multiply-add and one exponential per value; 2^(-inf) = 0 for masked keys
           const float p0 = fast_exp2(fmaf(sv[2 * i], p.scale_log2, neg_m));
           const float p1 = fast_exp2(fmaf(sv[2 * i + 1], p.scale_log2, neg_m));
@@ -289,27 +315,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       m_run = m_next;
       // P V of the tile before must be complete before O is rescaled and before P is overwritten
       if (j > 0) {
-        if (lane == 0) ok = mbar_wait(pv_done, (j - 1) & 1, 11);
+        ok = !failed;
+        if (ok && lane == 0) ok = mbar_wait(pv_done, (j - 1) & 1, 11);
         ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) break;
+        failed |= !ok;
         tcgen05_fence_after();
         // decided per warp: the tensor-memory instructions are executed by whole warps
         if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 16) {
+          for (int c = 0; c < HD; c += 16) {
             uint32_t o[16];
-            tmem_ld16(lane_addr + O_COL + c, o);
+            tmem_ld16(lane_addr + O_COL + half * HD + c, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st16(lane_addr + O_COL + c, o);
+            tmem_st16(lane_addr + O_COL + half * HD + c, o);
           }
           tmem_st_wait();
         }
       }
-      uint8_t* prow = smem + S::OFF_P + r * 128;
+      uint8_t* prow = smem + S::OFF_P + half * S::BLOCK + r * 128;     // this half's 64 keys are one 128-byte row
 #pragma unroll
-      for (int c8 = 0; c8 < TILE_KEYS / 8; ++c8)
+      for (int c8 = 0; c8 < HK / 8; ++c8)
         *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) =
             make_uint4(pw[4 * c8], pw[4 * c8 + 1], pw[4 * c8 + 2], pw[4 * c8 + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -317,21 +344,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
-    // ---- output: O / l
-    if (ok) {
-      if (lane == 0) ok = mbar_wait(o_full, 0, 10);
+    // ---- output: O / l, the sum l over both halves
+    {
+      bool ok = !failed;
+      if (ok && lane == 0) ok = mbar_wait(o_full, 0, 10);
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      failed |= !ok;
     }
-    if (ok) {
-      tcgen05_fence_after();
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    tcgen05_fence_after();
+    row_max[half * ROWS + r] = l_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float l_all = l_run + row_max[(half ^ 1) * ROWS + r];
+    if (!failed) {
+      const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
       const int tok = tok0 + r / G, head = kvh * G + r % G;
-      __nv_bfloat16* dst = p.out + ((int64_t)tok * H + head) * D;
+      __nv_bfloat16* dst = p.out + ((int64_t)tok * H + head) * D + half * HD;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 16) {
+      for (int c = 0; c < HD; c += 16) {
         uint32_t o[16];
         __syncwarp();
-        tmem_ld16(lane_addr + O_COL + c, o);
+        tmem_ld16(lane_addr + O_COL + half * HD + c, o);
         tmem_ld_wait();
         if (row_ok) {
           uint32_t w[8];
@@ -362,7 +394,7 @@ int launch_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& 
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  RB_LAUNCH("rb_attention_prefill_tc", (kernel), dim3(p.n_tiles, Kh), 192, smem, stream, tk, tv, p);
+  RB_LAUNCH("rb_attention_prefill_tc", (kernel), dim3(p.n_tiles, Kh), THREADS, smem, stream, tk, tv, p);
   return 0;
 }
 
@@ -374,7 +406,7 @@ int rb_attention_tc_error_flag(int* value, int reset) { return rb_file_error_fla
 RB_EXPORT int rb_attention_prefill_tc_supports(int H, int Kh, int D, int page_size) {
   if (Kh <= 0 || H % Kh) return 0;
   const int G = H / Kh;
-  return (D == 64 || D == 128) && page_size % TILE_KEYS == 0 && G <= ROWS;
+  return (D == 64 || D == 128) && page_size % PIECE == 0 && G <= ROWS;
 }
 
 // Prefill over the paged cache: tile i covers tile_ntok[i] <= 128/G tokens of one sequence starting
@@ -389,8 +421,8 @@ RB_EXPORT int rb_attention_prefill_tc(void* out, const void* q, const void* cach
              "rb_attention_prefill_tc: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
   CUtensorMap tk, tv;
   const long long rows = n_pages * Kh * page_size;
-  if (rb_get_tensor_map(&tk, cache_k, rows, D, D, TILE_KEYS) != 0) return -1;
-  if (rb_get_tensor_map(&tv, cache_v, rows, D, D, TILE_KEYS) != 0) return -1;
+  if (rb_get_tensor_map(&tk, cache_k, rows, D, D, PIECE) != 0) return -1;
+  if (rb_get_tensor_map(&tv, cache_v, rows, D, D, PIECE) != 0) return -1;
   TcAttnParams p;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
   p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size; p.n_kv_heads = Kh;
