@@ -109,8 +109,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
   rb_pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = p.n_tiles - 1 - (int)blockIdx.x;         // late tiles see the most keys: start them first
-  const int kvh = blockIdx.y;
+  // late tiles see the most keys: CTAs start in the order (tile descending, kv head), so the long
+  // ones of every kv head run first and the short ones fill the end
+  const int tile = p.n_tiles - 1 - (int)blockIdx.y;
+  const int kvh = blockIdx.x;
   const int G = p.G, H = p.H;
 
   if (threadIdx.x == 0) {
@@ -394,7 +396,7 @@ int launch_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& 
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  RB_LAUNCH("rb_attention_prefill_tc", (kernel), dim3(p.n_tiles, Kh), THREADS, smem, stream, tk, tv, p);
+  RB_LAUNCH("rb_attention_prefill_tc", (kernel), dim3(Kh, p.n_tiles), THREADS, smem, stream, tk, tv, p);
   return 0;
 }
 
@@ -417,6 +419,7 @@ RB_EXPORT int rb_attention_prefill_tc(void* out, const void* q, const void* cach
                                       const int* tile_ntok, int n_tiles, int H, int Kh, int D, float scale,
                                       int window, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  RB_REQUIRE(n_tiles <= 65535, "rb_attention_prefill_tc: %d tiles in one launch", n_tiles);
   RB_REQUIRE(rb_attention_prefill_tc_supports(H, Kh, D, page_size),
              "rb_attention_prefill_tc: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
   CUtensorMap tk, tv;
