@@ -13,7 +13,7 @@
 //   MMA:      S[128, 128] = Q[128, D] K[128, D]^T                   (bfloat16 in, float32 in TMEM)
 //   softmax:  read the row of S, mask by position (causal, window), running max and sum in
 //             float32, rescale the row of O in tensor memory when the max grew much, round P to
-//             bfloat16 into shared memory (the A operand of the next MMA)
+//             bfloat16 into tensor memory, in place of S (the A operand of the next MMA)
 //   MMA:      O[128, D] += P[128, 128] V[128, D]
 // S has two buffers: S of the next tile is issued before P V of this one, so the tensor cores work
 // while the softmax runs.  The score is (q.k)*scale with the scale folded into the exponent (base 2).
@@ -71,17 +71,27 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t saddr, uint32_t 
   return d;
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows, 16 bfloat16 = 8 columns of 32 bits per
+// row) is read from tensor memory instead of shared memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 template <int D>
 struct TcSmem {
   static constexpr int DB = D / 64;                         // 64-column blocks of a head
   static constexpr int BLOCK = ROWS * 128;                  // a block of [128 rows][128 bytes]
   static constexpr int Q_BYTES = BLOCK * DB;
   static constexpr int KV_TILE_BYTES = BLOCK * DB;          // 128 keys, DB blocks
-  static constexpr int P_BYTES = BLOCK * (TILE_KEYS / 64);  // 128 rows, two blocks of 64 keys
   static constexpr int OFF_K = Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
-  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_TILE_BYTES;
-  static constexpr int OFF_MAX = OFF_P + P_BYTES;           // float [2 tiles][2 halves][128 rows]
+  static constexpr int OFF_MAX = OFF_V + KV_STAGES * KV_TILE_BYTES;   // float [2 tiles][2 halves][128 rows]
   static constexpr int OFF_BAR = OFF_MAX + 2 * 2 * ROWS * 4;
   static constexpr int BYTES = OFF_BAR + 128;
 };
@@ -194,7 +204,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_mn(ROWS, TILE_KEYS, 0, 0);   // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = make_idesc_mn(ROWS, D, 0, 1);           // P (K-major) x V (D contiguous)
-      const uint32_t q_addr = smem_u32(smem), p_addr = smem_u32(smem + S::OFF_P);
+      const uint32_t q_addr = smem_u32(smem);
       bool ok = true;
       const int n_tiles = kt_end - kt_begin;
       // S of tile j goes to S buffer j & 1.  S(j+1) is issued before P V (j), so the tensor cores
@@ -229,10 +239,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         const uint32_t v_addr = smem_u32(smem + S::OFF_V + s * S::KV_TILE_BYTES);
 #pragma unroll
         for (int k16 = 0; k16 < TILE_KEYS / 16; ++k16) {
-          // A: 16 keys of P = 32 bytes along K inside the 64-key block k16 / 4;
+          // A: 16 keys of P = 8 columns of tensor memory, in place of the S buffer of this tile;
           // B: 16 key rows of V (2048 bytes further per step), all D columns: 64-column blocks S::BLOCK apart
-          umma_bf16(tmem_base + O_COL, smem_desc_sw128(p_addr + (k16 / 4) * S::BLOCK) + (uint64_t)((k16 % 4) * 32 >> 4),
-                    smem_desc_sw128_mn(v_addr + k16 * 2048, S::BLOCK), idesc_o, (j > 0 || k16 > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem_base + O_COL, tmem_base + (uint32_t)((j & 1) * TILE_KEYS + k16 * 8),
+                       smem_desc_sw128_mn(v_addr + k16 * 2048, S::BLOCK), idesc_o, (j > 0 || k16 > 0) ? 1u : 0u);
         }
         tcgen05_commit(&v_empty[s]);
         tcgen05_commit(pv_done);
@@ -272,19 +282,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // diagonal and at the window's edge)
       const bool whole = kt * TILE_KEYS + TILE_KEYS - 1 <= pos0 &&
                          (p.window <= 0 || kt * TILE_KEYS >= max(0, key_hi - p.window + 1));
-      float m_half = -INFINITY;
+      float m_half;
       if (whole) {
+        float t0 = sv[0], t1 = sv[1], t2 = sv[2], t3 = sv[3];          // four chains, not one of 64
 #pragma unroll
-        for (int c = 0; c < HK; ++c) m_half = fmaxf(m_half, sv[c]);
-        m_half *= p.scale_log2;                              // the scale is positive
-      } else {
-#pragma unroll
-        for (int c = 0; c < HK; ++c) {
-          const int key = key_base + c;
-          const bool allowed = row_ok && key <= row_pos && key >= row_lo;
-          sv[c] = allowed ? sv[c] : -INFINITY;
-          m_half = fmaxf(m_half, sv[c] * p.scale_log2);
+        for (int c = 4; c < HK; c += 4) {
+          t0 = fmaxf(t0, sv[c]); t1 = fmaxf(t1, sv[c + 1]); t2 = fmaxf(t2, sv[c + 2]); t3 = fmaxf(t3, sv[c + 3]);
         }
+        m_half = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * p.scale_log2;   // the scale is positive
+      } else {
+        float t0 = -INFINITY, t1 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < HK; c += 2) {
+          const int key = key_base + c;
+          sv[c] = (row_ok && key <= row_pos && key >= row_lo) ? sv[c] : -INFINITY;
+          sv[c + 1] = (row_ok && key + 1 <= row_pos && key + 1 >= row_lo) ? sv[c + 1] : -INFINITY;
+          t0 = fmaxf(t0, sv[c]); t1 = fmaxf(t1, sv[c + 1]);
+        }
+        m_half = fmaxf(t0, t1) * p.scale_log2;
       }
       // the row's max over both halves
       float* mx = row_max + (j & 1) * 2 * ROWS;
@@ -302,46 +317,49 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       uint32_t pw[HK / 2];
       {
         const float neg_m = -m_use;
-        float sum = 0.f;
+        float sum = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;           // four chains
 #pragma unroll
-        for (int i = 0; i < HK / 2; ++i) {
+        for (int i = 0; i < HK / 2; i += 2) {
           // one multiply-add and one exponential per value; 2^(-inf) = 0 for masked keys
           const float p0 = fast_exp2(fmaf(sv[2 * i], p.scale_log2, neg_m));
           const float p1 = fast_exp2(fmaf(sv[2 * i + 1], p.scale_log2, neg_m));
-          sum += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          pw[i] = *reinterpret_cast<uint32_t*>(&h);
+          const float p2 = fast_exp2(fmaf(sv[2 * i + 2], p.scale_log2, neg_m));
+          const float p3 = fast_exp2(fmaf(sv[2 * i + 3], p.scale_log2, neg_m));
+          sum += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+          pw[i] = *reinterpret_cast<uint32_t*>(&h0);
+          pw[i + 1] = *reinterpret_cast<uint32_t*>(&h1);
         }
+        sum = (sum + sum1) + (sum2 + sum3);
         l_run = l_run * corr + sum;
       }
       m_run = m_next;
-      // P V of the tile before must be complete before O is rescaled and before P is overwritten
-      if (j > 0) {
+      // P goes to tensor memory in place of this tile's S buffer (both threads of the row have
+      // their S values in registers: they passed the barrier above).  The last reader of that
+      // buffer, P V of tile j-2, is complete, since S of this tile was issued after it.  Only a
+      // rescale of O has to wait, for P V of tile j-1.
+      const bool rescale = j > 0 && __any_sync(0xffffffffu, moved);   // per warp: tensor-memory accesses are warp-wide
+      if (rescale) {
         ok = !failed;
         if (ok && lane == 0) ok = mbar_wait(pv_done, (j - 1) & 1, 11);
         ok = __shfl_sync(0xffffffffu, ok, 0);
         failed |= !ok;
         tcgen05_fence_after();
-        // decided per warp: the tensor-memory instructions are executed by whole warps
-        if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 16) {
-            uint32_t o[16];
-            tmem_ld16(lane_addr + O_COL + half * HD + c, o);
-            tmem_ld_wait();
+        for (int c = 0; c < HD; c += 16) {
+          uint32_t o[16];
+          tmem_ld16(lane_addr + O_COL + half * HD + c, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-            tmem_st16(lane_addr + O_COL + half * HD + c, o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st16(lane_addr + O_COL + half * HD + c, o);
         }
       }
-      uint8_t* prow = smem + S::OFF_P + half * S::BLOCK + r * 128;     // this half's 64 keys are one 128-byte row
+      // 64 keys of this row = 32 columns of two bfloat16 each, at columns half*32 of the buffer
+      const uint32_t p_addr = lane_addr + (uint32_t)((j & 1) * TILE_KEYS + half * (HK / 2));
 #pragma unroll
-      for (int c8 = 0; c8 < HK / 8; ++c8)
-        *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) =
-            make_uint4(pw[4 * c8], pw[4 * c8 + 1], pw[4 * c8 + 2], pw[4 * c8 + 3]);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      for (int c = 0; c < HK / 2; c += 16) tmem_st16(p_addr + c, pw + c);
+      tmem_st_wait();
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
