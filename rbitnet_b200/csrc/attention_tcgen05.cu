@@ -87,9 +87,8 @@ template <int D>
 struct TcSmem {
   static constexpr int DB = D / 64;                         // 64-column blocks of a head
   static constexpr int BLOCK = ROWS * 128;                  // a block of [128 rows][128 bytes]
-  static constexpr int Q_BYTES = BLOCK * DB;
   static constexpr int KV_TILE_BYTES = BLOCK * DB;          // 128 keys, DB blocks
-  static constexpr int OFF_K = Q_BYTES;
+  static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE_BYTES;
   static constexpr int OFF_MAX = OFF_V + KV_STAGES * KV_TILE_BYTES;   // float [2 tiles][2 halves][128 rows]
   static constexpr int OFF_BAR = OFF_MAX + 2 * 2 * ROWS * 4;
@@ -101,9 +100,11 @@ __global__ void __launch_bounds__(THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, TcAttnParams p) {
   using S = TcSmem<D>;
   constexpr int DB = S::DB;
-  constexpr int O_COL = 2 * TILE_KEYS;                      // tensor memory: two S buffers in columns [0,256), O in [256, 256+D)
+  // tensor memory: two S buffers in columns [0,256), O in [256, 256+D), Q (two bfloat16 a column) after it
+  constexpr int O_COL = 2 * TILE_KEYS;
+  constexpr int Q_COL = O_COL + D;
   constexpr int TMEM_COLS = 512;
-  static_assert(2 * TILE_KEYS + D <= 512, "tensor memory columns");
+  static_assert(2 * TILE_KEYS + D + D / 2 <= 512, "tensor memory columns");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::OFF_BAR);
   uint64_t* k_full = bars;                   // [2] keys of a tile have landed
@@ -152,22 +153,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   const int kt_begin = key_lo / TILE_KEYS, kt_end = key_hi / TILE_KEYS + 1;
   rb_pdl_wait();                                           // q and the cache come from earlier kernels
 
-  // ---- Q rows into shared memory, swizzled as the K-major A operand (rows beyond n_rows are zero)
-  for (int idx = threadIdx.x; idx < ROWS * (D / 8); idx += blockDim.x) {
-    const int r = idx / (D / 8), c8 = idx % (D / 8);       // 8 values = 16 bytes
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < n_rows) {
-      const int tok = tok0 + r / G, head = kvh * G + r % G;
-      v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + c8 * 8);
-    }
-    const int blk = c8 / 8, col = (c8 % 8) * 8;
-    *reinterpret_cast<uint4*>(smem + blk * S::BLOCK + sw128_offset(r, col)) = v;
-  }
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+
+  // ---- Q rows into tensor memory: the A operand of S = Q K^T is read from there, so that the
+  // MMAs fetch only K from shared memory.  Row r lives in lane r, two bfloat16 per column; the two
+  // softmax threads of a row write half of it each (rows beyond n_rows are zero).
+  if (warp >= 2) {
+    const int quarter = warp & 3, half = (warp - 2) >> 2, r = quarter * 32 + lane;
+    uint32_t w[D / 4];                                      // D/2 values = D/4 columns
+    if (r < n_rows) {
+      const int tok = tok0 + r / G, head = kvh * G + r % G;
+      const uint4* src = reinterpret_cast<const uint4*>(p.q + ((int64_t)tok * H + head) * D + half * (D / 2));
+#pragma unroll
+      for (int i = 0; i < D / 16; ++i) {
+        const uint4 v = src[i];
+        w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < D / 4; ++i) w[i] = 0u;
+    }
+    const uint32_t q_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(Q_COL + half * (D / 4));
+#pragma unroll
+    for (int c = 0; c < D / 4; c += 16) tmem_st16(q_addr + c, w + c);
+    tmem_st_wait();
+  }
+  if (warp >= 1) {                                         // the MMA warp waits for Q; the loader does not
+    tcgen05_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(THREADS - 32) : "memory");
+    tcgen05_fence_after();
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA loader
@@ -204,7 +222,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_mn(ROWS, TILE_KEYS, 0, 0);   // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = make_idesc_mn(ROWS, D, 0, 1);           // P (K-major) x V (D contiguous)
-      const uint32_t q_addr = smem_u32(smem);
       bool ok = true;
       const int n_tiles = kt_end - kt_begin;
       // S of tile j goes to S buffer j & 1.  S(j+1) is issued before P V (j), so the tensor cores
@@ -219,8 +236,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             const uint64_t koff = (uint64_t)(k4 * 32 >> 4);
-            umma_bf16(tmem_base + (uint32_t)((j & 1) * TILE_KEYS), smem_desc_sw128(q_addr + b * S::BLOCK) + koff,
-                      smem_desc_sw128(k_addr + b * S::BLOCK) + koff, idesc_s, (b > 0 || k4 > 0) ? 1u : 0u);
+            // A: 16 values of Q = 8 columns of tensor memory; B: the keys' 16 values of block b
+            umma_bf16_ts(tmem_base + (uint32_t)((j & 1) * TILE_KEYS), tmem_base + (uint32_t)(Q_COL + b * 32 + k4 * 8),
+                         smem_desc_sw128(k_addr + b * S::BLOCK) + koff, idesc_s, (b > 0 || k4 > 0) ? 1u : 0u);
           }
         tcgen05_commit(&s_full[j & 1]);
         tcgen05_commit(&k_empty[s]);
