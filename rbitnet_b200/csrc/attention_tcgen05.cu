@@ -58,6 +58,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Packed float32 pairs (one instruction for two values) and the three-input maximum of sm_100.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // MN-major operand (the contiguous dimension is M or N), 128-byte swizzle: 64 contiguous elements
 // per row of 128 bytes, eight K rows per group of 1024 bytes; `lbo` is the distance between
 // 64-element blocks along M/N.
@@ -302,11 +327,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                          (p.window <= 0 || kt * TILE_KEYS >= max(0, key_hi - p.window + 1));
       float m_half;
       if (whole) {
-        float t0 = sv[0], t1 = sv[1], t2 = sv[2], t3 = sv[3];          // four chains, not one of 64
+        float t0 = sv[0], t1 = sv[1], t2 = sv[2], t3 = sv[3];          // four chains of three-input maxima
 #pragma unroll
-        for (int c = 4; c < HK; c += 4) {
-          t0 = fmaxf(t0, sv[c]); t1 = fmaxf(t1, sv[c + 1]); t2 = fmaxf(t2, sv[c + 2]); t3 = fmaxf(t3, sv[c + 3]);
+        for (int c = 4; c + 8 <= HK; c += 8) {
+          t0 = max3(t0, sv[c], sv[c + 1]); t1 = max3(t1, sv[c + 2], sv[c + 3]);
+          t2 = max3(t2, sv[c + 4], sv[c + 5]); t3 = max3(t3, sv[c + 6], sv[c + 7]);
         }
+        t0 = max3(t0, sv[HK - 4], sv[HK - 3]); t1 = max3(t1, sv[HK - 2], sv[HK - 1]);
         m_half = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3)) * p.scale_log2;   // the scale is positive
       } else {
         float t0 = -INFINITY, t1 = -INFINITY;
@@ -334,21 +361,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
       // P = 2^(S*scale - m), rounded to bfloat16, kept in registers until the P buffer is free
       uint32_t pw[HK / 2];
       {
-        const float neg_m = -m_use;
-        float sum = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;           // four chains
+        // packed pairs: one multiply-add and one add per two values, one exponential per value;
+        // 2^(-inf) = 0 for masked keys
+        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_use, -m_use);
+        uint64_t acc_a = pack2(0.f, 0.f), acc_b = acc_a;                 // four chains in two registers pairs
 #pragma unroll
         for (int i = 0; i < HK / 2; i += 2) {
-          // one multiply-add and one exponential per value; 2^(-inf) = 0 for masked keys
-          const float p0 = fast_exp2(fmaf(sv[2 * i], p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(sv[2 * i + 1], p.scale_log2, neg_m));
-          const float p2 = fast_exp2(fmaf(sv[2 * i + 2], p.scale_log2, neg_m));
-          const float p3 = fast_exp2(fmaf(sv[2 * i + 3], p.scale_log2, neg_m));
-          sum += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          float x0, x1, x2, x3;
+          unpack2(fma2(pack2(sv[2 * i], sv[2 * i + 1]), scale2, neg_m2), x0, x1);
+          unpack2(fma2(pack2(sv[2 * i + 2], sv[2 * i + 3]), scale2, neg_m2), x2, x3);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+          acc_a = add2(acc_a, pack2(p0, p1));
+          acc_b = add2(acc_b, pack2(p2, p3));
           __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
           pw[i] = *reinterpret_cast<uint32_t*>(&h0);
           pw[i + 1] = *reinterpret_cast<uint32_t*>(&h1);
         }
-        sum = (sum + sum1) + (sum2 + sum3);
+        float s0, s1, s2, s3;
+        unpack2(acc_a, s0, s1);
+        unpack2(acc_b, s2, s3);
+        const float sum = (s0 + s1) + (s2 + s3);
         l_run = l_run * corr + sum;
       }
       m_run = m_next;
