@@ -431,33 +431,41 @@ RB_EXPORT int rb_add_partials(float* x, const float* partials, int n_partials, i
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// out[t, j] = silu(gu[t, j]) * gu[t, F + j], silu(v) = v / (1 + exp(-v)), in float32.
+// out[t, j] = silu(gate[t, j]) * up[t, j], silu(v) = v / (1 + exp(-v)), in float32.
 // crates/bitnet-core/src/llama/model.rs:116-120, 297-302
+// block == 0: a row of gu is [gate (F) | up (F)].  block == B > 0: it is made of groups of 2B
+// values, B of gate followed by the B of up for the same features (the row order the tensor-core
+// gated product wants of its weights); `ld` is the row length of gu.
 template <typename T, typename TI>
-__global__ void silu_mul_kernel(T* __restrict__ out, const TI* __restrict__ gu, int64_t n, int F) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const TI* __restrict__ gu, int64_t n, int F, int64_t ld, int block) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t t = i / F;
     const int j = (int)(i % F);
-    const float g = rb_to_float<TI>(gu[t * 2 * F + j]);
-    const float u = rb_to_float<TI>(gu[t * 2 * F + F + j]);
+    const int64_t at_g = block > 0 ? (int64_t)(j / block) * 2 * block + j % block : j;
+    const int64_t at_u = block > 0 ? at_g + block : (int64_t)F + j;
+    const float g = rb_to_float<TI>(gu[t * ld + at_g]);
+    const float u = rb_to_float<TI>(gu[t * ld + at_u]);
     out[i] = rb_from_float<T>(g / (1.0f + expf(-g)) * u);
   }
 }
 
 // in_dtype: dtype of gate_up (the output dtype, or RB_F32 for a bfloat16 output).
-RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int in_dtype, int T, int F, cudaStream_t stream) {
+RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int in_dtype, int T, int F, int64_t ld, int block,
+                          cudaStream_t stream) {
   if (T == 0) return 0;
+  RB_REQUIRE(block >= 0 && (block == 0 ? ld >= 2 * (int64_t)F : ld >= ((int64_t)(F + block - 1) / block) * 2 * block),
+             "rb_silu_mul: rows of %lld values do not hold %d features in blocks of %d", (long long)ld, F, block);
   const int64_t n = (int64_t)T * F;
   const int threads = 256;
   const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
   if (dtype == RB_F32 && in_dtype == RB_F32)
-    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<float, float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F);
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<float, float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F, ld, block);
   else if (dtype == RB_BF16 && in_dtype == RB_BF16)
-    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, F);
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16, __nv_bfloat16>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, F, ld, block);
   else if (dtype == RB_BF16 && in_dtype == RB_F32)
-    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16, float>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const float*)gate_up, n, F);
+    RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<__nv_bfloat16, float>), blocks, threads, 0, stream, (__nv_bfloat16*)out, (const float*)gate_up, n, F, ld, block);
   else
     RB_FAIL("rb_silu_mul: unsupported dtypes %d <- %d", dtype, in_dtype);
   return 0;

@@ -15,7 +15,9 @@
 //
 // Epilogues: plain store (bfloat16 or float32), add into a float32 matrix (the residual stream,
 // crates/bitnet-core/src/llama/model.rs:291-294, :303-306), float32 slices of a split product,
-// and SiLU(gate)*up from two accumulators (model.rs:297-302).
+// and SiLU(gate)*up (model.rs:297-302) from ONE accumulator: the caller interleaves the rows of the
+// gate and up matrices in blocks of 16, so that each warp of the epilogue holds 16 gate rows in its
+// lower lanes and the 16 up rows of the same features in its upper lanes, and a shuffle pairs them.
 //
 // Every wait on an mbarrier is bounded: after about two seconds the waiting thread records an
 // error code in a device word and the CTA leaves through the common exit, freeing its tensor
@@ -50,7 +52,7 @@ struct GemmParams {
   int n_tokens;       // rows of X
   int n_out;          // rows of W that produce output columns (the gate half for EPI_GATED)
   int K;
-  int up_row0;        // EPI_GATED: first row of the up matrix inside W
+  int n_features;     // EPI_GATED: output columns (W holds 32 rows, 16 gate and 16 up, per 16 of them)
   int kb_per_split;   // 64-wide k blocks per split
   int n_t_tiles;      // token tiles
   int splits;         // parts of K
@@ -76,10 +78,9 @@ __device__ __forceinline__ void cluster_sync_all() {
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 __global__ void __launch_bounds__(192, MINB)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
-  constexpr bool GATED = EPI == EPI_GATED;
   constexpr int X_TILE_BYTES = BN * BK * 2;
-  constexpr int STAGE_BYTES = W_TILE_BYTES * (GATED ? 2 : 1) + X_TILE_BYTES;
-  constexpr int ACC_COLS = BN * (GATED ? 2 : 1);
+  constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
+  constexpr int ACC_COLS = BN;
   constexpr int NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;
   constexpr int WANT_COLS = NBUF * ACC_COLS;
   constexpr int TMEM_COLS = WANT_COLS <= 32 ? 32 : (WANT_COLS <= 64 ? 64 : (WANT_COLS <= 128 ? 128 : (WANT_COLS <= 256 ? 256 : 512)));
@@ -154,12 +155,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           mbar_expect_tx(&full_bar[i], STAGE_BYTES);
           const int k = (kb_begin + i) * BK;
           tma_load_2d(stage, &tmW, k, n0, &full_bar[i]);
-          if (GATED) tma_load_2d(stage + W_TILE_BYTES, &tmW, k, p.up_row0 + n0, &full_bar[i]);
         }
         rb_pdl_wait();
         for (int i = 0; i < early; ++i) {
           uint8_t* stage = smem + (size_t)i * STAGE_BYTES;
-          tma_load_2d(stage + W_TILE_BYTES * (GATED ? 2 : 1), &tmX, (kb_begin + i) * BK, t0, &full_bar[i]);
+          tma_load_2d(stage + W_TILE_BYTES, &tmX, (kb_begin + i) * BK, t0, &full_bar[i]);
         }
       }
       for (int item = first_item; item < p.n_items && ok; item += item_stride) {
@@ -176,8 +176,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           mbar_expect_tx(&full_bar[s], STAGE_BYTES);
           const int k = (kb_begin + i) * BK;
           tma_load_2d(stage, &tmW, k, n0, &full_bar[s]);
-          if (GATED) tma_load_2d(stage + W_TILE_BYTES, &tmW, k, p.up_row0 + n0, &full_bar[s]);
-          tma_load_2d(stage + W_TILE_BYTES * (GATED ? 2 : 1), &tmX, k, t0, &full_bar[s]);
+          tma_load_2d(stage + W_TILE_BYTES, &tmX, k, t0, &full_bar[s]);
         }
       }
     }
@@ -203,16 +202,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tcgen05_fence_after();
           const uint32_t stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint64_t dw = smem_desc_sw128(stage);
-          const uint64_t dx = smem_desc_sw128(stage + W_TILE_BYTES * (GATED ? 2 : 1));
+          const uint64_t dx = smem_desc_sw128(stage + W_TILE_BYTES);
 #pragma unroll
           for (int k4 = 0; k4 < BK / UMMA_K; ++k4) {
             const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
             const uint64_t koff = (uint64_t)(k4 * UMMA_K * 2 >> 4);
             umma_bf16(acc_addr, dw + koff, dx + koff, idesc, acc);
-            if (GATED) {
-              const uint64_t du = smem_desc_sw128(stage + W_TILE_BYTES);
-              umma_bf16(acc_addr + BN, du + koff, dx + koff, idesc, acc);
-            }
           }
           tcgen05_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
         }
@@ -259,16 +254,15 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         if (t0 + c >= p.n_tokens) break;
-        uint32_t r[16], u[16];
+        uint32_t r[16];
         __syncwarp();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * ACC_COLS + c);
         if (nkb > 0) {
           tmem_ld16(taddr, r);
-          if (GATED) tmem_ld16(taddr + BN, u);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { r[j] = 0u; u[j] = 0u; }
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
         // rows of this chunk that exist (none for a lane whose weight row is beyond the matrix);
         // no lane leaves the loop early: tcgen05.ld is executed by the whole warp
@@ -287,14 +281,23 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (j < t_left) dst[(int64_t)j * p.ldc] = __uint_as_float(r[j]);
+        } else if (EPI == EPI_GATED) {
+          // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features: feature
+          // (weight row block of 32) * 16 + lane.  Every lane takes part in the shuffles.
+          const int f = (n0 + quarter * 32) / 2 + lane;
+          const int f_left = (lane < 16 && f < p.n_features) ? p.n_tokens - (t0 + c) : 0;
+          OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g = __uint_as_float(r[j]);
+            const float up = __shfl_down_sync(0xffffffffu, g, 16);
+            if (j < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, g / (1.0f + expf(-g)) * up);
+          }
         } else {
           OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float v = __uint_as_float(r[j]);
-            if (EPI == EPI_GATED) v = v / (1.0f + expf(-v)) * __uint_as_float(u[j]);
-            if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
-          }
+          for (int j = 0; j < 16; ++j)
+            if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]));
         }
       }
       // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
@@ -305,10 +308,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   }
   if (p.cluster) {
     // every thread of every CTA of the cluster arrives here, also after a wait that gave up
-    static_assert(EPI == EPI_GATED || BN * BM * 4 <= STAGES * STAGE_BYTES, "the ring holds one accumulator");
+    static_assert(BN * BM * 4 <= STAGES * STAGE_BYTES, "the ring holds one accumulator");
     __syncwarp();
     cluster_sync_all();
-    if (EPI != EPI_GATED && warp >= 2 && first_item < p.n_items) {
+    if (EPI != EPI_GATED && warp >= 2 && first_item < p.n_items) {   // (the gated product is never split)
       // every CTA of the cluster adds up a share of the token columns (column c belongs to rank
       // c mod splits), reading all parts of a column in split order through distributed shared memory
       int n0, t0, kb_begin, nkb, split;
@@ -446,7 +449,7 @@ int sm_count() {
 
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
-  constexpr int stage_bytes = W_TILE_BYTES * (EPI == EPI_GATED ? 2 : 1) + BN * BK * 2;
+  constexpr int stage_bytes = W_TILE_BYTES + BN * BK * 2;
   constexpr int smem = STAGES * stage_bytes + 1024;
   static_assert(smem * MINB <= 227 * 1024, "shared memory");
   auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT, MINB>;
@@ -483,13 +486,12 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
 
 template <int EPI, typename OutT>
 int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
-  constexpr bool G = EPI == EPI_GATED;
   switch (bn) {
-    case 16: return launch<16, 5, EPI, OutT, G ? 1 : 2>(tw, tx, p, stream);
-    case 32: return launch<32, 5, EPI, OutT, G ? 1 : 2>(tw, tx, p, stream);
-    case 64: return launch<64, G ? 5 : 4, EPI, OutT, G ? 1 : 2>(tw, tx, p, stream);
-    case 128: return launch<128, G ? 4 : 6, EPI, OutT, 1>(tw, tx, p, stream);
-    case 256: return launch<256, G ? 3 : 4, EPI, OutT, 1>(tw, tx, p, stream);
+    case 16: return launch<16, 5, EPI, OutT, 2>(tw, tx, p, stream);
+    case 32: return launch<32, 5, EPI, OutT, 2>(tw, tx, p, stream);
+    case 64: return launch<64, 4, EPI, OutT, 2>(tw, tx, p, stream);
+    case 128: return launch<128, 6, EPI, OutT, 1>(tw, tx, p, stream);
+    case 256: return launch<256, 4, EPI, OutT, 1>(tw, tx, p, stream);
   }
   RB_FAIL("rb_gemm_tc: no kernel for a token tile of %d", bn);
 }
@@ -513,11 +515,12 @@ RB_EXPORT int rb_read_error_flag(int* value, int reset) {
 //   (epilogues 0 and 1 with 2..8 splits: the CTAs of a tile form a cluster and the first adds
 //    the parts up through distributed shared memory, in split order; token tile <= 64)
 //   epilogue 2: C is [splits][tokens][ldc] float32 slices; slice z holds the product over its part of K
-//   epilogue 3: W = [gate ; up] with up starting at row up_row0; C[tokens, n_out] = silu(gate)*up
+//   epilogue 3: W holds, for every 16 output features, 16 gate rows followed by their 16 up rows
+//               (n_out rows in all, a multiple of 32); C[tokens, n_features] = silu(gate)*up
 // Requirements (refused otherwise): bfloat16 X and W, K a multiple of 8, row strides multiples of 8
 // elements, 16-byte aligned bases.
 RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
-                         int64_t ldw, int w_rows, int n_out, int K, int epilogue, int up_row0, int splits,
+                         int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
                          int token_tile, cudaStream_t stream) {
   if (n_tokens == 0 || n_out == 0) return 0;
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
@@ -529,15 +532,14 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
   int bn = token_tile;
   if (bn == 0) bn = n_tokens <= 16 ? 16 : n_tokens <= 32 ? 32 : n_tokens <= 64 ? 64 : n_tokens <= 128 ? 128 : 256;
-  // the gated product holds two accumulators per item: with a 128-token tile two items fit in
-  // tensor memory and the epilogue of one overlaps the products of the next
-  if (token_tile == 0 && epilogue == EPI_GATED && bn == 256) bn = 128;
+  RB_REQUIRE(epilogue != EPI_GATED || (n_out % 32 == 0 && n_features > 0 && n_features <= n_out / 2),
+             "rb_gemm_tc: the gated product wants rows in blocks of 32 (%d rows, %d features)", n_out, n_features);
   CUtensorMap tw, tx;
   if (rb_get_tensor_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
   if (rb_get_tensor_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
   GemmParams p;
   p.C = C; p.ldc = ldc; p.slice = (int64_t)n_tokens * ldc; p.n_tokens = n_tokens; p.n_out = n_out; p.K = K;
-  p.up_row0 = up_row0; p.kb_per_split = (nkb + splits - 1) / splits;
+  p.n_features = n_features; p.kb_per_split = (nkb + splits - 1) / splits;
   RB_REQUIRE((int64_t)(splits - 1) * p.kb_per_split < nkb, "rb_gemm_tc: a split of K would be empty");
   const int n_w_tiles = (n_out + BM - 1) / BM, n_t_tiles = (n_tokens + bn - 1) / bn;
   const long long items = (long long)n_w_tiles * n_t_tiles * splits;

@@ -36,10 +36,15 @@ class LinearWeight:
 
 @dataclass
 class GateUpWeight:
-    """Gate and up matrices made ready for ``gated_linear``: rows [gate | up]."""
+    """Gate and up matrices made ready for ``gated_linear``.
+
+    ``block == 0``: rows [gate | up].  ``block == 16``: for every 16 output features, their 16 gate
+    rows followed by their 16 up rows (the last group padded with zero rows), which is how the
+    tensor-core product pairs gate and up inside one warp of its epilogue."""
     w: torch.Tensor
     inner: int
     n_in: int
+    block: int = 0
 
 
 class CudaOps:
@@ -93,8 +98,19 @@ class CudaOps:
         return LinearWeight(w, w.shape[0], w.shape[1])
 
     def prepare_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> GateUpWeight:
-        w = torch.cat([self.to_compute(gate), self.to_compute(up)], dim=0).contiguous()
-        return GateUpWeight(w, gate.shape[0], gate.shape[1])
+        gate, up = self.to_compute(gate), self.to_compute(up)
+        F, K = gate.shape
+        if self.dtype == torch.bfloat16 and K % 8 == 0:
+            # the layout of the tensor-core gated product: groups of 16 gate rows and their 16 up rows
+            groups = -(-F // 16)
+            w = torch.zeros((groups, 2, 16, K), dtype=gate.dtype, device=gate.device)
+            for half, m in ((0, gate), (1, up)):
+                whole = F // 16
+                w[:whole, half] = m[:whole * 16].view(whole, 16, K)
+                if F % 16:
+                    w[whole, half, :F % 16] = m[whole * 16:]
+            return GateUpWeight(w.view(groups * 32, K), F, K, 16)
+        return GateUpWeight(torch.cat([gate, up], dim=0).contiguous(), F, K, 0)
 
     # ------------------------------------------------------------------ ops
     def embed(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -165,23 +181,17 @@ class CudaOps:
         """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype."""
         T = x.shape[0]
         out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
-        if self._tensor_core_ok(x, weight.w) and T <= 64:
-            # few tokens: the product is bound by reading W, and twice as many plain tiles keep more
-            # SMs streaming than the two-accumulator tiles; gate and up stay float32 until activated
-            gu = torch.empty((T, 2 * weight.inner), dtype=torch.float32, device=self.device)
-            self.lib.call("rb_gemm_tc", _ptr(gu), gu.stride(0), F32, _ptr(x), x.stride(0), T, _ptr(weight.w),
-                          weight.w.stride(0), 2 * weight.inner, 2 * weight.inner, weight.n_in, 0, 0, 1, 0,
-                          self._stream())
-            self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, F32, T, weight.inner, self._stream())
-            return out
-        if self._tensor_core_ok(x, weight.w):
-            # two accumulators per tile; the activation and the product happen on the way out
+        rows = weight.w.shape[0]
+        if weight.block == 16 and self._tensor_core_ok(x, weight.w):
+            # one accumulator per tile; gate and up of a feature meet in the epilogue, and the
+            # activation and the product happen on the way out
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), T,
-                          _ptr(weight.w), weight.w.stride(0), 2 * weight.inner, weight.inner, weight.n_in,
-                          3, weight.inner, 1, 0, self._stream())
+                          _ptr(weight.w), weight.w.stride(0), rows, rows, weight.n_in, 3, weight.inner, 1, 0,
+                          self._stream())
             return out
-        gu = self.linear(x, LinearWeight(weight.w, 2 * weight.inner, weight.n_in))
-        self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, self.code, T, weight.inner, self._stream())
+        gu = self.linear(x, LinearWeight(weight.w, rows, weight.n_in))
+        self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, self.code, T, weight.inner, gu.stride(0),
+                      weight.block, self._stream())
         return out
 
     def rotate_append(self, qkv: torch.Tensor, rotary, meta, view, n_heads: int) -> torch.Tensor:
