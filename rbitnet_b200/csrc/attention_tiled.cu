@@ -343,19 +343,39 @@ __global__ void attn_combine_kernel(__nv_bfloat16* __restrict__ out, const float
                                     const float* __restrict__ part_ml, int n_splits, int D) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
+  // One thread per output value.  The parts are taken 16 at a time with all their loads issued
+  // before the first use, so that a merge of up to 16 parts waits for memory once.
   const int64_t th = blockIdx.x;   // token * H + head
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(th * n_splits + s) * 2]);
-  const float mu = m == -INFINITY ? 0.f : m;
-  float l = 0.f;
-  for (int s = 0; s < n_splits; ++s) l += part_ml[(th * n_splits + s) * 2 + 1] * exp2f(part_ml[(th * n_splits + s) * 2] - mu);
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < n_splits; ++s)
-      acc += part_o[(th * n_splits + s) * D + d] * exp2f(part_ml[(th * n_splits + s) * 2] - mu);
-    out[th * D + d] = __float2bfloat16_rn(acc * inv);
+  const int d = threadIdx.x;
+  if (d >= D) return;
+  const float* ml = part_ml + th * n_splits * 2;
+  const float* po = part_o + th * n_splits * D + d;
+  float m_run = -INFINITY, l_run = 0.f, acc = 0.f;
+  for (int s0 = 0; s0 < n_splits; s0 += 16) {
+    float m[16], l[16], o[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const bool have = s0 + i < n_splits;
+      m[i] = have ? ml[(s0 + i) * 2] : -INFINITY;
+      l[i] = have ? ml[(s0 + i) * 2 + 1] : 0.f;
+      o[i] = have ? po[(int64_t)(s0 + i) * D] : 0.f;
+    }
+    float mg = m_run;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mg = fmaxf(mg, m[i]);
+    const float mu = mg == -INFINITY ? 0.f : mg;
+    const float keep = exp2f(m_run - mu);          // 0 for the first group
+    l_run *= keep;
+    acc *= keep;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float w = exp2f(m[i] - mu);            // 0 for a part without keys and beyond the last part
+      l_run += l[i] * w;
+      acc += o[i] * w;
+    }
+    m_run = mg;
   }
+  out[th * D + d] = __float2bfloat16_rn(l_run > 0.f ? acc / l_run : 0.f);
 }
 
 template <int D, bool DECODE>
@@ -442,7 +462,7 @@ RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k,
   p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
   if (launch_d<true>(D, p, dim3(B, Kh, n_splits), stream) != 0) return -1;
   if (n_splits > 1) {
-    RB_LAUNCH("attn_combine_kernel", (attn_combine_kernel), B * H, D >= 128 ? 128 : 64, 0, stream, (__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
+    RB_LAUNCH("attn_combine_kernel", (attn_combine_kernel), B * H, (D + 31) / 32 * 32, 0, stream, (__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
     RB_CHECK_LAUNCH("rb_attention_combine");
   }
   return 0;

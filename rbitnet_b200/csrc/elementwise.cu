@@ -38,23 +38,44 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
                              const int* __restrict__ ids, int E, int V) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
+  // four values per thread and the whole row in flight at once: the rows come from anywhere in a
+  // table far larger than L2, and a loop over the row would wait for memory once per turn
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
   const TW* row = table + (int64_t)(ok ? id : 0) * E;
   float* o = out + (int64_t)t * E;
-  for (int j = threadIdx.x; j < E; j += blockDim.x) o[j] = ok ? rb_to_float<TW>(row[j]) : 0.f;
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (j >= E) return;
+  if ((E & 3) == 0) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (ok) {
+      if constexpr (sizeof(TW) == 4) {
+        v = *reinterpret_cast<const float4*>(row + j);
+      } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(row + j);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        v = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+      }
+    }
+    *reinterpret_cast<float4*>(o + j) = v;
+  } else {
+    for (int i = j; i < min(E, j + 4); ++i) o[i] = ok ? rb_to_float<TW>(row[i]) : 0.f;
+  }
 }
 
 RB_EXPORT int rb_embed(float* out, const void* table, int table_dtype, const int* ids, int T, int E,
                        int V, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(T > 0 && E > 0 && V > 0, "rb_embed: bad sizes T=%d E=%d V=%d", T, E, V);
-  const int threads = E >= 1024 ? 256 : 128;
+  const int threads = 256;
+  const dim3 grid(T, (E + threads * 4 - 1) / (threads * 4));
+  RB_REQUIRE(grid.y <= 65535, "rb_embed: rows of %d values", E);
   if (table_dtype == RB_F32)
-    RB_LAUNCH("embed_kernel", (embed_kernel<float>), T, threads, 0, stream, out, (const float*)table, ids, E, V);
+    RB_LAUNCH("embed_kernel", (embed_kernel<float>), grid, threads, 0, stream, out, (const float*)table, ids, E, V);
   else if (table_dtype == RB_BF16)
-    RB_LAUNCH("embed_kernel", (embed_kernel<__nv_bfloat16>), T, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, E, V);
+    RB_LAUNCH("embed_kernel", (embed_kernel<__nv_bfloat16>), grid, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, E, V);
   else
     RB_FAIL("rb_embed: unknown dtype %d", table_dtype);
   RB_CHECK_LAUNCH("rb_embed");
@@ -476,15 +497,22 @@ __global__ void gather_rows_kernel(float* __restrict__ out, const float* __restr
                                    const int* __restrict__ rows, int E) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
+  // one element (or one group of four) per thread: the copies of a row are all in flight together
   const int r = blockIdx.x;
   const float* src = x + (int64_t)rows[r] * E;
   float* dst = out + (int64_t)r * E;
-  for (int j = threadIdx.x; j < E; j += blockDim.x) dst[j] = src[j];
+  const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if ((E & 3) == 0) {
+    if (j < E) *reinterpret_cast<float4*>(dst + j) = *reinterpret_cast<const float4*>(src + j);
+  } else {
+    for (int i = j; i < min(E, j + 4); ++i) dst[i] = src[i];
+  }
 }
 
 RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R, int E, cudaStream_t stream) {
   if (R == 0) return 0;
-  RB_LAUNCH("gather_rows_kernel", (gather_rows_kernel), R, 256, 0, stream, out, x, rows, E);
+  RB_REQUIRE(R <= 2147483647 && (E + 1023) / 1024 <= 65535, "rb_gather_rows: %d rows of %d", R, E);
+  RB_LAUNCH("gather_rows_kernel", (gather_rows_kernel), dim3(R, (E + 1023) / 1024), 256, 0, stream, out, x, rows, E);
   RB_CHECK_LAUNCH("rb_gather_rows");
   return 0;
 }

@@ -34,7 +34,7 @@ def test_extension_is_loaded_from_the_tree(ops16):
     assert os.path.basename(ops16.lib.path) in maps
 
 
-@pytest.mark.parametrize("V,E,T", [(257, 48, 5), (1000, 272, 33)])
+@pytest.mark.parametrize("V,E,T", [(257, 48, 5), (1000, 272, 33), (300, 4100, 7), (100, 50, 3), (64, 2049, 2)])
 def test_embed(ops32, ops16, V, E, T):
     g = torch.Generator(device="cuda").manual_seed(1)
     table = torch.randn(V, E, device="cuda", generator=g)
@@ -318,8 +318,9 @@ def test_sampling(ops32, V):
     assert ops32.sample(flat, one, torch.tensor([0.0, 0.99999994], device="cuda")).tolist() == [0, V - 1]
 
 
-def test_gather_rows(ops32):
-    x = torch.randn(20, 48, device="cuda")
+@pytest.mark.parametrize("E", [48, 50, 1028, 3001])
+def test_gather_rows(ops32, E):
+    x = torch.randn(20, E, device="cuda")
     rows = torch.tensor([19, 0, 7, 7], dtype=torch.int32, device="cuda")
     assert torch.equal(ops32.gather_rows(x, rows), x[rows.long()])
 
