@@ -282,16 +282,24 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int j = 0; j < 16; ++j)
             if (j < t_left) dst[(int64_t)j * p.ldc] = __uint_as_float(r[j]);
         } else if (EPI == EPI_GATED) {
-          // lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features: feature
-          // (weight row block of 32) * 16 + lane.  Every lane takes part in the shuffles.
-          const int f = (n0 + quarter * 32) / 2 + lane;
-          const int f_left = (lane < 16 && f < p.n_features) ? p.n_tokens - (t0 + c) : 0;
-          OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + f;
+          // Lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features (feature =
+          // (weight row block of 32) * 16 + lane % 16).  Columns are taken in pairs: the lower lanes
+          // finish the even token of a pair, the upper lanes the odd one, so that every lane does one
+          // activation per two columns.  Every lane takes part in the shuffles.
+          const bool low = lane < 16;
+          const int f = (n0 + quarter * 32) / 2 + (lane & 15);
+          const int f_left = f < p.n_features ? p.n_tokens - (t0 + c) : 0;
+          OutT* dst = (OutT*)p.C + (int64_t)(t0 + c + (low ? 0 : 1)) * p.ldc + f;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float g = __uint_as_float(r[j]);
-            const float up = __shfl_down_sync(0xffffffffu, g, 16);
-            if (j < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, g / (1.0f + expf(-g)) * up);
+          for (int j = 0; j < 16; j += 2) {
+            const float mine = __uint_as_float(low ? r[j] : r[j + 1]);       // gate (low) or up (high) of my token
+            const float send = __uint_as_float(low ? r[j + 1] : r[j]);       // what the partner needs
+            const float got = __shfl_xor_sync(0xffffffffu, send, 16);
+            const float g = low ? mine : got, up = low ? got : mine;
+            // silu(g) * up = g * up / (1 + e^-g), with the hardware's exponential and reciprocal: their
+            // error (a few units of float32) is far below the rounding to bfloat16 that follows
+            const float v = __fdividef(g, 1.0f + __expf(-g)) * up;
+            if (j + (low ? 0 : 1) < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
           }
         } else {
           OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
