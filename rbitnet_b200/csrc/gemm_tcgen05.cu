@@ -223,13 +223,24 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int n0, t0, kb_begin, nkb, split;
       item_of(item, n0, t0, kb_begin, nkb, split);
       const int b = li % NBUF;
+      const int n = n0 + quarter * 32 + lane;           // output column = weight row
+      const bool n_ok = n < p.n_out;
+      // EPI_ADD: the values to add to do not depend on the accumulator.  They are fetched one chunk
+      // ahead, the first chunk while the products of this item still run, so that the epilogue
+      // waits for memory once per item and not once per chunk.
+      float ahead[16];
+      auto fetch_old = [&](int c, float* into) {
+        const int left = n_ok ? p.n_tokens - (t0 + c) : 0;
+        const float* src = (const float*)p.C + (int64_t)(t0 + c) * p.ldc + n;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) into[j] = j < left ? src[(int64_t)j * p.ldc] : 0.f;
+      };
+      if (EPI == EPI_ADD && !p.cluster) fetch_old(0, ahead);
       bool ok = true;
       if (lane == 0) ok = mbar_wait(&accum_full[b], (li / NBUF) & 1, 3);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       tcgen05_fence_after();
-      const int n = n0 + quarter * 32 + lane;           // output column = weight row
-      const bool n_ok = n < p.n_out;
       if (p.cluster) {
         // this split's accumulator goes to shared memory (the stage ring is idle now: every MMA
         // that read it has completed); rank 0 adds the splits up after the cluster barrier below
@@ -268,11 +279,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // no lane leaves the loop early: tcgen05.ld is executed by the whole warp
         const int t_left = n_ok ? p.n_tokens - (t0 + c) : 0;
         if (EPI == EPI_ADD) {
-          // all loads first, then all stores: the read-modify-write of the 16 rows overlaps
           float* dst = (float*)p.C + (int64_t)(t0 + c) * p.ldc + n;
           float old[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) old[j] = j < t_left ? dst[(int64_t)j * p.ldc] : 0.f;
+          for (int j = 0; j < 16; ++j) old[j] = ahead[j];
+          if (c + 16 < BN) fetch_old(c + 16, ahead);       // the next chunk's loads are in flight during these stores
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]);
