@@ -278,6 +278,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1/64 points")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="'prefill': only the 2,048-token prefill, one short line (for profiling)")
+    ap.add_argument("--prefill-tokens", type=int, default=PROMPT_LEN,
+                    help="with --phase prefill: the prompt's length (up to 8,000), for profiling other lengths")
     ap.add_argument("--timeline", action="store_true",
                     help="print when each kernel of one decode step ran inside the captured graph, and exit")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
@@ -314,9 +316,10 @@ def main():
         print_timeline(engine, args.batch, PROMPT_LEN)
         return 0
     if args.phase == "prefill":
-        pf_ms = time_prefill(engine, PROMPT_LEN, reps=max(1, min(3, steps)))
-        print(json.dumps({"phase": "prefill", "tokens": PROMPT_LEN, "layers": args.layers, "ms": round(pf_ms, 3),
-                          "tokens_per_s": round(PROMPT_LEN / pf_ms * 1e3, 1)}))
+        n_tok = max(1, min(8000, args.prefill_tokens))
+        pf_ms = time_prefill(engine, n_tok, reps=max(1, min(3, steps)))
+        print(json.dumps({"phase": "prefill", "tokens": n_tok, "layers": args.layers, "ms": round(pf_ms, 3),
+                          "tokens_per_s": round(n_tok / pf_ms * 1e3, 1)}))
         return 0
 
     sampler = ClockSampler().start()
