@@ -329,6 +329,7 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
 // Many tokens, bfloat16 in and out, head_dim a multiple of 16: one block per token.  A thread owns
 // eight rotation pairs (the same eight in every head), computes their sines and cosines once,
 // and walks over the heads with 16-byte loads and stores; values are copied 16 bytes at a time.
+constexpr int ROWS_MAX_PAIRS = 256;      // head sizes up to 512 take the many-token kernel
 __global__ void __launch_bounds__(256) rotate_append_rows_kernel(
     __nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride,
     const float* __restrict__ inv_freq, const int* __restrict__ tok_pos, const int* __restrict__ tok_slot,
@@ -345,10 +346,14 @@ __global__ void __launch_bounds__(256) rotate_append_rows_kernel(
   const int n_rot = H + (write_kv ? Kh : 0);
   __nv_bfloat16* kdst = (__nv_bfloat16*)cache.k;
   __nv_bfloat16* vdst = (__nv_bfloat16*)cache.v;
+  // the token's D/2 sines and cosines, once per block
+  __shared__ float s_sn[ROWS_MAX_PAIRS], s_cs[ROWS_MAX_PAIRS];
+  for (int i = threadIdx.x; i < D / 2; i += blockDim.x) sincosf((float)pos * inv_freq[i], &s_sn[i], &s_cs[i]);
+  __syncthreads();
   if (lane < lanes) {
     float sn[8], cs[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sincosf((float)pos * inv_freq[grp * 8 + j], &sn[j], &cs[j]);
+    for (int j = 0; j < 8; ++j) { sn[j] = s_sn[grp * 8 + j]; cs[j] = s_cs[grp * 8 + j]; }
     // element offsets of the two 16-byte pieces this thread rotates in every head
     const int off_a = interleaved ? grp * 16 : grp * 8;
     const int off_b = interleaved ? grp * 16 + 8 : D / 2 + grp * 8;
@@ -412,7 +417,7 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   if (by > n_heads) by = n_heads;
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
-  if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 32 && D % 16 == 0 && D <= 256 * 16 &&
+  if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 32 && D % 16 == 0 && D <= 2 * ROWS_MAX_PAIRS &&
       qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)cache_k % 16 == 0) && ((uintptr_t)cache_v % 16 == 0)) {
     RB_LAUNCH("rotate_append_rows_kernel", (rotate_append_rows_kernel), T, 256, 0, stream, (__nv_bfloat16*)q_out,

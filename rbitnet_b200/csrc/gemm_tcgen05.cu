@@ -50,7 +50,7 @@ struct GemmParams {
   int64_t ldc;        // row stride of C in elements
   int64_t slice;      // elements between split slices (EPI_PARTIAL)
   int n_tokens;       // rows of X
-  int n_out;          // rows of W that produce output columns (the gate half for EPI_GATED)
+  int n_out;          // rows of W (for EPI_GATED: gate and up rows together)
   int K;
   int n_features;     // EPI_GATED: output columns (W holds 32 rows, 16 gate and 16 up, per 16 of them)
   int kb_per_split;   // 64-wide k blocks per split
