@@ -19,8 +19,11 @@
 // while the softmax runs.  The score is (q.k)*scale with the scale folded into the exponent (base 2).
 // crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound, P V), :102-114 (softmax).
 //
-// All operands are K-major with the 128-byte swizzle except V, whose tile [keys, D] has D
-// contiguous: it is the MN-major B operand of O += P V.  Every mbarrier wait is bounded.
+// The A operands of both products live in tensor memory: Q is written there once (two bfloat16 per
+// column), and P overwrites the S it was made from.  The products therefore read only K and V from
+// shared memory, which is what bounds N = 128 products whose operands both come from there.  K is
+// K-major with the 128-byte swizzle; V, whose tile [keys, D] has D contiguous, is the MN-major B
+// operand of O += P V.  Every mbarrier wait is bounded.
 #include "rb_tcgen05.cuh"
 
 namespace {
@@ -45,11 +48,6 @@ struct TcAttnParams {
   float scale_log2;
   int window;
 };
-
-// byte offset of element (row, col) in a K-major tile of 64 columns with the 128-byte swizzle
-__device__ __forceinline__ uint32_t sw128_offset(int row, int col) {
-  return (uint32_t)(row * 128 + ((((col >> 3) ^ (row & 7))) << 4) + (col & 7) * 2);
-}
 
 // 2^x for x <= 0 (and -inf -> 0) with the hardware approximation (relative error about 2^-22)
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -137,7 +135,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
   uint64_t* v_full = bars + 4;               // [2]
   uint64_t* v_empty = bars + 6;              // [2] P V of that tile is complete
   uint64_t* s_full = bars + 8;               // [2] one per S buffer
-  uint64_t* p_full = bars + 10;              // P of a tile is in shared memory (one arrival per softmax warp)
+  uint64_t* p_full = bars + 10;              // P of a tile is in tensor memory (one arrival per softmax warp)
   uint64_t* pv_done = bars + 11;             // P V of a tile is complete: O is consistent, the P buffer is free
   uint64_t* o_full = bars + 12;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 13);
@@ -274,7 +272,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
         if (j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
         const int s = j % KV_STAGES;
-        ok = mbar_wait(p_full, j & 1, 7);                    // P of this tile is in shared memory
+        ok = mbar_wait(p_full, j & 1, 7);                    // P of this tile is in tensor memory
         if (!ok) break;
         ok = mbar_wait(&v_full[s], (j / KV_STAGES) & 1, 6);
         if (!ok) break;

@@ -109,9 +109,10 @@ __global__ void __launch_bounds__(WARPS * 32) attn_tiled_kernel(AttnParams p) {
   const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;      // first key any row may see
   int kt_begin = key_lo / TILE_KEYS, kt_end = key_hi / TILE_KEYS + 1;
   if (DECODE && p.n_splits > 1) {
-    const int per = (kt_end - kt_begin + p.n_splits - 1) / p.n_splits;
-    kt_begin += blockIdx.z * per;
-    kt_end = min(kt_end, kt_begin + per);
+    // the tiles are dealt evenly: part z takes [z*n/parts, (z+1)*n/parts), sizes that differ by at most one
+    const int n = kt_end - kt_begin, z = blockIdx.z;
+    kt_end = kt_begin + (int)((int64_t)(z + 1) * n / p.n_splits);
+    kt_begin += (int)((int64_t)z * n / p.n_splits);
   }
 
   const __nv_bfloat16* Kbase = reinterpret_cast<const __nv_bfloat16*>(p.cache.k);
