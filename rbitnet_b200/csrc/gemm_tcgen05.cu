@@ -35,7 +35,7 @@ constexpr int BK = 64;         // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int W_TILE_BYTES = BM * BK * 2;
 
-enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_GATED = 3 };
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_GATED = 3, EPI_QKV = 4 };
 
 __host__ __device__ constexpr uint32_t make_idesc(int n) { return make_idesc_mn(BM, n, 0, 0); }
 
@@ -44,6 +44,21 @@ template <> __device__ __forceinline__ void store_out<float>(float* p, float v) 
 template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) {
   *p = __float2bfloat16_rn(v);
 }
+
+// What the q/k/v product of a few tokens does with its result instead of storing it (EPI_QKV):
+// rotate the q and k heads by the token's position (crates/bitnet-core/src/llama/model.rs:122-136),
+// write q to q_out [tokens, H, D], the rotated k and the raw v to the token's place in the paged
+// cache (model.rs:254-257).  Rows of W: [H*D of q | Kh*D of k | Kh*D of v], or q alone.
+struct QkvTail {
+  __nv_bfloat16* q_out;
+  const float* inv_freq;     // [D/2]
+  const int* tok_pos;
+  const int* tok_slot;
+  RbPagedLayer cache;
+  int H;
+  int write_kv;              // 0: W holds q rows only (a layer that reads another layer's cache)
+  int interleaved;           // pairs (2i, 2i+1) instead of (i, i + D/2)
+};
 
 struct GemmParams {
   void* C;            // output (or float32 slices for EPI_PARTIAL)
@@ -58,6 +73,7 @@ struct GemmParams {
   int splits;         // parts of K
   int n_items;        // weight tiles * token tiles * splits
   int cluster;        // 1: the splits of a tile form a thread-block cluster and are summed through shared memory
+  QkvTail qkv;        // EPI_QKV only
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -330,7 +346,59 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     static_assert(BN * BM * 4 <= STAGES * STAGE_BYTES, "the ring holds one accumulator");
     __syncwarp();
     cluster_sync_all();
-    if (EPI != EPI_GATED && warp >= 2 && first_item < p.n_items) {   // (the gated product is never split)
+    if (EPI == EPI_QKV && warp >= 2 && first_item < p.n_items) {
+      // As below, every CTA of the cluster adds up its share of the token columns; a thread also adds
+      // up the row that its own row is rotated with (both lie in this tile: the head size divides
+      // 128), rotates in float32 and writes the one rounded result where it belongs.
+      int n0, t0, kb_begin, nkb, split;
+      item_of(first_item, n0, t0, kb_begin, nkb, split);
+      const QkvTail& q = p.qkv;
+      const int D = q.cache.head_dim, HD = q.H * D, KD = q.write_kv ? q.cache.n_kv_heads * D : 0;
+      const int row = (warp & 3) * 32 + lane, n = n0 + row, d = n % D;
+      const int my = (int)cluster_rank();
+      int pair, prow;
+      bool first;
+      if (q.interleaved) { pair = d >> 1; first = (d & 1) == 0; prow = row ^ 1; }
+      else { pair = d % (D / 2); first = d < D / 2; prow = first ? row + D / 2 : row - D / 2; }
+      const bool is_v = n >= HD + KD;
+      uint32_t own[8], other[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const uint32_t rank = (uint32_t)(r < p.splits ? r : 0);
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(own[r]) : "r"(smem_u32(smem) + (uint32_t)row * 4), "r"(rank));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(other[r]) : "r"(smem_u32(smem) + (uint32_t)prow * 4), "r"(rank));
+      }
+      if (n < p.n_out) {
+        const float inv = is_v ? 0.f : q.inv_freq[pair];
+        for (int col = my; col < BN && t0 + col < p.n_tokens; col += p.splits) {
+          float a[8], b[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {        // all loads first, then the sums in split order
+            a[r] = 0.f; b[r] = 0.f;
+            if (r < p.splits) {
+              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(a[r]) : "r"(own[r] + (uint32_t)(col * BM) * 4));
+              if (!is_v) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(b[r]) : "r"(other[r] + (uint32_t)(col * BM) * 4));
+            }
+          }
+          float x = a[0], xp = b[0];
+#pragma unroll
+          for (int r = 1; r < 8; ++r) { x += a[r]; xp += b[r]; }
+          const int t = t0 + col, pos = q.tok_pos[t];
+          float y = x;
+          if (!is_v) {
+            float sn, cs;
+            sincosf((float)pos * inv, &sn, &cs);
+            y = first ? x * cs - xp * sn : xp * sn + x * cs;
+          }
+          __nv_bfloat16* dst;
+          if (n < HD) dst = q.q_out + (int64_t)t * HD + n;
+          else if (!is_v) dst = (__nv_bfloat16*)q.cache.k + rb_page_offset(q.cache, q.tok_slot[t], pos, (n - HD) / D) + d;
+          else dst = (__nv_bfloat16*)q.cache.v + rb_page_offset(q.cache, q.tok_slot[t], pos, (n - HD - KD) / D) + d;
+          *dst = __float2bfloat16_rn(y);
+        }
+      }
+    }
+    if (EPI != EPI_GATED && EPI != EPI_QKV && warp >= 2 && first_item < p.n_items) {   // (the gated product is never split)
       // every CTA of the cluster adds up a share of the token columns (column c belongs to rank
       // c mod splits), reading all parts of a column in split order through distributed shared memory
       int n0, t0, kb_begin, nkb, split;
@@ -538,9 +606,9 @@ RB_EXPORT int rb_read_error_flag(int* value, int reset) {
 //               (n_out rows in all, a multiple of 32); C[tokens, n_features] = silu(gate)*up
 // Requirements (refused otherwise): bfloat16 X and W, K a multiple of 8, row strides multiples of 8
 // elements, 16-byte aligned bases.
-RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
-                         int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
-                         int token_tile, cudaStream_t stream) {
+static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
+                   int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
+                   int token_tile, const QkvTail* tail, cudaStream_t stream) {
   if (n_tokens == 0 || n_out == 0) return 0;
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
   RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
@@ -566,10 +634,48 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
   p.cluster = (splits > 1 && epilogue != EPI_PARTIAL) ? 1 : 0;
   RB_REQUIRE(!p.cluster || bn <= 64, "rb_gemm_tc: K is split only for token tiles of at most 64");
+  if (epilogue == EPI_QKV) {
+    RB_REQUIRE(tail != nullptr && p.cluster, "rb_gemm_tc: the q/k/v tail wants K split into a cluster");
+    p.qkv = *tail;
+    return dispatch<EPI_QKV, __nv_bfloat16>(bn, tw, tx, p, stream);
+  }
   if (epilogue == EPI_STORE && c_dtype == RB_BF16) return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, stream);
   if (epilogue == EPI_STORE && c_dtype == RB_F32) return dispatch<EPI_STORE, float>(bn, tw, tx, p, stream);
   if (epilogue == EPI_ADD && c_dtype == RB_F32) return dispatch<EPI_ADD, float>(bn, tw, tx, p, stream);
   if (epilogue == EPI_PARTIAL && c_dtype == RB_F32) return dispatch<EPI_PARTIAL, float>(bn, tw, tx, p, stream);
   if (epilogue == EPI_GATED && c_dtype == RB_BF16) return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, p, stream);
   RB_FAIL("rb_gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, c_dtype);
+}
+
+RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
+                         int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
+                         int token_tile, cudaStream_t stream) {
+  RB_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_GATED, "rb_gemm_tc: unknown epilogue %d", epilogue);
+  return gemm_tc(C, ldc, c_dtype, X, ldx, n_tokens, W, ldw, w_rows, n_out, K, epilogue, n_features, splits, token_tile,
+                 nullptr, stream);
+}
+
+// Whether rb_gemm_tc_qkv takes these sizes: a head may not straddle two 128-row tiles of W, and the
+// product must be one that is split along K (2..8 parts).  At most 16 tokens: with more, the
+// rotation in the epilogue (measured at 64) costs more than the kernel it saves.
+RB_EXPORT int rb_gemm_tc_qkv_supports(int n_tokens, int D, int splits) {
+  return n_tokens >= 1 && n_tokens <= 16 && splits >= 2 && splits <= 8 && D >= 2 && D % 2 == 0 && BM % D == 0;
+}
+
+// The q/k/v product of up to 64 tokens with rotation and cache append in its epilogue (see QkvTail).
+// W: [H*D + (write_kv ? 2*Kh*D : 0), K].  K is cut into `splits` >= 2 parts (one cluster per tile).
+RB_EXPORT int rb_gemm_tc_qkv(void* q_out, const void* X, int64_t ldx, int n_tokens, const void* W, int64_t ldw, int K,
+                             int splits, const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
+                             void* cache_v, const int* page_table, int max_pages, int page_size, int H, int Kh, int D,
+                             int write_kv, int interleaved, cudaStream_t stream) {
+  RB_REQUIRE(rb_gemm_tc_qkv_supports(n_tokens, D, splits), "rb_gemm_tc_qkv: tokens=%d head=%d splits=%d not supported",
+             n_tokens, D, splits);
+  RB_REQUIRE(H > 0 && Kh >= 0 && page_size > 0, "rb_gemm_tc_qkv: bad sizes H=%d Kh=%d page=%d", H, Kh, page_size);
+  QkvTail tail;
+  tail.q_out = (__nv_bfloat16*)q_out; tail.inv_freq = inv_freq; tail.tok_pos = tok_pos; tail.tok_slot = tok_slot;
+  tail.cache = RbPagedLayer{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
+  tail.H = H; tail.write_kv = write_kv ? 1 : 0; tail.interleaved = interleaved ? 1 : 0;
+  const int rows = (H + (write_kv ? 2 * Kh : 0)) * D;
+  return gemm_tc(q_out, (int64_t)H * D, RB_BF16, X, ldx, n_tokens, W, ldw, rows, rows, K, EPI_QKV, 0, splits, 0, &tail,
+                 stream);
 }

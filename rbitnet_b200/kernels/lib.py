@@ -26,6 +26,7 @@ _SIGNATURES = {
     "rb_sample": [P, P, L, I, I, P, P, P, P],
     "rb_sample_chunks": [I],
     "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, P],
+    "rb_gemm_tc_qkv": [P, P, L, I, P, L, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "rb_read_error_flag": [P, I],
     "rb_decode_advance": [P, P, P, I, P],
     "rb_attention_prefill": [P, P, P, P, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
@@ -50,6 +51,7 @@ class KernelLibrary:
             self.declare(name, argtypes)
         self.declare("rb_attention_tiled_supports", [I, I, I, I, I])
         self.declare("rb_attention_prefill_tc_supports", [I, I, I, I])
+        self.declare("rb_gemm_tc_qkv_supports", [I, I, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

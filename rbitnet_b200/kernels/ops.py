@@ -213,6 +213,29 @@ class CudaOps:
                       1 if interleaved else 0, in_code, n_slices, slice_stride, self._stream())
         return q
 
+    def project_rotate_append(self, h: torch.Tensor, weight: LinearWeight, rotary, meta, view,
+                              n_heads: int) -> torch.Tensor:
+        """q/k/v product of the normed rows ``h``, rotation by position and cache append; returns the
+        rotated q [T, H, D].  For a few tokens (a decode step) the product's own epilogue rotates and
+        appends, from its float32 sums; otherwise the product is stored and ``rotate_append`` follows."""
+        T, K = h.shape
+        D, Kh = view.head_dim, view.n_kv_heads
+        splits = self._k_splits(T, weight.n_out, K)
+        if rotary is None:
+            inv_freq, interleaved, rot_dim = self._zeros_freq(D), False, D
+        else:
+            inv_freq, interleaved, rot_dim = rotary
+        if (self.dtype == torch.bfloat16 and rot_dim == D and self._tensor_core_ok(h, weight.w)
+                and weight.n_out == (n_heads + (2 * Kh if view.writes else 0)) * D
+                and self.lib.raw("rb_gemm_tc_qkv_supports")(T, D, splits)):
+            q = torch.empty((T, n_heads, D), dtype=self.dtype, device=self.device)
+            self.lib.call("rb_gemm_tc_qkv", _ptr(q), _ptr(h), h.stride(0), T, _ptr(weight.w), weight.w.stride(0), K,
+                          splits, _ptr(inv_freq), _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k), _ptr(view.v),
+                          _ptr(view.page_table), view.max_pages, view.page_size, n_heads, Kh, D,
+                          1 if view.writes else 0, 1 if interleaved else 0, self._stream())
+            return q
+        return self.rotate_append(self.linear(h, weight), rotary, meta, view, n_heads)
+
     def _zeros_freq(self, D):
         z = getattr(self, "_zf", None)
         if z is None or z.shape[0] < D // 2:

@@ -49,12 +49,12 @@ class Attention(Mixer):
         ops = ctx.ops
         view = ctx.cache_view(entry)
         if view.writes:
-            qkv = ops.linear(h, self.w_qkv)
+            w = self.w_qkv
         else:
             if self.w_q is None:
                 self.w_q = ops.prepare_linear([self._q_weight])
-            qkv = ops.linear(h, self.w_q)
-        q = ops.rotate_append(qkv, self.position.rotary(), ctx.meta, view, self.n_heads)
+            w = self.w_q
+        q = ops.project_rotate_append(h, w, self.position.rotary(), ctx.meta, view, self.n_heads)
         a = ops.attention(q, ctx.meta, view, self.n_heads, self.scale, self.window)
         ops.linear(a, self.w_o, accumulate_into=accumulate_into)
 

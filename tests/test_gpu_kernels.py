@@ -286,6 +286,64 @@ def test_rotation_and_cache_append(ops32, ops16, H, Kh, D, interleaved):
         assert int((k.abs().sum(dim=(1, 3)) > 0).sum()) == written       # nothing else was touched
 
 
+@pytest.mark.parametrize("H,Kh,D,interleaved,K,T,writes", [
+    (4, 2, 16, True, 512, 5, True), (3, 1, 32, False, 1024, 6, True), (8, 8, 64, False, 2048, 1, True),
+    (6, 2, 128, True, 4096, 6, True), (5, 1, 64, False, 1024, 6, False), (2, 1, 128, False, 520, 40, True)])
+def test_qkv_product_that_rotates_and_appends_in_its_epilogue(ops16, H, Kh, D, interleaved, K, T, writes):
+    """The q/k/v product of a few tokens whose epilogue rotates q and k and writes k and v into the paged
+    cache, against the product in float64 followed by the rotation; and the step's own choice of path."""
+    from rbitnet_b200.cache import CacheLayerView
+    theta = 10000.0 if interleaved else 500000.0
+    page, max_pages, n_slots = 16, 8, 6
+    places = [(0, 0), (0, 1), (2, 100), (1, 15), (1, 16), (2, 127)]
+    rows = [places[i % 6] if i < 6 else (3 + (i - 6) // 20, i) for i in range(T)]
+    g = torch.Generator(device="cuda").manual_seed(31)
+    n_out = (H + (2 * Kh if writes else 0)) * D
+    h = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    w = (torch.randn(n_out, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    lw = ops16.prepare_linear([w])
+    k = torch.zeros(n_slots * max_pages, Kh, page, D, device="cuda", dtype=BF16)
+    v = torch.zeros_like(k)
+    table = torch.randperm(n_slots * max_pages).to(torch.int32).reshape(n_slots, max_pages).cuda()
+    view = CacheLayerView(k, v, table, max_pages, page, Kh, D, writes, 0)
+    meta = _meta(rows)
+    i = torch.arange(D // 2, dtype=torch.float32)
+    inv = (1.0 / torch.pow(torch.tensor(theta), 2.0 * i / D)).cuda()
+    splits = ops16._k_splits(T, n_out, K)
+    fused = bool(ops16.lib.raw("rb_gemm_tc_qkv_supports")(T, D, splits))
+    assert fused == (splits >= 2 and T <= 16), (splits, fused)
+    before = ops16.lib.launches
+    q = ops16.project_rotate_append(h, lw, (inv, interleaved, D), meta, view, H)
+    assert ops16.lib.launches - before == (1 if fused else 2)
+    ops16.check_errors()
+
+    def rot(x, pos):     # x [heads, D] float64
+        ang = (torch.tensor(float(pos), dtype=torch.float32) * inv.cpu()).double()
+        c, s = torch.cos(ang), torch.sin(ang)
+        out = torch.empty_like(x)
+        if interleaved:
+            a, b = x[:, 0::2], x[:, 1::2]
+            out[:, 0::2], out[:, 1::2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = x[:, :D // 2], x[:, D // 2:]
+            out[:, :D // 2], out[:, D // 2:] = a * c - b * s, a * s + b * c
+        return out
+
+    x = (h.double() @ w.double().T).cpu()
+    scale = float(x.abs().max())
+    for t, (slot, pos) in enumerate(rows):
+        assert float((q[t].cpu().double() - rot(x[t, :H * D].reshape(H, D), pos)).abs().max()) < 6e-3 * scale
+        if writes:
+            pg = int(table[slot, pos // page])
+            got_k, got_v = k[pg, :, pos % page].cpu().double(), v[pg, :, pos % page].cpu().double()
+            assert float((got_k - rot(x[t, H * D:(H + Kh) * D].reshape(Kh, D), pos)).abs().max()) < 6e-3 * scale
+            assert float((got_v - x[t, (H + Kh) * D:].reshape(Kh, D)).abs().max()) < 6e-3 * scale
+    if writes:
+        assert int((k.abs().sum(dim=(1, 3)) > 0).sum()) == len(set(rows))       # nothing else was touched
+    else:
+        assert float(k.abs().sum()) == 0 and float(v.abs().sum()) == 0
+
+
 @pytest.mark.parametrize("V", [257, 1000, 128256])
 def test_sampling(ops32, V):
     import plain_llama as plain

@@ -67,6 +67,9 @@ class TorchOps:
         g, u = gu[:, :weight.inner], gu[:, weight.inner:]
         return (g / (1.0 + torch.exp(-g)) * u).to(self.dtype)
 
+    def project_rotate_append(self, h, weight, rotary, meta, view, n_heads):
+        return self.rotate_append(self.linear(h, weight), rotary, meta, view, n_heads)
+
     def rotate_append(self, qkv, rotary, meta, view, n_heads):
         T = qkv.shape[0]
         D, Kh = view.head_dim, view.n_kv_heads
