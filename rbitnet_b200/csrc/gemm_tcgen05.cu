@@ -412,19 +412,20 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       for (int r = 0; r < 8; ++r)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[r]) : "r"(red), "r"((uint32_t)(r < p.splits ? r : 0)));
       if (n < p.n_out) {
-        for (int cb = 0; cb < BN; cb += 2 * p.splits) {
-          int col[2];
-          bool ok[2];
-          float old[2], part[2][8];
+        constexpr int CPI = BN >= 64 ? 8 : (BN >= 32 ? 4 : 2);      // columns whose loads are in flight together
+        for (int cb = 0; cb < BN; cb += CPI * p.splits) {
+          int col[CPI];
+          bool ok[CPI];
+          float old[CPI], part[CPI][8];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < CPI; ++h) {
             col[h] = cb + h * p.splits + my;
             ok[h] = col[h] < BN && t0 + col[h] < p.n_tokens;
             old[h] = 0.f;
             if (EPI == EPI_ADD && ok[h]) old[h] = ((const float*)p.C)[(int64_t)(t0 + col[h]) * p.ldc + n];
           }
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+          for (int h = 0; h < CPI; ++h)
 #pragma unroll
             for (int r = 0; r < 8; ++r) {      // all loads first, then the sums in split order
               part[h][r] = 0.f;
@@ -432,7 +433,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[h][r]) : "r"(remote[r] + (uint32_t)(col[h] * BM) * 4));
             }
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < CPI; ++h) {
             if (!ok[h]) continue;
             float v = part[h][0];
 #pragma unroll
