@@ -469,6 +469,7 @@ int launch_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& 
 }  // namespace
 
 int rb_attention_tc_error_flag(int* value, int reset) { return rb_file_error_flag(value, reset); }
+int rb_attention_tc_error_flag_address(int** out) { return rb_file_error_flag_address(out); }
 
 // Whether the tensor-memory prefill kernel takes these sizes.
 RB_EXPORT int rb_attention_prefill_tc_supports(int H, int Kh, int D, int page_size) {

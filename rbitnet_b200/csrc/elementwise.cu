@@ -526,7 +526,8 @@ RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R,
 // After a decode step has sampled: the sampled ids become the next step's tokens and every
 // position moves on by one, so that steps can follow one another without the host.
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ tok_pos,
-                                      const int* __restrict__ sampled, int B) {
+                                      const int* __restrict__ sampled, int B, const int* flag_a,
+                                      const int* flag_b, int* __restrict__ flag_out) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -534,11 +535,18 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restri
     token_ids[i] = sampled[i];
     tok_pos[i] += 1;
   }
+  // the error words of the kernels that wait on barriers travel with the step's results
+  if (i == 0 && flag_out != nullptr) {
+    const int a = flag_a != nullptr ? *flag_a : 0, b = flag_b != nullptr ? *flag_b : 0;
+    *flag_out = a != 0 ? a : b;
+  }
 }
 
-RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled, int B, cudaStream_t stream) {
+RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled, int B, const int* flag_a,
+                                const int* flag_b, int* flag_out, cudaStream_t stream) {
   if (B == 0) return 0;
-  RB_LAUNCH("decode_advance_kernel", (decode_advance_kernel), (B + 127) / 128, 128, 0, stream, token_ids, tok_pos, sampled, B);
+  RB_LAUNCH("decode_advance_kernel", (decode_advance_kernel), (B + 127) / 128, 128, 0, stream, token_ids, tok_pos, sampled, B,
+            flag_a, flag_b, flag_out);
   RB_CHECK_LAUNCH("rb_decode_advance");
   return 0;
 }

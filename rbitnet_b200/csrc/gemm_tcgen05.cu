@@ -589,6 +589,15 @@ int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmPar
 // The device word that a kernel sets when one of its bounded waits ran out (0: none).
 int rb_attention_tc_error_flag(int* value, int reset);   // attention_tcgen05.cu
 
+int rb_attention_tc_error_flag_address(int** out);   // attention_tcgen05.cu
+
+// Device addresses of the two error words, so that a step can report them with its results
+// instead of the host reading them after every step.
+RB_EXPORT int rb_error_flag_addresses(int** a, int** b) {
+  if (rb_file_error_flag_address(a) != 0) return -1;
+  return rb_attention_tc_error_flag_address(b);
+}
+
 RB_EXPORT int rb_read_error_flag(int* value, int reset) {
   int a = 0, b = 0;
   if (rb_file_error_flag(&a, reset) != 0) return -1;

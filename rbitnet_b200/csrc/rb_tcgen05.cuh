@@ -22,6 +22,14 @@ static inline int rb_file_error_flag(int* value, int reset) {
   return 0;
 }
 
+// Device address of this file's error word (for a kernel that reports it with a step's results).
+static inline int rb_file_error_flag_address(int** out) {
+  void* p = nullptr;
+  RB_CUDA(cudaGetSymbolAddress(&p, g_error_flag));
+  *out = (int*)p;
+  return 0;
+}
+
 // Tensor map of a row-major bfloat16 matrix [rows, cols] (cols contiguous, row stride ld elements),
 // box [box_rows, 64], 128-byte swizzle, zero fill outside; cached by its arguments.
 int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows);

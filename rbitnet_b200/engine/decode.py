@@ -6,7 +6,8 @@ host, the gaps between them cost as much as the kernels.  The chain is therefore
 captured once per batch size and replayed.  Which sequences, tokens and positions a
 replay works on is data in fixed device buffers (slot ids index the cache's page
 tables), so one graph serves any B sequences.  Per step the host writes one small
-pinned buffer, copies it, replays, and reads B sampled ids back.
+pinned buffer, copies it, replays, and reads B sampled ids back, and with them the word in
+which a kernel records that one of its bounded waits ran out.
 """
 from __future__ import annotations
 
@@ -31,7 +32,9 @@ class DecodeGraph:
         self.token_ids, self.tok_pos, self.tok_slot, self.want = (self.buf[i * B:(i + 1) * B] for i in range(4))
         fl = self.buf.view(torch.float32)
         self.temps, self.uniforms = fl[4 * B:5 * B], fl[5 * B:6 * B]
-        self.out_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.out_host = torch.zeros(B + 1, dtype=torch.int32).pin_memory()     # sampled ids, then the error word
+        self.result = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+        self.error_code = 0
         self.meta = StepMeta(self.token_ids, self.tok_pos, self.tok_slot, self.want, B, B,
                              [SeqChunk(0, 0, 1, i) for i in range(B)], True, cache.max_seq)
         self.graph = None
@@ -40,8 +43,8 @@ class DecodeGraph:
 
     def _body(self):
         logits = self.model.forward(StepContext(self.ops, self.meta, self.cache))
-        sampled = self.ops.sample(logits, self.temps, self.uniforms)
-        self.ops.decode_advance(self.token_ids, self.tok_pos, sampled)
+        sampled = self.ops.sample(logits, self.temps, self.uniforms, out=self.result[:self.B])
+        self.ops.decode_advance(self.token_ids, self.tok_pos, sampled, flag_out=self.result[self.B:])
         return sampled
 
     def capture(self, pool=None):
@@ -84,9 +87,12 @@ class DecodeGraph:
         self.ops.lib.launches += self.kernels
 
     def read(self) -> List[int]:
-        self.out_host.copy_(self.sampled, non_blocking=True)
+        """The sampled ids of the last replay; ``error_code`` is the kernels' error word (0: none)."""
+        self.out_host.copy_(self.result, non_blocking=True)
         torch.cuda.current_stream(self.ops.device).synchronize()
-        return self.out_host.tolist()
+        out = self.out_host.tolist()
+        self.error_code = out[self.B]
+        return out[:self.B]
 
     @property
     def h2d_bytes(self) -> int:

@@ -217,15 +217,15 @@ class Engine:
                 self._graph_pool = g.graph.pool()
         g.replay()
         ids = g.read()[:n]
+        if g.error_code:
+            self.ops.check_errors()            # raises with the code, and clears the word
         for s in slots:
             self.cache.advance(s, 1)
         return ids
 
     def _step_sample(self, feed, temperatures, uniforms) -> List[int]:
         if self.use_graphs and all(len(t) == 1 for _, t in feed):
-            ids = self._decode_step(feed, temperatures, uniforms)
-            self.ops.check_errors()
-            return ids
+            return self._decode_step(feed, temperatures, uniforms)   # the error word comes back with the ids
         entries = [StepEntry(slot, toks, [len(toks) - 1]) for slot, toks in feed]
         logits = self.stepper.step(entries)
         params = torch.from_numpy(np.asarray([temperatures, uniforms], dtype=np.float32)).to(self.ops.device)

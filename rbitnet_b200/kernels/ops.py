@@ -63,6 +63,7 @@ class CudaOps:
         self.lib = load(verbose=verbose_build)
         #: prefill attention of head sizes 64 and 128 runs on tcgen05 (else on the mma.sync kernel)
         self.prefill_on_tcgen05 = True
+        self._flag_ptrs = None
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -325,17 +326,28 @@ class CudaOps:
         self.lib.call("rb_gather_rows", _ptr(out), _ptr(x), _ptr(rows), R, E, self._stream())
         return out
 
-    def sample(self, logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor) -> torch.Tensor:
-        """One token id per row of float32 logits; temperature <= 0 is the arg-max."""
+    def sample(self, logits: torch.Tensor, temperature: torch.Tensor, uniform: torch.Tensor,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One token id per row of float32 logits (into ``out`` if given); temperature <= 0 is the arg-max."""
         self._check(logits, torch.float32, "sample logits")
         R, V = logits.shape
-        out = torch.empty((R,), dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty((R,), dtype=torch.int32, device=self.device)
         stats = torch.empty((R, self.lib.raw("rb_sample_chunks")(V) * 3), dtype=torch.float32, device=self.device)
         self.lib.call("rb_sample", _ptr(out), _ptr(logits), logits.stride(0), R, V, _ptr(temperature),
                       _ptr(uniform), _ptr(stats), self._stream(), launches=2)
         return out
 
-    def decode_advance(self, token_ids: torch.Tensor, tok_pos: torch.Tensor, sampled: torch.Tensor) -> None:
-        """token_ids <- sampled; tok_pos += 1 (the next decode step's inputs, made on the device)."""
+    def decode_advance(self, token_ids: torch.Tensor, tok_pos: torch.Tensor, sampled: torch.Tensor,
+                       flag_out: Optional[torch.Tensor] = None) -> None:
+        """token_ids <- sampled; tok_pos += 1 (the next decode step's inputs, made on the device).
+        With ``flag_out`` (one int32) the kernels' error word is written there too, so that it comes
+        back with the step's results (0: no bounded wait ran out)."""
+        if self._flag_ptrs is None:
+            import ctypes
+            a, b = ctypes.c_void_p(0), ctypes.c_void_p(0)
+            self.lib.call("rb_error_flag_addresses", ctypes.byref(a), ctypes.byref(b), launches=0)
+            self._flag_ptrs = (a, b)
+        a, b = self._flag_ptrs if flag_out is not None else (c_void_p(0), c_void_p(0))
         self.lib.call("rb_decode_advance", _ptr(token_ids), _ptr(tok_pos), _ptr(sampled), token_ids.shape[0],
-                      self._stream())
+                      a, b, _ptr(flag_out), self._stream())
