@@ -92,6 +92,9 @@ class SlotBook:
         if total > self.max_seq:
             raise ContextOverflow(f"sequence would reach {total} positions; the cache holds "
                                   f"at most {self.max_seq} per sequence")
+        have = self.pages[slot]
+        if all(total <= len(pg) * self.page_size for pg in have):
+            return [[] for _ in have]            # the usual case of a decode step: room in the last page
         want = -(-total // self.page_size)
         added = [[] for _ in self.pools]
         try:
