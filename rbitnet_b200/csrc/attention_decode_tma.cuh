@@ -1,0 +1,297 @@
+// Decode attention (one token per sequence) with keys and values brought in by TMA.
+//
+// The arithmetic is that of the decode mode of attention_tiled.cu: one CTA works for ONE kv head of
+// ONE sequence on a part of its keys; its rows are the token's G query heads (G <= 16, padded to the
+// 16 rows of mma.sync m16n8k16); keys and values come in tiles of 64 positions, of which each of the
+// four warps takes 16 keys; the warps are merged at the end and the CTA writes an unnormalised
+// partial (max, sum, O) that attn_combine_kernel merges, or the result itself when the keys are not
+// split.  crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound, P V), :102-114.
+//
+// What differs is how a tile gets into shared memory.  There, every thread issues 32 cp.async of 16
+// bytes per tile, which costs the four warps about a third of a tile's time; here one thread asks
+// for a tile with 2 * D/64 TMA boxes of [64 positions, 64 values] (128-byte swizzle, the layout
+// ldmatrix reads without bank conflicts) and everybody waits on the stage's mbarrier.  Head sizes 64
+// and 128.  This header is included by attention_tcgen05.cu, whose TMA and mbarrier helpers and
+// error word it shares; every wait is bounded.
+#pragma once
+
+namespace decode_tma {
+
+constexpr int TILE = 64;           // positions per tile = per TMA box
+constexpr int WARPS_D = 4;
+constexpr int NS = 2;              // stages of keys and values
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2bf(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Params {
+  const __nv_bfloat16* q;   // [B, H, D]
+  __nv_bfloat16* out;       // [B, H*D]
+  const int* page_table;
+  int max_pages, page_size, n_kv_heads;
+  const int* tok_pos;
+  const int* tok_slot;
+  int H, G;
+  float scale_log2;         // scale * log2(e)
+  int window;               // 0: none
+  float* part_o;            // [B, H, n_splits, D]
+  float* part_ml;           // [B, H, n_splits, 2]
+  int n_splits;
+};
+
+template <int D> struct Smem {
+  static constexpr int DB = D / 64;                      // 64-value blocks of a head
+  static constexpr int BLOCK = TILE * 128;               // [64 positions][128 bytes]
+  static constexpr int TILE_BYTES = DB * BLOCK;          // keys (or values) of one tile
+  static constexpr int LDQ = D + 8;                      // row stride of Q (padded against bank conflicts)
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = NS * TILE_BYTES;
+  static constexpr int OFF_Q = 2 * NS * TILE_BYTES;
+  static constexpr int OFF_BAR = OFF_Q + 16 * LDQ * 2;
+  static constexpr int KV_BYTES = 2 * NS * TILE_BYTES;
+  // the merge of the four warps reuses the tile buffers: [4 warps][16 rows][D] floats, then max and sum
+  static constexpr int MERGE_BYTES = (WARPS_D * 16 * D + 2 * WARPS_D * 16) * 4;
+  static constexpr int BYTES = (MERGE_BYTES > OFF_BAR ? MERGE_BYTES : OFF_BAR) + 64 + 1024;   // + room to align
+};
+
+// byte offset of element (row, col) of a tile: 64-value blocks of [64 rows][128 bytes] whose
+// 16-byte chunks are exchanged by the row's low three bits (the 128-byte swizzle of the TMA box)
+template <int D> __device__ __forceinline__ uint32_t tile_off(int row, int col) {
+  return (uint32_t)((col >> 6) * Smem<D>::BLOCK + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + (col & 7) * 2);
+}
+
+template <int D>
+__global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK,
+                                                                      const __grid_constant__ CUtensorMap tmV, Params p) {
+  rb_pdl_launch_dependents();
+  using S = Smem<D>;
+  constexpr int DB = S::DB, LDQ = S::LDQ;
+  constexpr int NT = 2;                       // 8-key column tiles of S per warp (16 keys)
+  constexpr int DT = D / 8;                   // 8-wide column tiles of O
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + S::OFF_Q);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (S::MERGE_BYTES > S::OFF_BAR ? S::MERGE_BYTES : S::OFF_BAR));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int kvh = blockIdx.y, tok0 = blockIdx.x;
+  const int G = p.G, H = p.H;
+  // positions, slots and page tables were written before the step began: they are read at once
+  const int slot = p.tok_slot[tok0];
+  const int pos0 = p.tok_pos[tok0];
+  const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  int kt_begin = key_lo / TILE, kt_end = pos0 / TILE + 1;
+  if (p.n_splits > 1) {
+    // the tiles are dealt evenly: part z takes [z*n/parts, (z+1)*n/parts), sizes that differ by at most one
+    const int n = kt_end - kt_begin, z = blockIdx.z;
+    kt_end = kt_begin + (int)((int64_t)(z + 1) * n / p.n_splits);
+    kt_begin += (int)((int64_t)z * n / p.n_splits);
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NS; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  // one thread asks for a tile: keys and values of 64 positions of this kv head, D/64 boxes each
+  auto request = [&](int kt, int buf) {
+    const int key0 = kt * TILE;
+    const int page = p.page_table[(int64_t)slot * p.max_pages + key0 / p.page_size];
+    const int row = (page * p.n_kv_heads + kvh) * p.page_size + key0 % p.page_size;
+    mbar_expect_tx(&full[buf], 2 * S::TILE_BYTES);
+#pragma unroll
+    for (int b = 0; b < DB; ++b) {
+      tma_load_2d(smem + S::OFF_K + buf * S::TILE_BYTES + b * S::BLOCK, &tmK, b * 64, row, &full[buf]);
+      tma_load_2d(smem + S::OFF_V + buf * S::TILE_BYTES + b * S::BLOCK, &tmV, b * 64, row, &full[buf]);
+    }
+  };
+  // Every tile but the one that holds the newest position was written by earlier steps, so this
+  // CTA's first tile can be on its way before the wait for the kernel that wrote the newest.
+  const int newest = pos0 / TILE;
+  int n_early = 0;
+  if (threadIdx.x == 0 && kt_begin < kt_end && kt_begin != newest) {
+    request(kt_begin, 0);
+    n_early = 1;
+  }
+  rb_pdl_wait();
+
+  // ---- the token's G query rows into shared memory (rows beyond G are zero)
+  for (int idx = threadIdx.x; idx < 16 * (D / 8); idx += WARPS_D * 32) {
+    const int r = idx / (D / 8), c = idx % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok0 * H + kvh * G + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(sQ + r * LDQ + c * 8) = v;
+  }
+  if (threadIdx.x == 0 && n_early == 0 && kt_begin < kt_end) request(kt_begin, 0);
+
+  // ---- per-warp state: all 16 rows, keys kw0 .. kw0+15 of every tile
+  const int kw0 = warp * 16;
+  float o[DT][4];
+#pragma unroll
+  for (int i = 0; i < DT; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const bool row_ok[2] = {g < G, g + 8 < G};
+  const uint32_t q_base = smem_u32(sQ);
+  bool failed = false;
+  __syncthreads();                       // Q is in shared memory
+
+  for (int kt = kt_begin; kt < kt_end; ++kt) {
+    const int i = kt - kt_begin, buf = i % NS;
+    // the next tile goes into the other stage, which everybody left at the end of the last round
+    if (threadIdx.x == 0 && kt + 1 < kt_end) request(kt + 1, buf ^ 1);
+    if (!failed && !mbar_wait(&full[buf], (uint32_t)((i / NS) & 1), 14)) failed = true;
+    const uint32_t tK = smem_u32(smem + S::OFF_K + buf * S::TILE_BYTES);
+    const uint32_t tV = smem_u32(smem + S::OFF_V + buf * S::TILE_BYTES);
+    const int key_base = kt * TILE + kw0;
+    if (key_base <= pos0) {
+      // ---- S = Q K^T: two accumulators per 8-key tile, over even and odd steps of d, so that the
+      // chain of dependent products is half as long
+      float s[NT][4], s2[NT][4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; s2[n][0] = s2[n][1] = s2[n][2] = s2[n][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, q_base + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * LDQ + kk * 16 + (lane >> 4) * 8) * 2);
+        // matrices: (keys 0-7, d lo), (keys 0-7, d hi), (keys 8-15, d lo), (keys 8-15, d hi)
+        ldsm_x4(b, tK + tile_off<D>(kw0 + (lane >> 4) * 8 + (lane & 7), kk * 16 + ((lane >> 3) & 1) * 8));
+        if (kk & 1) { mma16816(s2[0], a, b[0], b[1]); mma16816(s2[1], a, b[2], b[3]); }
+        else { mma16816(s[0], a, b[0], b[1]); mma16816(s[1], a, b[2], b[3]); }
+      }
+      // ---- mask, running max
+      float m_new[2] = {m_run[0], m_run[1]};
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int h = c >> 1;
+          const int key = key_base + n * 8 + t4 * 2 + (c & 1);
+          const bool ok = row_ok[h] && key <= pos0 && key >= key_lo;
+          const float v = ok ? (s[n][c] + s2[n][c]) * p.scale_log2 : -INFINITY;
+          s[n][c] = v;
+          m_new[h] = fmaxf(m_new[h], v);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 1));
+        m_new[h] = fmaxf(m_new[h], __shfl_xor_sync(0xffffffffu, m_new[h], 2));
+      }
+      float corr[2], m_use[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        m_use[h] = m_new[h] == -INFINITY ? 0.f : m_new[h];      // a row with nothing allowed so far
+        corr[h] = exp2f(m_run[h] - m_use[h]);                    // exp2(-inf) = 0 on the first tile
+        m_run[h] = m_new[h];
+        l_run[h] *= corr[h];
+      }
+#pragma unroll
+      for (int d = 0; d < DT; ++d) {
+        o[d][0] *= corr[0]; o[d][1] *= corr[0];
+        o[d][2] *= corr[1]; o[d][3] *= corr[1];
+      }
+      // ---- P = exp2(S - m), row sums, P V
+      uint32_t pa[4];
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
+        const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+        l_run[0] += p0 + p1;
+        l_run[1] += p2 + p3;
+        pa[n * 2 + 0] = pack2bf(p0, p1);
+        pa[n * 2 + 1] = pack2bf(p2, p3);
+      }
+#pragma unroll
+      for (int dn = 0; dn < DT; dn += 2) {
+        uint32_t b[4];
+        // matrices: (keys 0-7, d dn), (keys 8-15, d dn), (keys 0-7, d dn+1), (keys 8-15, d dn+1)
+        ldsm_x4_trans(b, tV + tile_off<D>(kw0 + ((lane >> 3) & 1) * 8 + (lane & 7), (dn + (lane >> 4)) * 8));
+        mma16816(o[dn], pa, b[0], b[1]);
+        mma16816(o[dn + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncthreads();   // everybody has left this stage: the round after next may refill it
+  }
+
+  // ---- row sums over the four threads of a quad
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  // ---- merge the four warps (each saw a quarter of every tile's keys), over the tile buffers,
+  // which are free: every request has been waited for
+  float* mO = reinterpret_cast<float*>(smem);
+  float* mM = mO + WARPS_D * 16 * D;
+  float* mL = mM + WARPS_D * 16;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = g + 8 * h;
+#pragma unroll
+    for (int dn = 0; dn < DT; ++dn) {
+      mO[(warp * 16 + r) * D + dn * 8 + t4 * 2] = o[dn][2 * h];
+      mO[(warp * 16 + r) * D + dn * 8 + t4 * 2 + 1] = o[dn][2 * h + 1];
+    }
+    if (t4 == 0) {
+      mM[warp * 16 + r] = m_run[h];
+      mL[warp * 16 + r] = l_run[h];
+    }
+  }
+  __syncthreads();
+  if (failed) return;
+  for (int idx = threadIdx.x; idx < G * D; idx += WARPS_D * 32) {
+    const int r = idx / D, d = idx % D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS_D; ++w) m = fmaxf(m, mM[w * 16 + r]);
+    const float mu = m == -INFINITY ? 0.f : m;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS_D; ++w) {
+      const float f = exp2f(mM[w * 16 + r] - mu);
+      acc += mO[(w * 16 + r) * D + d] * f;
+      l += mL[w * 16 + r] * f;
+    }
+    const int head = kvh * G + r;
+    if (p.n_splits > 1) {
+      const int64_t base = ((int64_t)tok0 * H + head) * p.n_splits + blockIdx.z;
+      p.part_o[base * D + d] = acc;
+      if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
+    } else {
+      p.out[((int64_t)tok0 * H + head) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+  }
+}
+
+template <int D>
+int launch(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B, int Kh, cudaStream_t stream) {
+  auto kernel = attn_decode_tma_kernel<D>;
+  constexpr int smem = Smem<D>::BYTES;
+  static bool configured = false;
+  if (!configured) {
+    RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  RB_LAUNCH("rb_attention_decode_tma", (kernel), dim3(B, Kh, p.n_splits), WARPS_D * 32, smem, stream, tk, tv, p);
+  return 0;
+}
+
+}  // namespace decode_tma

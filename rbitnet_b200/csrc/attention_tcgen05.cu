@@ -468,6 +468,46 @@ int launch_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& 
 
 }  // namespace
 
+#include "attention_decode_tma.cuh"
+
+int rb_attention_combine(void* out, const float* part_o, const float* part_ml, int B, int H, int D, int n_splits,
+                         cudaStream_t stream);   // attention_tiled.cu
+
+// Whether the TMA-fed decode kernel takes these sizes (else rb_attention_decode).
+RB_EXPORT int rb_attention_decode_tma_supports(int H, int Kh, int D, int page_size) {
+  if (Kh <= 0 || H % Kh) return 0;
+  return (D == 64 || D == 128) && page_size % decode_tma::TILE == 0 && H / Kh <= 16;
+}
+
+// Decode: one token per sequence (batch row b is sequence b's token), keys and values by TMA.  With
+// n_splits > 1, part_o [B, H, n_splits, D] and part_ml [B, H, n_splits, 2] float32 are scratch.
+// cache_k / cache_v: [n_pages, Kh, page_size, D] bfloat16.
+RB_EXPORT int rb_attention_decode_tma(void* out, const void* q, const void* cache_k, const void* cache_v,
+                                      long long n_pages, const int* page_table, int max_pages, int page_size,
+                                      const int* tok_pos, const int* tok_slot, int B, int H, int Kh, int D,
+                                      float scale, int window, float* part_o, float* part_ml, int n_splits,
+                                      cudaStream_t stream) {
+  if (B == 0) return 0;
+  RB_REQUIRE(rb_attention_decode_tma_supports(H, Kh, D, page_size),
+             "rb_attention_decode_tma: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
+  RB_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 2147483647, "rb_attention_decode_tma: n_splits %d", n_splits);
+  RB_REQUIRE(n_splits == 1 || (part_o && part_ml), "rb_attention_decode_tma: split decode needs scratch");
+  CUtensorMap tk, tv;
+  const long long rows = n_pages * Kh * page_size;
+  if (rb_get_tensor_map(&tk, cache_k, rows, D, D, decode_tma::TILE) != 0) return -1;
+  if (rb_get_tensor_map(&tv, cache_v, rows, D, D, decode_tma::TILE) != 0) return -1;
+  decode_tma::Params p;
+  p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out;
+  p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size; p.n_kv_heads = Kh;
+  p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.H = H; p.G = H / Kh;
+  p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
+  p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
+  const int rc = D == 64 ? decode_tma::launch<64>(tk, tv, p, B, Kh, stream) : decode_tma::launch<128>(tk, tv, p, B, Kh, stream);
+  if (rc != 0) return rc;
+  if (n_splits > 1) return rb_attention_combine(out, part_o, part_ml, B, H, D, n_splits, stream);
+  return 0;
+}
+
 int rb_attention_tc_error_flag(int* value, int reset) { return rb_file_error_flag(value, reset); }
 int rb_attention_tc_error_flag_address(int** out) { return rb_file_error_flag_address(out); }
 

@@ -445,6 +445,14 @@ RB_EXPORT int rb_attention_prefill(void* out, const void* q, const void* cache_k
   return launch_d<false>(D, p, dim3(n_tiles, Kh, 1), stream);
 }
 
+// Merges the partials of a split decode (also for the TMA-fed decode kernel, which lives in another file).
+int rb_attention_combine(void* out, const float* part_o, const float* part_ml, int B, int H, int D, int n_splits,
+                         cudaStream_t stream) {
+  RB_LAUNCH("attn_combine_kernel", (attn_combine_kernel), B * H, (D + 31) / 32 * 32, 0, stream, (__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
+  RB_CHECK_LAUNCH("rb_attention_combine");
+  return 0;
+}
+
 // Decode: one token per sequence (batch row b is sequence b's token).  With n_splits > 1,
 // part_o [B, H, n_splits, D] and part_ml [B, H, n_splits, 2] float32 are scratch.
 RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k, const void* cache_v,
@@ -462,10 +470,7 @@ RB_EXPORT int rb_attention_decode(void* out, const void* q, const void* cache_k,
   p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
   p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
   if (launch_d<true>(D, p, dim3(B, Kh, n_splits), stream) != 0) return -1;
-  if (n_splits > 1) {
-    RB_LAUNCH("attn_combine_kernel", (attn_combine_kernel), B * H, (D + 31) / 32 * 32, 0, stream, (__nv_bfloat16*)out, part_o, part_ml, n_splits, D);
-    RB_CHECK_LAUNCH("rb_attention_combine");
-  }
+  if (n_splits > 1) return rb_attention_combine(out, part_o, part_ml, B, H, D, n_splits, stream);
   return 0;
 }
 

@@ -33,6 +33,7 @@ _SIGNATURES = {
     "rb_attention_prefill": [P, P, P, P, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
     "rb_attention_prefill_tc": [P, P, P, P, L, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
+    "rb_attention_decode_tma": [P, P, P, P, L, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
     "rb_attention_decode_static": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, I, P],
 }
 
@@ -53,6 +54,7 @@ class KernelLibrary:
         self.declare("rb_attention_tiled_supports", [I, I, I, I, I])
         self.declare("rb_attention_prefill_tc_supports", [I, I, I, I])
         self.declare("rb_gemm_tc_qkv_supports", [I, I, I])
+        self.declare("rb_attention_decode_tma_supports", [I, I, I, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

@@ -63,6 +63,8 @@ class CudaOps:
         self.lib = load(verbose=verbose_build)
         #: prefill attention of head sizes 64 and 128 runs on tcgen05 (else on the mma.sync kernel)
         self.prefill_on_tcgen05 = True
+        #: decode attention of head sizes 64 and 128 gets its keys and values by TMA (else by cp.async)
+        self.decode_on_tma = True
         self._flag_ptrs = None
 
     # ------------------------------------------------------------------ helpers
@@ -257,10 +259,18 @@ class CudaOps:
             if n_splits > 1:
                 part_o = torch.empty((T, H, n_splits, D), dtype=torch.float32, device=self.device)
                 part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=self.device)
-            self.lib.call("rb_attention_decode", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
-                          _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
-                          _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, _ptr(part_o), _ptr(part_ml),
-                          n_splits, self._stream(), launches=2 if n_splits > 1 else 1)
+            if self.decode_on_tma and self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size):
+                # keys and values by TMA (head sizes 64 and 128)
+                self.lib.call("rb_attention_decode_tma", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
+                              view.k.shape[0], _ptr(view.page_table), view.max_pages, view.page_size,
+                              _ptr(meta.tok_pos), _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win,
+                              _ptr(part_o), _ptr(part_ml), n_splits, self._stream(),
+                              launches=2 if n_splits > 1 else 1)
+            else:
+                self.lib.call("rb_attention_decode", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
+                              _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
+                              _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, _ptr(part_o), _ptr(part_ml),
+                              n_splits, self._stream(), launches=2 if n_splits > 1 else 1)
         elif self.dtype == torch.bfloat16 and self.prefill_on_tcgen05 and \
                 self.lib.raw("rb_attention_prefill_tc_supports")(H, Kh, D, view.page_size):
             tok0, ntok, n_tiles = self._prefill_tiles(meta, 128 // (H // Kh))

@@ -180,7 +180,8 @@ def _meta(rows, single_token=False, max_context=512):
 
 ATTN_CASES = [(4, 2, 16, 16, None), (3, 1, 32, 64, None), (6, 3, 48, 16, 5), (8, 2, 128, 64, None),
               (5, 5, 80, 32, 40), (2, 1, 256, 16, None), (6, 2, 64, 64, 100), (32, 8, 128, 128, None),
-              (7, 7, 96, 64, None), (4, 1, 112, 64, 33), (18, 1, 16, 64, None), (2, 2, 256, 64, None)]
+              (7, 7, 96, 64, None), (4, 1, 112, 64, 33), (18, 1, 16, 64, None), (2, 2, 256, 64, None),
+              (16, 1, 128, 64, 70), (12, 4, 64, 128, None)]
 
 
 @pytest.mark.parametrize("H,Kh,D,page,window", ATTN_CASES)
