@@ -19,7 +19,7 @@ namespace decode_tma {
 
 constexpr int TILE = 64;           // positions per tile = per TMA box
 constexpr int WARPS_D = 4;
-constexpr int NS = 2;              // stages of keys and values
+constexpr int NS = 2;              // stages of keys and values (three, with two CTAs per SM instead of three, measured slower)
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -126,10 +126,13 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
   // Every tile but the one that holds the newest position was written by earlier steps, so this
   // CTA's first tile can be on its way before the wait for the kernel that wrote the newest.
   const int newest = pos0 / TILE;
-  int n_early = 0;
-  if (threadIdx.x == 0 && kt_begin < kt_end && kt_begin != newest) {
-    request(kt_begin, 0);
-    n_early = 1;
+  int n_early = 0;                     // tiles requested before the wait (thread 0's count)
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NS - 1; ++i)
+      if (kt_begin + i < kt_end && kt_begin + i != newest && n_early == i) {
+        request(kt_begin + i, i);
+        n_early = i + 1;
+      }
   }
   rb_pdl_wait();
 
@@ -140,7 +143,9 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
     if (r < G) v = *reinterpret_cast<const uint4*>(p.q + ((int64_t)tok0 * H + kvh * G + r) * D + c * 8);
     *reinterpret_cast<uint4*>(sQ + r * LDQ + c * 8) = v;
   }
-  if (threadIdx.x == 0 && n_early == 0 && kt_begin < kt_end) request(kt_begin, 0);
+  if (threadIdx.x == 0)
+    for (int i = n_early; i < NS - 1; ++i)        // the rest of the first NS - 1 tiles
+      if (kt_begin + i < kt_end) request(kt_begin + i, i);
 
   // ---- per-warp state: all 16 rows, keys kw0 .. kw0+15 of every tile
   const int kw0 = warp * 16;
@@ -155,8 +160,8 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
 
   for (int kt = kt_begin; kt < kt_end; ++kt) {
     const int i = kt - kt_begin, buf = i % NS;
-    // the next tile goes into the other stage, which everybody left at the end of the last round
-    if (threadIdx.x == 0 && kt + 1 < kt_end) request(kt + 1, buf ^ 1);
+    // the tile NS - 1 ahead goes into the stage that everybody left at the end of the last round
+    if (threadIdx.x == 0 && kt + NS - 1 < kt_end) request(kt + NS - 1, (i + NS - 1) % NS);
     if (!failed && !mbar_wait(&full[buf], (uint32_t)((i / NS) & 1), 14)) failed = true;
     const uint32_t tK = smem_u32(smem + S::OFF_K + buf * S::TILE_BYTES);
     const uint32_t tV = smem_u32(smem + S::OFF_V + buf * S::TILE_BYTES);
