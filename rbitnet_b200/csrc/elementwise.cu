@@ -330,7 +330,7 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
 // eight rotation pairs (the same eight in every head), computes their sines and cosines once,
 // and walks over the heads with 16-byte loads and stores; values are copied 16 bytes at a time.
 constexpr int ROWS_MAX_PAIRS = 256;      // head sizes up to 512 take the many-token kernel
-__global__ void __launch_bounds__(256) rotate_append_rows_kernel(
+__global__ void __launch_bounds__(1024) rotate_append_rows_kernel(
     __nv_bfloat16* __restrict__ q_out, const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride,
     const float* __restrict__ inv_freq, const int* __restrict__ tok_pos, const int* __restrict__ tok_slot,
     RbPagedLayer cache, int H, int write_kv, int interleaved) {
@@ -346,21 +346,33 @@ __global__ void __launch_bounds__(256) rotate_append_rows_kernel(
   const int n_rot = H + (write_kv ? Kh : 0);
   __nv_bfloat16* kdst = (__nv_bfloat16*)cache.k;
   __nv_bfloat16* vdst = (__nv_bfloat16*)cache.v;
+  // element offsets of the two 16-byte pieces this thread rotates in every head
+  const int off_a = interleaved ? grp * 16 : grp * 8;
+  const int off_b = interleaved ? grp * 16 + 8 : D / 2 + grp * 8;
+  // the first head's values and the value rows are asked for before anything else, so that the loads
+  // run while the sines and cosines are made (with one thread per head and group that is all of them)
+  const bool active = lane < lanes && lane < n_rot;
+  uint4 va = make_uint4(0, 0, 0, 0), vb = va, vv = va;
+  if (active) {
+    va = *reinterpret_cast<const uint4*>(row + (int64_t)lane * D + off_a);
+    vb = *reinterpret_cast<const uint4*>(row + (int64_t)lane * D + off_b);
+  }
+  const int per_head = D / 8;
+  const bool copies = write_kv && (int)threadIdx.x < Kh * per_head;
+  if (copies) vv = *reinterpret_cast<const uint4*>(row + (int64_t)(H + Kh) * D + (int64_t)threadIdx.x * 8);
   // the token's D/2 sines and cosines, once per block
   __shared__ float s_sn[ROWS_MAX_PAIRS], s_cs[ROWS_MAX_PAIRS];
   for (int i = threadIdx.x; i < D / 2; i += blockDim.x) sincosf((float)pos * inv_freq[i], &s_sn[i], &s_cs[i]);
   __syncthreads();
-  if (lane < lanes) {
+  if (active) {
     float sn[8], cs[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) { sn[j] = s_sn[grp * 8 + j]; cs[j] = s_cs[grp * 8 + j]; }
-    // element offsets of the two 16-byte pieces this thread rotates in every head
-    const int off_a = interleaved ? grp * 16 : grp * 8;
-    const int off_b = interleaved ? grp * 16 + 8 : D / 2 + grp * 8;
     for (int head = lane; head < n_rot; head += lanes) {
-      const __nv_bfloat16* src = row + (int64_t)head * D;
-      uint4 va = *reinterpret_cast<const uint4*>(src + off_a);
-      uint4 vb = *reinterpret_cast<const uint4*>(src + off_b);
+      if (head != lane) {
+        va = *reinterpret_cast<const uint4*>(row + (int64_t)head * D + off_a);
+        vb = *reinterpret_cast<const uint4*>(row + (int64_t)head * D + off_b);
+      }
       __nv_bfloat16* ea = reinterpret_cast<__nv_bfloat16*>(&va);
       __nv_bfloat16* eb = reinterpret_cast<__nv_bfloat16*>(&vb);
       if (interleaved) {
@@ -389,11 +401,10 @@ __global__ void __launch_bounds__(256) rotate_append_rows_kernel(
   }
   if (write_kv) {
     const __nv_bfloat16* vsrc = row + (int64_t)(H + Kh) * D;
-    const int per_head = D / 8;
     for (int idx = threadIdx.x; idx < Kh * per_head; idx += blockDim.x) {
       const int kvh = idx / per_head, c = idx % per_head;
-      *reinterpret_cast<uint4*>(vdst + rb_page_offset(cache, slot, pos, kvh) + c * 8) =
-          *reinterpret_cast<const uint4*>(vsrc + (int64_t)kvh * D + c * 8);
+      if (idx != (int)threadIdx.x) vv = *reinterpret_cast<const uint4*>(vsrc + (int64_t)kvh * D + c * 8);
+      *reinterpret_cast<uint4*>(vdst + rb_page_offset(cache, slot, pos, kvh) + c * 8) = vv;
     }
   }
 }
@@ -420,7 +431,10 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 32 && D % 16 == 0 && D <= 2 * ROWS_MAX_PAIRS &&
       qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)cache_k % 16 == 0) && ((uintptr_t)cache_v % 16 == 0)) {
-    RB_LAUNCH("rotate_append_rows_kernel", (rotate_append_rows_kernel), T, 256, 0, stream, (__nv_bfloat16*)q_out,
+    // one thread per (rotated head, group of eight pairs) where a block can hold them: one pass over the heads
+    const int items = (H + (write_kv ? Kh : 0)) * (D / 16);
+    const int rows_threads = items >= 1024 ? 1024 : (items < 128 ? 128 : (items + 31) / 32 * 32);
+    RB_LAUNCH("rotate_append_rows_kernel", (rotate_append_rows_kernel), T, rows_threads, 0, stream, (__nv_bfloat16*)q_out,
               (const __nv_bfloat16*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
     return 0;
   }
