@@ -19,7 +19,6 @@ namespace decode_tma {
 
 constexpr int TILE = 64;           // positions per tile = per TMA box
 constexpr int WARPS_D = 4;
-constexpr int NS = 2;              // stages of keys and values (three, with two CTAs per SM instead of three, measured slower)
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -55,7 +54,10 @@ struct Params {
   int n_splits;
 };
 
-template <int D> struct Smem {
+// NS: stages of keys and values.  Two stages let three CTAs share an SM, three stages two: the
+// launcher takes three when the whole grid fits two CTAs per SM at once (a small batch), where one
+// more tile in flight per CTA counts for more than a third CTA, and two otherwise.
+template <int D, int NS> struct Smem {
   static constexpr int DB = D / 64;                      // 64-value blocks of a head
   static constexpr int BLOCK = TILE * 128;               // [64 positions][128 bytes]
   static constexpr int TILE_BYTES = DB * BLOCK;          // keys (or values) of one tile
@@ -73,14 +75,14 @@ template <int D> struct Smem {
 // byte offset of element (row, col) of a tile: 64-value blocks of [64 rows][128 bytes] whose
 // 16-byte chunks are exchanged by the row's low three bits (the 128-byte swizzle of the TMA box)
 template <int D> __device__ __forceinline__ uint32_t tile_off(int row, int col) {
-  return (uint32_t)((col >> 6) * Smem<D>::BLOCK + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + (col & 7) * 2);
+  return (uint32_t)((col >> 6) * (TILE * 128) + row * 128 + (((((col & 63) >> 3) ^ (row & 7))) << 4) + (col & 7) * 2);
 }
 
-template <int D>
+template <int D, int NS>
 __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK,
                                                                       const __grid_constant__ CUtensorMap tmV, Params p) {
   rb_pdl_launch_dependents();
-  using S = Smem<D>;
+  using S = Smem<D, NS>;
   constexpr int DB = S::DB, LDQ = S::LDQ;
   constexpr int NT = 2;                       // 8-key column tiles of S per warp (16 keys)
   constexpr int DT = D / 8;                   // 8-wide column tiles of O
@@ -286,10 +288,10 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
   }
 }
 
-template <int D>
-int launch(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B, int Kh, cudaStream_t stream) {
-  auto kernel = attn_decode_tma_kernel<D>;
-  constexpr int smem = Smem<D>::BYTES;
+template <int D, int NS>
+int launch_ns(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B, int Kh, cudaStream_t stream) {
+  auto kernel = attn_decode_tma_kernel<D, NS>;
+  constexpr int smem = Smem<D, NS>::BYTES;
   static bool configured = false;
   if (!configured) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -297,6 +299,23 @@ int launch(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B,
   }
   RB_LAUNCH("rb_attention_decode_tma", (kernel), dim3(B, Kh, p.n_splits), WARPS_D * 32, smem, stream, tk, tv, p);
   return 0;
+}
+
+// CTAs that run together when each SM takes two (the three-stage kernel) and three (two stages).
+inline int places(int per_sm) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  return sms * per_sm;
+}
+
+template <int D>
+int launch(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B, int Kh, cudaStream_t stream) {
+  if ((long long)B * Kh * p.n_splits <= places(2)) return launch_ns<D, 3>(tk, tv, p, B, Kh, stream);
+  return launch_ns<D, 2>(tk, tv, p, B, Kh, stream);
 }
 
 }  // namespace decode_tma

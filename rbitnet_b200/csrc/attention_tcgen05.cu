@@ -479,6 +479,26 @@ RB_EXPORT int rb_attention_decode_tma_supports(int H, int Kh, int D, int page_si
   return (D == 64 || D == 128) && page_size % decode_tma::TILE == 0 && H / Kh <= 16;
 }
 
+// The number of parts to cut the keys of a decode into, for `pairs` = sequences x kv heads and
+// `tiles` 64-key tiles of the longest context: as many as fill one wave of two CTAs per SM (the
+// three-stage kernel) when the pairs fit such a wave; one when they fit a wave of three per SM; else
+// the count (up to 16) that fills whole waves of three per SM best.
+RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
+  if (pairs <= 0 || tiles <= 0) return 1;
+  const int two = decode_tma::places(2), three = decode_tma::places(3);
+  const int most = tiles < 16 ? tiles : 16;
+  if (pairs <= two) { const int s = two / pairs; return s < 1 ? 1 : (s > most ? most : s); }
+  if (pairs <= three) return 1;
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= most; ++s) {
+    const long long ctas = (long long)pairs * s;
+    const double eff = (double)ctas / (double)(((ctas + three - 1) / three) * three);
+    if (eff > best_eff + 0.02) { best = s; best_eff = eff; }
+  }
+  return best;
+}
+
 // Decode: one token per sequence (batch row b is sequence b's token), keys and values by TMA.  With
 // n_splits > 1, part_o [B, H, n_splits, D] and part_ml [B, H, n_splits, 2] float32 are scratch.
 // cache_k / cache_v: [n_pages, Kh, page_size, D] bfloat16.

@@ -254,12 +254,16 @@ class CudaOps:
         win = int(window or 0)
         if self.dtype == torch.bfloat16 and meta.single_token and \
                 self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 1):
-            n_splits = self._decode_splits(T, Kh, meta.max_context)
+            on_tma = self.decode_on_tma and self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size)
+            if on_tma:
+                n_splits = self.lib.raw("rb_attention_decode_tma_parts")(T * Kh, max(1, -(-meta.max_context // 64)))
+            else:
+                n_splits = self._decode_splits(T, Kh, meta.max_context)
             part_o = part_ml = None
             if n_splits > 1:
                 part_o = torch.empty((T, H, n_splits, D), dtype=torch.float32, device=self.device)
                 part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=self.device)
-            if self.decode_on_tma and self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size):
+            if on_tma:
                 # keys and values by TMA (head sizes 64 and 128)
                 self.lib.call("rb_attention_decode_tma", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
                               view.k.shape[0], _ptr(view.page_table), view.max_pages, view.page_size,
