@@ -10,11 +10,13 @@
 //
 // Roles in a CTA of 192 threads: warp 0 issues TMA loads into a ring of stages, warp 1 owns the
 // tensor memory and issues tcgen05.mma (one lane), warps 2..5 read the accumulators back with
-// tcgen05.ld and write the result.  K may be split over gridDim.z; then each split writes its
-// own float32 slice and the consumer adds the slices in a fixed order.
+// tcgen05.ld and write the result.  For at most 64 tokens K may be cut into 2..8 parts: the CTAs
+// of a tile then form a thread-block cluster, and after their products each of them adds up a
+// share of the token columns from all parts, in part order, through distributed shared memory.
 //
 // Epilogues: plain store (bfloat16 or float32), add into a float32 matrix (the residual stream,
 // crates/bitnet-core/src/llama/model.rs:291-294, :303-306), float32 slices of a split product,
+// the q/k/v product of a decode step that rotates and appends to the cache (QkvTail below),
 // and SiLU(gate)*up (model.rs:297-302) from ONE accumulator: the caller interleaves the rows of the
 // gate and up matrices in blocks of 16, so that each warp of the epilogue holds 16 gate rows in its
 // lower lanes and the 16 up rows of the same features in its upper lanes, and a shuffle pairs them.
