@@ -349,9 +349,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncwarp();
     cluster_sync_all();
     if (EPI == EPI_QKV && warp >= 2 && first_item < p.n_items) {
-      // As below, every CTA of the cluster adds up its share of the token columns; a thread also adds
-      // up the row that its own row is rotated with (both lie in this tile: the head size divides
-      // 128), rotates in float32 and writes the one rounded result where it belongs.
+      // As below, every CTA of the cluster adds up its share of the token columns (column c belongs
+      // to rank c mod splits).  The sums of this CTA's columns are then parked in its own shared
+      // memory, behind the accumulators, so that a thread finds there the sum of the row its own row
+      // is rotated with (both lie in this tile: the head size divides 128).  It rotates in float32
+      // and writes the one rounded result where it belongs.  All four epilogue warps pass the
+      // barrier between the two steps, whatever their rows.
+      static_assert(BN > 64 || 2 * BN * BM * 4 <= STAGES * STAGE_BYTES, "the ring holds the accumulators and the sums");
       int n0, t0, kb_begin, nkb, split;
       item_of(first_item, n0, t0, kb_begin, nkb, split);
       const QkvTail& q = p.qkv;
@@ -362,32 +366,47 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       bool first;
       if (q.interleaved) { pair = d >> 1; first = (d & 1) == 0; prow = row ^ 1; }
       else { pair = d % (D / 2); first = d < D / 2; prow = first ? row + D / 2 : row - D / 2; }
-      const bool is_v = n >= HD + KD;
-      uint32_t own[8], other[8];
+      const bool is_v = n >= HD + KD, live = n < p.n_out;
+      float* sums = reinterpret_cast<float*>(smem) + BN * BM;       // [column][row], this CTA's columns only
+      uint32_t own[8];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const uint32_t rank = (uint32_t)(r < p.splits ? r : 0);
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(own[r]) : "r"(smem_u32(smem) + (uint32_t)row * 4), "r"(rank));
-        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(other[r]) : "r"(smem_u32(smem) + (uint32_t)prow * 4), "r"(rank));
-      }
-      if (n < p.n_out) {
-        const float inv = is_v ? 0.f : q.inv_freq[pair];
-        for (int col = my; col < BN && t0 + col < p.n_tokens; col += p.splits) {
-          float a[8], b[8];
+      for (int r = 0; r < 8; ++r)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(own[r]) : "r"(smem_u32(smem) + (uint32_t)row * 4), "r"((uint32_t)(r < p.splits ? r : 0)));
+      constexpr int CPI = BN >= 64 ? 4 : 2;                          // columns whose loads are in flight together
+      if (live) {
+        for (int cb = my; cb < BN && t0 + cb < p.n_tokens; cb += CPI * p.splits) {
+          float part[CPI][8];
 #pragma unroll
-          for (int r = 0; r < 8; ++r) {        // all loads first, then the sums in split order
-            a[r] = 0.f; b[r] = 0.f;
-            if (r < p.splits) {
-              asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(a[r]) : "r"(own[r] + (uint32_t)(col * BM) * 4));
-              if (!is_v) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(b[r]) : "r"(other[r] + (uint32_t)(col * BM) * 4));
+          for (int h = 0; h < CPI; ++h) {
+            const int col = cb + h * p.splits;
+            const bool ok = col < BN && t0 + col < p.n_tokens;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {      // all loads first, then the sums in split order
+              part[h][r] = 0.f;
+              if (ok && r < p.splits)
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(part[h][r]) : "r"(own[r] + (uint32_t)(col * BM) * 4));
             }
           }
-          float x = a[0], xp = b[0];
 #pragma unroll
-          for (int r = 1; r < 8; ++r) { x += a[r]; xp += b[r]; }
+          for (int h = 0; h < CPI; ++h) {
+            const int col = cb + h * p.splits;
+            if (col >= BN || t0 + col >= p.n_tokens) continue;
+            float x = part[h][0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) x += part[h][r];
+            sums[col * BM + row] = x;
+          }
+        }
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");                 // the four epilogue warps
+      if (live) {
+        const float inv = is_v ? 0.f : q.inv_freq[pair];
+        for (int col = my; col < BN && t0 + col < p.n_tokens; col += p.splits) {
+          const float x = sums[col * BM + row];
           const int t = t0 + col, pos = q.tok_pos[t];
           float y = x;
           if (!is_v) {
+            const float xp = sums[col * BM + prow];
             float sn, cs;
             sincosf((float)pos * inv, &sn, &cs);
             y = first ? x * cs - xp * sn : xp * sn + x * cs;
@@ -668,13 +687,14 @@ RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64
 }
 
 // Whether rb_gemm_tc_qkv takes these sizes: a head may not straddle two 128-row tiles of W, and the
-// product must be one that is split along K (2..8 parts).  At most 16 tokens: with more, the
-// rotation in the epilogue (measured at 64) costs more than the kernel it saves.
+// product must be one that is split along K (2..8 parts).  At most 16 tokens: with 64, the rotation
+// in the epilogue (also with the sines and cosines made once per step) measured slower than the
+// rotation kernel it saves (9,490 against 9,840 tokens/s).
 RB_EXPORT int rb_gemm_tc_qkv_supports(int n_tokens, int D, int splits) {
   return n_tokens >= 1 && n_tokens <= 16 && splits >= 2 && splits <= 8 && D >= 2 && D % 2 == 0 && BM % D == 0;
 }
 
-// The q/k/v product of up to 64 tokens with rotation and cache append in its epilogue (see QkvTail).
+// The q/k/v product of up to 16 tokens with rotation and cache append in its epilogue (see QkvTail).
 // W: [H*D + (write_kv ? 2*Kh*D : 0), K].  K is cut into `splits` >= 2 parts (one cluster per tile).
 RB_EXPORT int rb_gemm_tc_qkv(void* q_out, const void* X, int64_t ldx, int n_tokens, const void* W, int64_t ldw, int K,
                              int splits, const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
