@@ -278,6 +278,9 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip prefill and the batch 1/64 points")
     ap.add_argument("--phase", default="all", choices=["all", "prefill"],
                     help="'prefill': only the 2,048-token prefill, one short line (for profiling)")
+    ap.add_argument("--context", type=int, default=PROMPT_LEN,
+                    help="cached positions per sequence when the decode steps begin (default: the 2,048 of the headline; "
+                         "other values are for further measurements and are named in config.seq_len)")
     ap.add_argument("--prefill-tokens", type=int, default=PROMPT_LEN,
                     help="with --phase prefill: the prompt's length (up to 8,000), for profiling other lengths")
     ap.add_argument("--timeline", action="store_true",
@@ -304,7 +307,8 @@ def main():
     cfg = dict(MODEL, num_hidden_layers=args.layers)
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     room = steps + warmup + 16
-    max_tokens = max(b * (-(-(PROMPT_LEN + room) // 64) * 64) for b in batches) + 64 * 64
+    ctx = max(1, min(8192 - room, args.context))
+    max_tokens = max(b * (-(-(max(ctx, PROMPT_LEN) + room) // 64) * 64) for b in batches) + 64 * 64
     t_build = time.time()
     engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seq=8192, max_batch=64)
     for g in engine.cache.groups:                   # random cache content; finite values, no work depends on it
@@ -313,7 +317,7 @@ def main():
     build_s = time.time() - t_build
 
     if args.timeline:
-        print_timeline(engine, args.batch, PROMPT_LEN)
+        print_timeline(engine, args.batch, ctx)
         return 0
     if args.phase == "prefill":
         n_tok = max(1, min(8000, args.prefill_tokens))
@@ -324,15 +328,15 @@ def main():
 
     sampler = ClockSampler().start()
     try:
-        ms, launches, clocks = time_decode(engine, args.batch, PROMPT_LEN, steps, warmup, sampler)
-        e2e_ms, h2d, d2h = time_decode_e2e(engine, args.batch, PROMPT_LEN, steps, warmup)
+        ms, launches, clocks = time_decode(engine, args.batch, ctx, steps, warmup, sampler)
+        e2e_ms, h2d, d2h = time_decode_e2e(engine, args.batch, ctx, steps, warmup)
         points, prefill = {}, None
         if not args.no_points:
             for b in (1, 64):
                 if b == args.batch:
                     points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
                 else:
-                    pms, _, _ = time_decode(engine, b, PROMPT_LEN, max(8, steps // 2), warmup)
+                    pms, _, _ = time_decode(engine, b, ctx, max(8, steps // 2), warmup)
                     points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
             pf_ms = time_prefill(engine, PROMPT_LEN)
             flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
@@ -342,11 +346,11 @@ def main():
     finally:
         sampler.stop()
 
-    nbytes = decode_bytes(engine, args.batch, PROMPT_LEN)
+    nbytes = decode_bytes(engine, args.batch, ctx)
     achieved = nbytes / (ms * 1e-3) / 1e9
     value = args.batch / ms * 1e3
     line = {
-        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "metric": METRIC if ctx == PROMPT_LEN else METRIC.replace("2048-token", f"{ctx}-token"), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cache)",
         "impl": "ours",
@@ -355,7 +359,7 @@ def main():
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False,
-                   "global_batch": args.batch, "seq_len": PROMPT_LEN, "max_context": 8192,
+                   "global_batch": args.batch, "seq_len": ctx, "max_context": 8192,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read once per step)",
                    "step": "one decode token per sequence, CUDA graph, sampled on device"},
         "e2e": {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
