@@ -37,6 +37,7 @@ class DecodeGraph:
         self.error_code = 0
         self.meta = StepMeta(self.token_ids, self.tok_pos, self.tok_slot, self.want, B, B,
                              [SeqChunk(0, 0, 1, i) for i in range(B)], True, cache.max_seq)
+        self.meta.want_every_row = True     # the wanted rows are 0 .. B-1, always
         self.graph = None
         self.sampled = None
         self.kernels = 0

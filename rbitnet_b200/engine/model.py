@@ -82,6 +82,6 @@ class Model:
             self.blocks[entry.layer].run(ctx, x, e)
         if meta.n_want == 0:
             return None
-        rows = ops.gather_rows(x, meta.want_rows)
+        rows = x if meta.want_every_row else ops.gather_rows(x, meta.want_rows)
         h = self.final_norm.forward(ctx, rows)
         return ops.linear(h, self.head, out_dtype=torch.float32)

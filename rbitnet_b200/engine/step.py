@@ -49,6 +49,7 @@ class StepMeta:
     single_token: bool              # every sequence brings exactly one token
     max_context: int                # longest sequence length after this batch
     extra: dict = field(default_factory=dict)
+    want_every_row: bool = False    # want_rows is 0, 1, .., n_tokens-1: the rows need no gathering
 
 
 class StepContext:
@@ -72,9 +73,11 @@ def build_meta(chunks: List[SeqChunk], tokens: np.ndarray, want_rows: np.ndarray
     R = int(want_rows.shape[0])
     packed = np.concatenate([tokens.astype(np.int32), pos, slot, want_rows.astype(np.int32)])
     dev = torch.from_numpy(packed).to(device)       # pageable copy: staged before the call returns
-    return StepMeta(dev[0:T], dev[T:2 * T], dev[2 * T:3 * T], dev[3 * T:3 * T + R], T, R, chunks,
+    meta = StepMeta(dev[0:T], dev[T:2 * T], dev[2 * T:3 * T], dev[3 * T:3 * T + R], T, R, chunks,
                     all(c.n_new == 1 for c in chunks),
                     max((c.start + c.n_new for c in chunks), default=0))
+    meta.want_every_row = R == T and bool(np.array_equal(want_rows, np.arange(T)))
+    return meta
 
 
 class Stepper:
