@@ -112,6 +112,31 @@ class SequenceCache:
     def advance(self, slot: int, n_new: int) -> None:
         self.book.advance(slot, n_new)
 
+    def lengths(self, slots) -> list:
+        length = self.book.length
+        return [length[s] for s in slots]
+
+    def reserve_one_each(self, slots) -> None:
+        """Room for one more position in each slot: the decode step's call, which finds room in the
+        last page nearly always and then touches nothing."""
+        book = self.book
+        page, pages, length, most = book.page_size, book.pages, book.length, book.max_seq
+        for s in slots:
+            want = length[s] + 1
+            if want > most:
+                self.reserve(s, 1)           # raises ContextOverflow
+                continue
+            for pg in pages[s]:
+                if want > len(pg) * page:
+                    self.reserve(s, 1)
+                    break
+
+    def advance_one_each(self, slots) -> None:
+        """After ``reserve_one_each``: every slot holds one position more."""
+        length = self.book.length
+        for s in slots:
+            length[s] += 1
+
     def fits(self, lengths) -> bool:
         """Whether new sequences that grow to these lengths fit beside what is live now."""
         if len(lengths) > self.book.slots.n_free:

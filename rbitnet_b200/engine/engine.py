@@ -189,9 +189,8 @@ class Engine:
 
     def _decode_step(self, feed, temperatures, uniforms) -> List[int]:
         slots = [s for s, _ in feed]
-        positions = [self.cache.length(s) for s in slots]
-        for s in slots:
-            self.cache.reserve(s, 1)
+        positions = self.cache.lengths(slots)
+        self.cache.reserve_one_each(slots)
         n = len(feed)
         tokens = [t[0] for _, t in feed]
         temperatures, uniforms = list(temperatures), list(uniforms)
@@ -219,8 +218,7 @@ class Engine:
         ids = g.read()[:n]
         if g.error_code:
             self.ops.check_errors()            # raises with the code, and clears the word
-        for s in slots:
-            self.cache.advance(s, 1)
+        self.cache.advance_one_each(slots)
         return ids
 
     def _step_sample(self, feed, temperatures, uniforms) -> List[int]:

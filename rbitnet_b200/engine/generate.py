@@ -18,7 +18,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
-from ..sampling.rng import uniform
+from ..sampling.rng import uniforms
 
 
 @dataclass
@@ -89,7 +89,10 @@ class GenerationLoop:
                 self.prefill_tokens += sum(len(t) for _, t in feed)
                 while live:
                     temps = [temperature] * len(live)
-                    us = [uniform(seed, s.request, len(s.out)) for s in live]
+                    if temperature > 0:          # a draw per request, a function of (seed, request, tokens so far)
+                        us = uniforms(seed, [s.request for s in live], [len(s.out) for s in live]).tolist()
+                    else:
+                        us = [0.0] * len(live)   # the arg-max needs none
                     sampled = self.step_sample(feed, temps, us)
                     self.steps += 1
                     still: List[_Live] = []

@@ -2,6 +2,6 @@
 inverse CDF (crates/bitnet-core/src/llama/runtime.rs:81-107); the reference has no
 other sampling option (no top-k, top-p or penalties), and neither has this
 library.  The choice itself is a CUDA kernel (``CudaOps.sample``)."""
-from .rng import uniform
+from .rng import uniform, uniforms
 
-__all__ = ["uniform"]
+__all__ = ["uniform", "uniforms"]

@@ -22,3 +22,21 @@ def uniform(seed: int, request: int, step: int) -> float:
     """A float32-exact number in [0, 1)."""
     h = _mix(_mix(_mix(seed & _M) ^ (request & _M)) ^ (step & _M))
     return (h >> 40) / float(1 << 24)
+
+
+def uniforms(seed: int, requests, steps):
+    """``uniform(seed, r, s)`` for every pair of the two equally long sequences, as float32 values
+    in a numpy array (the same numbers, made with wrapping 64-bit integer arithmetic)."""
+    import numpy as np
+    r = np.asarray(requests, dtype=np.uint64)
+    t = np.asarray(steps, dtype=np.uint64)
+
+    def mix(x):
+        x = x + np.uint64(0x9E3779B97F4A7C15)
+        x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return x ^ (x >> np.uint64(31))
+
+    with np.errstate(over="ignore"):
+        h = mix(mix(np.uint64(_mix(seed & _M)) ^ r) ^ t)
+    return ((h >> np.uint64(40)).astype(np.float64) / float(1 << 24)).astype(np.float32)

@@ -216,3 +216,41 @@ def test_uniform_depends_on_seed_request_and_step_only():
     assert uniform(2, 0, 0) != uniform(1, 0, 0)
     assert abs(sum(uniform(3, 0, s) for s in range(4000)) / 4000 - 0.5) < 0.03
     assert all(float(torch.tensor(u, dtype=torch.float32)) == u for u in a)   # exact in float32
+
+
+def test_uniforms_for_a_batch_are_the_single_draws():
+    from rbitnet_b200.sampling import uniforms
+    for seed in (0, 7, 2 ** 63 + 5, 12345678901234567890):
+        reqs, steps = [0, 1, 2, 63, 1000, 2 ** 40], [0, 5, 7, 1023, 99999, 3]
+        got = uniforms(seed, reqs, steps)
+        assert got.dtype.name == "float32"
+        assert got.tolist() == [uniform(seed, r, s) for r, s in zip(reqs, steps)]
+    assert uniforms(1, [], []).shape == (0,)
+
+
+def test_the_decode_step_s_bookkeeping_of_many_slots_is_that_of_one_slot_at_a_time():
+    """reserve_one_each / advance_one_each against reserve / advance: same lengths, same pages, same
+    rows marked for upload, page after page; and the same error at the end of a sequence's room."""
+    def make():
+        return SequenceCache({0: CacheNeed(1, 8), 1: CacheNeed(1, 8, window=4)}, reads={}, state_needs={},
+                             max_tokens=256, max_seq=40, dtype=torch.float32, device="cpu", page_size=16)
+    a, b = make(), make()
+    sa, sb = [a.alloc() for _ in range(3)], [b.alloc() for _ in range(3)]
+    for c, slots in ((a, sa), (b, sb)):
+        for s, n in zip(slots, (1, 15, 16)):
+            c.reserve(s, n)
+            c.advance(s, n)
+    for step in range(24):
+        a.reserve_one_each(sa)
+        for s in sb:
+            b.reserve(s, 1)
+        assert a.lengths(sa) == [b.length(s) for s in sb]
+        assert [a.book.pages[s] for s in sa] == [b.book.pages[s] for s in sb]
+        assert [sorted(g.dirty) for g in a.groups] == [sorted(g.dirty) for g in b.groups]
+        a.advance_one_each(sa)
+        for s in sb:
+            b.advance(s, 1)
+        assert a.lengths(sa) == [b.length(s) for s in sb]
+    assert a.lengths(sa) == [25, 39, 40]
+    with pytest.raises(ContextOverflow):
+        a.reserve_one_each(sa)            # the third slot is full
