@@ -352,6 +352,138 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path, dt
         unregister_part("mixer", "toy_decay")
 
 
+# --------------------------------------------------------------------------- a toy feed-forward with routing
+def _routed_plain(cfg, tensors, tokens, n_experts):
+    """Plain whole-sequence forward of the toy model below: ordinary layers, but the last layer's
+    feed-forward sends every token to the one expert (two matrices with a ReLU between) whose router
+    logit is largest.  Returns the logits and, per token, how far the two largest router logits are
+    apart relative to the largest magnitude (a near tie may go either way under rounding)."""
+    c = plain.normalise_config(cfg)
+    t64 = {k: v.double() for k, v in tensors.items()}
+    ids = torch.as_tensor(tokens, dtype=torch.long)
+    x = t64["model.embed_tokens.weight"][ids]
+    pos = torch.arange(len(tokens))
+    L = c["num_hidden_layers"]
+    for i in range(L - 1):
+        x, _ = plain.block(x, plain.layer_weights(t64, i, torch.float64), c, pos)
+    lp = f"model.layers.{L - 1}."
+    lw = {k: t64[lp + f"self_attn.{k}_proj.weight"] for k in ("q", "k", "v", "o")}
+    x = x + plain.attention_mixer(plain.rmsnorm(x, t64[lp + "input_layernorm.weight"], c["rms_norm_eps"]), lw, c, pos)[0]
+    h = plain.rmsnorm(x, t64[lp + "post_attention_layernorm.weight"], c["rms_norm_eps"])
+    pre = lp + "mlp."
+    logits = h @ t64[pre + "router.weight"].T
+    top = torch.topk(logits, 2, dim=1).values
+    gap = (top[:, 0] - top[:, 1]) / logits.abs().max(dim=1).values
+    choice = logits.argmax(dim=1)
+    y = torch.zeros_like(x)
+    for t in range(len(tokens)):
+        e = int(choice[t])
+        y[t] = t64[pre + "w2.weight"][e] @ torch.relu(t64[pre + "w1.weight"][e] @ h[t])
+    x = x + y
+    xn = plain.rmsnorm(x, t64["model.norm.weight"], c["rms_norm_eps"])
+    return xn @ t64["lm_head.weight"].T, gap
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_feed_forward_with_routing_can_be_registered_built_and_stepped(tmp_path, dtype):
+    """A feed-forward that chooses one of several experts per token (router logits in float32), defined
+    here and put into the last layer of an otherwise ordinary model, without a change to the library:
+    prompts of unequal lengths, tokens one by one, and captured decode steps through generate()."""
+    from rbitnet_b200 import Engine, StepEntry
+    from rbitnet_b200.config import LlamaConfig, register_architecture, unregister_architecture
+    from rbitnet_b200.models.llama import build_llama_spec
+    from rbitnet_b200.parts import FeedForward, PartSpec, register_part, unregister_part
+    from rbitnet_b200.weights import random_tensors, write_safetensors
+    N_EXPERTS, INNER = 3, 40
+
+    class RoutedExperts(FeedForward):
+        """Written with torch on the device, with shapes that do not depend on the routing (every
+        expert runs on every row and a mask keeps the chosen one), so that it works inside a
+        captured step: a test part, not a kernel."""
+
+        def __init__(self, width, inner, n_experts):
+            self.width, self.inner, self.n = width, inner, n_experts
+
+        def weight_shapes(self):
+            return {"router": ((self.n, self.width), "matrix"), "w1": ((self.n, self.inner, self.width), "matrix"),
+                    "w2": ((self.n, self.width, self.inner), "matrix")}
+
+        def bind(self, weights, ops):
+            self.router, self.w1, self.w2 = (weights[k].to(torch.float32) for k in ("router", "w1", "w2"))
+
+        def forward(self, ctx, h, accumulate_into):
+            hf = h.to(torch.float32)
+            choice = (hf @ self.router.T).argmax(dim=1)                       # float32 logits
+            for e in range(self.n):
+                y = torch.relu(hf @ self.w1[e].T) @ self.w2[e].T
+                accumulate_into += y * (choice == e).to(torch.float32)[:, None]
+
+    @dataclass
+    class RoutedConfig(LlamaConfig):
+        architecture: ClassVar[str] = "ToyRoutedLM"
+
+    def build(cfg):
+        spec = build_llama_spec(cfg)
+        last = spec.layers[-1]
+        last.feed_forward = PartSpec("toy_routed", {"width": cfg.hidden_size, "inner": INNER, "n_experts": N_EXPERTS})
+        names = {k: v for k, v in last.names.items() if not k.startswith("feed_forward.")}
+        i = len(spec.layers) - 1
+        for k in ("router", "w1", "w2"):
+            names[f"feed_forward.{k}"] = f"model.layers.{i}.mlp.{k}.weight"
+        last.names = names
+        return spec
+
+    register_part("feed_forward", "toy_routed", RoutedExperts, replace=True)
+    register_architecture("ToyRoutedLM", RoutedConfig, build, replace=True)
+    try:
+        cfgd = dict(TINY_B, architectures=["ToyRoutedLM"], num_hidden_layers=2)
+        folder = tmp_path / "routed"
+        folder.mkdir()
+        cfg = RoutedConfig.from_dict(cfgd)
+        tensors = random_tensors(build(cfg), 9)
+        tensors["model.layers.1.mlp.router.weight"] *= 30          # router logits of order one
+        tensors["model.layers.1.mlp.w1.weight"] *= 8
+        tensors["model.layers.1.mlp.w2.weight"] *= 8
+        tensors = {k: v.to(DTYPES[dtype]) for k, v in tensors.items()}
+        (folder / "config.json").write_text(json.dumps(cfgd))
+        write_safetensors(folder / "model.safetensors", tensors)
+        eng = Engine.load_path(folder, dtype=dtype, max_tokens=1024)
+        pc, pt = plain.load_folder(folder)
+        min_gap = 1e-4 if dtype == "float32" else 5e-2
+        compared = 0
+        for round_ in range(2):                                 # the second round uses the slots again
+            ps = prompts([30, 5, 12], cfgd["vocab_size"], 50 + round_)
+            lens = [20, 1, 6]
+            slots = [eng.new_sequence() for _ in ps]
+            got = [[] for _ in ps]
+            out = eng.step([StepEntry(s, p[:n], list(range(n))) for s, p, n in zip(slots, ps, lens)])
+            off = 0
+            for i, n in enumerate(lens):
+                got[i].append(out[off:off + n])
+                off += n
+            for k in range(4):
+                out = eng.step([StepEntry(s, [p[n + k]], [0]) for s, p, n in zip(slots, ps, lens)])
+                for i in range(len(ps)):
+                    got[i].append(out[i:i + 1])
+            for i, (p, n) in enumerate(zip(ps, lens)):
+                want, gap = _routed_plain(pc, pt, p[:n + 4], N_EXPERTS)
+                clear = gap > min_gap                            # the routed layer is the last: a near tie touches only its own row
+                assert int(clear.sum()) >= (n + 4) * 3 // 4
+                assert_close(torch.cat(got[i]).cpu()[clear], want[clear], dtype, f"routed model round {round_} request {i}")
+                compared += int(clear.sum())
+            for s in slots:
+                eng.end_sequence(s)
+        assert compared > 60
+        probe = torch.randn(64, cfg.hidden_size) @ tensors["model.layers.1.mlp.router.weight"].float().T
+        assert len(set(probe.argmax(dim=1).tolist())) == N_EXPERTS        # the router does choose
+        # generation (captured decode steps) runs the routed part too
+        res = eng.generate([ps[0][:9], ps[2][:4]], max_tokens=5, temperature=0.0)
+        assert all(len(r.tokens) == 5 for r in res)
+    finally:
+        unregister_architecture("ToyRoutedLM")
+        unregister_part("feed_forward", "toy_routed")
+
+
 @pytest.mark.parametrize("head_dim,theta", [(16, 10000.0), (48, 500000.0), (128, 1e6)])
 def test_position_encoding_part(head_dim, theta):
     """The rotary part's inverse frequencies are the reference's 1/theta^(2i/D) in float32
