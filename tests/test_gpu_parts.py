@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_llama as plain
-from helpers import assert_close, make_model_dir, PlainModel
+from helpers import assert_close, make_model_dir, PlainModel, sharpen
 from tiny import TINY_A, TINY_B, prompts
 
 pytestmark = pytest.mark.gpu
@@ -482,6 +482,87 @@ def test_a_toy_feed_forward_with_routing_can_be_registered_built_and_stepped(tmp
     finally:
         unregister_architecture("ToyRoutedLM")
         unregister_part("feed_forward", "toy_routed")
+
+
+# --------------------------------------------------------------------------- a toy position encoding
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_position_encoding_can_be_registered_built_and_stepped(tmp_path, dtype, monkeypatch):
+    """Another position encoding, defined here: the pairs of a head are rotated with frequencies that
+    fall off linearly (1 / (1 + slope * i)) instead of geometrically.  Every attention layer of an
+    otherwise ordinary model takes it by name; whole prompts, tokens one by one (where the q/k/v
+    product's own epilogue rotates), and generation, against the plain model with the same angles."""
+    from rbitnet_b200 import Engine, StepEntry
+    from rbitnet_b200.config import LlamaConfig, register_architecture, unregister_architecture
+    from rbitnet_b200.models.llama import build_llama_spec
+    from rbitnet_b200.parts import PositionEncoding, register_part, unregister_part
+    from rbitnet_b200.weights import random_tensors, write_safetensors
+
+    def frequencies(head_dim, slope):
+        return 1.0 / (1.0 + slope * torch.arange(head_dim // 2, dtype=torch.float32))
+
+    class LinearFrequencies(PositionEncoding):
+        def __init__(self, head_dim, slope, pairing):
+            self.head_dim, self.slope, self.pairing = head_dim, slope, pairing
+
+        def bind(self, weights, ops):
+            self.inv_freq = frequencies(self.head_dim, self.slope).to(ops.device)
+
+        def rotary(self):
+            return self.inv_freq, self.pairing == "interleaved", self.head_dim
+
+    @dataclass
+    class ToyConfig(LlamaConfig):
+        architecture: ClassVar[str] = "ToyLinearRopeLM"
+        slope: float = 0.5
+
+    def build(cfg):
+        spec = build_llama_spec(cfg)
+        for layer in spec.layers:
+            layer.mixer.params["position"] = {"kind": "toy_linear_frequencies",
+                                              "params": {"head_dim": cfg.head_dim, "slope": cfg.slope,
+                                                         "pairing": cfg.rope_pairing}}
+        return spec
+
+    register_part("position", "toy_linear_frequencies", LinearFrequencies, replace=True)
+    register_architecture("ToyLinearRopeLM", ToyConfig, build, replace=True)
+    try:
+        cfgd = dict(TINY_A, architectures=["ToyLinearRopeLM"], slope=0.25)
+        folder = tmp_path / "toyrope"
+        folder.mkdir()
+        cfg = ToyConfig.from_dict(cfgd)
+        tensors = {k: v.to(DTYPES[dtype]) for k, v in sharpen(random_tensors(build(cfg), 4), 4.0).items()}
+        (folder / "config.json").write_text(json.dumps(cfgd))
+        write_safetensors(folder / "model.safetensors", tensors)
+        eng = Engine.load_path(folder, dtype=dtype, max_tokens=1024)
+        pc, pt = plain.load_folder(folder)
+        inv = frequencies(cfg.head_dim, cfg.slope)
+        monkeypatch.setattr(plain, "rope_angles", lambda positions, head_dim, theta: positions.to(torch.float32)[:, None] * inv[None, :])
+        ps = prompts([40, 3, 17], cfgd["vocab_size"], 61)
+        lens = [33, 1, 9]
+        slots = [eng.new_sequence() for _ in ps]
+        got = [[] for _ in ps]
+        out = eng.step([StepEntry(s, p[:n], list(range(n))) for s, p, n in zip(slots, ps, lens)])
+        off = 0
+        for i, n in enumerate(lens):
+            got[i].append(out[off:off + n])
+            off += n
+        for k in range(2):
+            out = eng.step([StepEntry(s, [p[n + k]], [0]) for s, p, n in zip(slots, ps, lens)])
+            for i in range(len(ps)):
+                got[i].append(out[i:i + 1])
+        for i, (p, n) in enumerate(zip(ps, lens)):
+            assert_close(torch.cat(got[i]), plain.forward(pc, pt, p[:n + 2]), dtype, f"toy rope request {i}")
+        # and the encoding matters: the ordinary geometric frequencies give other logits
+        monkeypatch.undo()
+        other = plain.forward(pc, pt, ps[0][:lens[0] + 2])
+        assert float((torch.cat(got[0]).double().cpu() - other).abs().max()) > 1e-2 * float(other.abs().max())
+        for s in slots:
+            eng.end_sequence(s)
+        res = eng.generate([ps[0][:9], ps[2][:4]], max_tokens=4, temperature=0.0)
+        assert all(len(r.tokens) == 4 for r in res)
+    finally:
+        unregister_architecture("ToyLinearRopeLM")
+        unregister_part("position", "toy_linear_frequencies")
 
 
 @pytest.mark.parametrize("head_dim,theta", [(16, 10000.0), (48, 500000.0), (128, 1e6)])
