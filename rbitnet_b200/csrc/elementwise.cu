@@ -84,10 +84,7 @@ RB_EXPORT int rb_embed(float* out, const void* table, int table_dtype, const int
 
 // ---------------------------------------------------------------- RMSNorm
 // y = x * w / sqrt(mean(x^2) + eps)  (crates/bitnet-core/src/llama/model.rs:93-100).
-// x is the float32 residual stream.  When `partials` is given, x first takes
-// in the sum of `n_partials` float32 slices [n_partials][T][E] (the pieces of a
-// matrix product that was split along its inner dimension) and the updated x is
-// written back, so the residual add and the norm read the row once.
+// x is the float32 residual stream.
 template <typename TO> __device__ __forceinline__ void store4(TO* p, float a, float b, float c, float d);
 template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
   *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
@@ -102,36 +99,24 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
 
 // VEC: the width is a multiple of 4 and rows are read and written four values at a time.
 template <typename TO, bool VEC>
-__global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, const float* __restrict__ w,
-                               const float* __restrict__ partials, int n_partials, int64_t partial_stride,
+__global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                                int E, float eps) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   __shared__ float scratch[33];
   extern __shared__ __align__(16) float row[];  // E floats
   const int t = blockIdx.x;
-  float* xr = x + (int64_t)t * E;
+  const float* xr = x + (int64_t)t * E;
   float ss = 0.f;
   if (VEC) {
     for (int j = threadIdx.x * 4; j < E; j += blockDim.x * 4) {
-      float4 v = *reinterpret_cast<const float4*>(xr + j);
-      if (n_partials > 0) {
-        for (int p = 0; p < n_partials; ++p) {
-          const float4 q = *reinterpret_cast<const float4*>(partials + p * partial_stride + (int64_t)t * E + j);
-          v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
-        }
-        *reinterpret_cast<float4*>(xr + j) = v;
-      }
+      const float4 v = *reinterpret_cast<const float4*>(xr + j);
       *reinterpret_cast<float4*>(row + j) = v;
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   } else {
     for (int j = threadIdx.x; j < E; j += blockDim.x) {
-      float v = xr[j];
-      if (n_partials > 0) {
-        for (int p = 0; p < n_partials; ++p) v += partials[p * partial_stride + (int64_t)t * E + j];
-        xr[j] = v;
-      }
+      const float v = xr[j];
       row[j] = v;
       ss += v * v;
     }
@@ -153,13 +138,12 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ x, cons
 // Rows of up to 4*NV*blockDim values (a multiple of 4) kept in registers: every load of a row
 // is in flight before the first is used, and nothing goes through shared memory.
 template <typename TO, int NV>
-__global__ void rmsnorm_reg_kernel(TO* __restrict__ out, float* __restrict__ x, const float* __restrict__ w,
-                                   const float* __restrict__ partials, int n_partials, int64_t partial_stride,
+__global__ void rmsnorm_reg_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
                                    int E, float eps) {
   rb_pdl_launch_dependents();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
-  float* xr = x + (int64_t)t * E;
+  const float* xr = x + (int64_t)t * E;
   float4 v[NV], g[NV];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {       // the norm's weights do not depend on the kernel before
@@ -171,32 +155,6 @@ __global__ void rmsnorm_reg_kernel(TO* __restrict__ out, float* __restrict__ x, 
   for (int i = 0; i < NV; ++i) {
     const int j = (threadIdx.x + i * blockDim.x) * 4;
     v[i] = j < E ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  if (n_partials > 0) {
-    const float* pr = partials + (int64_t)t * E;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int j = (threadIdx.x + i * blockDim.x) * 4;
-      if (j < E) {
-        // slices are added in slice order; four loads at a time are in flight
-        int p = 0;
-        for (; p + 4 <= n_partials; p += 4) {
-          const float4 q0 = *reinterpret_cast<const float4*>(pr + (p + 0) * partial_stride + j);
-          const float4 q1 = *reinterpret_cast<const float4*>(pr + (p + 1) * partial_stride + j);
-          const float4 q2 = *reinterpret_cast<const float4*>(pr + (p + 2) * partial_stride + j);
-          const float4 q3 = *reinterpret_cast<const float4*>(pr + (p + 3) * partial_stride + j);
-          v[i].x = (((v[i].x + q0.x) + q1.x) + q2.x) + q3.x;
-          v[i].y = (((v[i].y + q0.y) + q1.y) + q2.y) + q3.y;
-          v[i].z = (((v[i].z + q0.z) + q1.z) + q2.z) + q3.z;
-          v[i].w = (((v[i].w + q0.w) + q1.w) + q2.w) + q3.w;
-        }
-        for (; p < n_partials; ++p) {
-          const float4 q = *reinterpret_cast<const float4*>(pr + p * partial_stride + j);
-          v[i].x += q.x; v[i].y += q.y; v[i].z += q.z; v[i].w += q.w;
-        }
-        *reinterpret_cast<float4*>(xr + j) = v[i];
-      }
-    }
   }
   float ss = 0.f;
 #pragma unroll
@@ -212,56 +170,52 @@ __global__ void rmsnorm_reg_kernel(TO* __restrict__ out, float* __restrict__ x, 
 }
 
 template <typename TO>
-static int launch_rmsnorm_reg(TO* out, float* x, const float* w, const float* partials, int n_partials, int T, int E,
-                              float eps, cudaStream_t stream) {
+static int launch_rmsnorm_reg(TO* out, const float* x, const float* w, int T, int E, float eps, cudaStream_t stream) {
   const int threads = E <= 1024 ? 128 : (E <= 4096 ? 256 : 1024);
   const int nv = (E / 4 + threads - 1) / threads;
-  const int64_t ps = (int64_t)T * E;
   switch (nv) {
-    case 1: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 1>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
-    case 2: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 2>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
-    case 3: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 3>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
-    default: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 4>), T, threads, 0, stream, out, x, w, partials, n_partials, ps, E, eps); break;
+    case 1: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 1>), T, threads, 0, stream, out, x, w, E, eps); break;
+    case 2: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 2>), T, threads, 0, stream, out, x, w, E, eps); break;
+    case 3: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 3>), T, threads, 0, stream, out, x, w, E, eps); break;
+    default: RB_LAUNCH("rmsnorm_reg_kernel", (rmsnorm_reg_kernel<TO, 4>), T, threads, 0, stream, out, x, w, E, eps); break;
   }
   RB_CHECK_LAUNCH("rb_rmsnorm");
   return 0;
 }
 
 template <typename TO, bool VEC>
-static int launch_rmsnorm(TO* out, float* x, const float* w, const float* partials, int n_partials, int T, int E,
-                          float eps, cudaStream_t stream) {
+static int launch_rmsnorm(TO* out, const float* x, const float* w, int T, int E, float eps, cudaStream_t stream) {
   const int per = VEC ? 4 : 1;
   int threads = 128;
   while (threads < 1024 && threads * per * 2 <= E) threads *= 2;     // about two loads per thread
   const size_t smem = (size_t)E * sizeof(float);
   if (smem > 48 * 1024)
     RB_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  RB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<TO, VEC>), T, threads, smem, stream, out, x, w, partials, n_partials, (int64_t)T * E, E, eps);
+  RB_LAUNCH("rmsnorm_kernel", (rmsnorm_kernel<TO, VEC>), T, threads, smem, stream, out, x, w, E, eps);
   RB_CHECK_LAUNCH("rb_rmsnorm");
   return 0;
 }
 
-RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, const float* partials,
-                         int n_partials, int T, int E, float eps, cudaStream_t stream) {
+RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, const float* x, const float* w, int T, int E, float eps,
+                         cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(T > 0 && E > 0, "rb_rmsnorm: bad sizes T=%d E=%d", T, E);
   RB_REQUIRE((size_t)E * 4 <= 200 * 1024, "rb_rmsnorm: width %d exceeds the %d floats one block can hold",
              E, 200 * 1024 / 4);
-  if (partials == nullptr) n_partials = 0;
   const bool vec = E % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
-                   ((uintptr_t)out % 16 == 0) && ((uintptr_t)partials % 16 == 0);
+                   ((uintptr_t)out % 16 == 0);
   if (vec && E <= 16384) {
     if (out_dtype == RB_F32)
-      return launch_rmsnorm_reg<float>((float*)out, x, w, partials, n_partials, T, E, eps, stream);
+      return launch_rmsnorm_reg<float>((float*)out, x, w, T, E, eps, stream);
     if (out_dtype == RB_BF16)
-      return launch_rmsnorm_reg<__nv_bfloat16>((__nv_bfloat16*)out, x, w, partials, n_partials, T, E, eps, stream);
+      return launch_rmsnorm_reg<__nv_bfloat16>((__nv_bfloat16*)out, x, w, T, E, eps, stream);
   }
   if (out_dtype == RB_F32)
-    return vec ? launch_rmsnorm<float, true>((float*)out, x, w, partials, n_partials, T, E, eps, stream)
-               : launch_rmsnorm<float, false>((float*)out, x, w, partials, n_partials, T, E, eps, stream);
+    return vec ? launch_rmsnorm<float, true>((float*)out, x, w, T, E, eps, stream)
+               : launch_rmsnorm<float, false>((float*)out, x, w, T, E, eps, stream);
   if (out_dtype == RB_BF16)
-    return vec ? launch_rmsnorm<__nv_bfloat16, true>((__nv_bfloat16*)out, x, w, partials, n_partials, T, E, eps, stream)
-               : launch_rmsnorm<__nv_bfloat16, false>((__nv_bfloat16*)out, x, w, partials, n_partials, T, E, eps, stream);
+    return vec ? launch_rmsnorm<__nv_bfloat16, true>((__nv_bfloat16*)out, x, w, T, E, eps, stream)
+               : launch_rmsnorm<__nv_bfloat16, false>((__nv_bfloat16*)out, x, w, T, E, eps, stream);
   RB_FAIL("rb_rmsnorm: unknown dtype %d", out_dtype);
 }
 
@@ -274,12 +228,8 @@ RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, float* x, const float* w, con
 // `qkv` rows hold [H*D | Kh*D | Kh*D]; with write_kv == 0 only q is read (a
 // layer that reads another layer's cache).  The whole head is rotated
 // (rot_dim == D); a rotated prefix is refused by the entry point.
-// TI is the type of the input rows: the compute type T, or float when the rows are the float32
-// slices of a product that was split along its inner dimension (n_slices of them, slice_stride
-// elements apart), which are summed here in slice order.
-template <typename T, typename TI>
-__global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict__ qkv, int64_t qkv_stride,
-                                     int n_slices, int64_t slice_stride,
+template <typename T>
+__global__ void rotate_append_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, int64_t qkv_stride,
                                      const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
                                      int interleaved, int heads_per_block) {
@@ -289,13 +239,8 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const TI* __restrict
   const int pos = tok_pos[t];
   const int slot = tok_slot[t];
   rb_pdl_wait();     // positions and slots were written before the step began; qkv comes from the kernel before
-  const TI* row = qkv + (int64_t)t * qkv_stride;
-  auto value = [&](int64_t i) {
-    float v = rb_to_float<TI>(row[i]);
-#pragma unroll 4
-    for (int s = 1; s < n_slices; ++s) v += rb_to_float<TI>(row[s * slice_stride + i]);
-    return v;
-  };
+  const T* row = qkv + (int64_t)t * qkv_stride;
+  auto value = [&](int64_t i) { return rb_to_float<T>(row[i]); };
   const int half = D / 2;
   const int n_rot_heads = H + (write_kv ? Kh : 0);
   const int n_heads = n_rot_heads + (write_kv ? Kh : 0);        // rotated heads, then the v heads
@@ -409,17 +354,15 @@ __global__ void __launch_bounds__(1024) rotate_append_rows_kernel(
   }
 }
 
-// in_dtype: dtype of qkv (the compute dtype, or RB_F32 slices for a bfloat16 cache); n_slices >= 1.
+// dtype: the type of qkv, of q_out and of the cache.
 RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride, int dtype,
                                const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
                                void* cache_v, const int* page_table, int max_pages, int page_size, int T, int H,
-                               int Kh, int D, int write_kv, int rot_dim, int interleaved, int in_dtype,
-                               int n_slices, int64_t slice_stride, cudaStream_t stream) {
+                               int Kh, int D, int write_kv, int rot_dim, int interleaved, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(D % 2 == 0 && D > 0, "rb_rotate_append: head_dim %d must be even", D);
   RB_REQUIRE(rot_dim == D, "rb_rotate_append: a rotated prefix of %d of %d is not built", rot_dim, D);
   RB_REQUIRE(H > 0 && Kh >= 0 && page_size > 0, "rb_rotate_append: bad sizes H=%d Kh=%d page=%d", H, Kh, page_size);
-  RB_REQUIRE(n_slices >= 1, "rb_rotate_append: n_slices %d", n_slices);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
   const int threads = 256;
   // few tokens: spread a token's heads over several blocks so that enough blocks run
@@ -428,7 +371,7 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   if (by > n_heads) by = n_heads;
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
-  if (dtype == RB_BF16 && in_dtype == RB_BF16 && n_slices == 1 && T >= 32 && D % 16 == 0 && D <= 2 * ROWS_MAX_PAIRS &&
+  if (dtype == RB_BF16 && T >= 32 && D % 16 == 0 && D <= 2 * ROWS_MAX_PAIRS &&
       qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)cache_k % 16 == 0) && ((uintptr_t)cache_v % 16 == 0)) {
     // one thread per (rotated head, group of eight pairs) where a block can hold them: one pass over the heads
@@ -438,35 +381,13 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
               (const __nv_bfloat16*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved);
     return 0;
   }
-  if (dtype == RB_F32 && in_dtype == RB_F32)
-    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<float, float>), grid, threads, 0, stream, (float*)q_out, (const float*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
-  else if (dtype == RB_BF16 && in_dtype == RB_BF16)
-    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16, __nv_bfloat16>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
-  else if (dtype == RB_BF16 && in_dtype == RB_F32)
-    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16, float>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const float*)qkv, qkv_stride, n_slices, slice_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
+  if (dtype == RB_F32)
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<float>), grid, threads, 0, stream, (float*)q_out, (const float*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
+  else if (dtype == RB_BF16)
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
   else
-    RB_FAIL("rb_rotate_append: unsupported dtypes %d <- %d", dtype, in_dtype);
+    RB_FAIL("rb_rotate_append: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_rotate_append");
-  return 0;
-}
-
-// x[i] += sum over slices of partials[s][i], in slice order (float32).
-__global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partials, int n_partials,
-                                    int64_t n) {
-  rb_pdl_launch_dependents();
-  rb_pdl_wait();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float v = x[i];
-    for (int p = 0; p < n_partials; ++p) v += partials[p * n + i];
-    x[i] = v;
-  }
-}
-
-RB_EXPORT int rb_add_partials(float* x, const float* partials, int n_partials, int64_t n, cudaStream_t stream) {
-  if (n == 0 || n_partials == 0) return 0;
-  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  RB_LAUNCH("add_partials_kernel", (add_partials_kernel), blocks, 256, 0, stream, x, partials, n_partials, n);
-  RB_CHECK_LAUNCH("rb_add_partials");
   return 0;
 }
 

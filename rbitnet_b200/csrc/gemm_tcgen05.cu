@@ -15,7 +15,7 @@
 // share of the token columns from all parts, in part order, through distributed shared memory.
 //
 // Epilogues: plain store (bfloat16 or float32), add into a float32 matrix (the residual stream,
-// crates/bitnet-core/src/llama/model.rs:291-294, :303-306), float32 slices of a split product,
+// crates/bitnet-core/src/llama/model.rs:291-294, :303-306),
 // the q/k/v product of a decode step that rotates and appends to the cache (QkvTail below),
 // and SiLU(gate)*up (model.rs:297-302) from ONE accumulator: the caller interleaves the rows of the
 // gate and up matrices in blocks of 16, so that each warp of the epilogue holds 16 gate rows in its
@@ -37,7 +37,7 @@ constexpr int BK = 64;         // 64 bfloat16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int W_TILE_BYTES = BM * BK * 2;
 
-enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_GATED = 3, EPI_QKV = 4 };
+enum Epilogue { EPI_STORE = 0, EPI_ADD = 1, EPI_GATED = 3, EPI_QKV = 4 };     // (2 is not in use)
 
 __host__ __device__ constexpr uint32_t make_idesc(int n) { return make_idesc_mn(BM, n, 0, 0); }
 
@@ -63,9 +63,8 @@ struct QkvTail {
 };
 
 struct GemmParams {
-  void* C;            // output (or float32 slices for EPI_PARTIAL)
+  void* C;            // output
   int64_t ldc;        // row stride of C in elements
-  int64_t slice;      // elements between split slices (EPI_PARTIAL)
   int n_tokens;       // rows of X
   int n_out;          // rows of W (for EPI_GATED: gate and up rows together)
   int K;
@@ -261,7 +260,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tcgen05_fence_after();
       if (p.cluster) {
         // this split's accumulator goes to shared memory (the stage ring is idle now: every MMA
-        // that read it has completed); rank 0 adds the splits up after the cluster barrier below
+        // that read it has completed); the splits are added up after the cluster barrier below
         float* red = reinterpret_cast<float*>(smem);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 16) {
@@ -305,11 +304,6 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]);
-        } else if (EPI == EPI_PARTIAL) {
-          float* dst = (float*)p.C + (int64_t)split * p.slice + (int64_t)(t0 + c) * p.ldc + n;
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (j < t_left) dst[(int64_t)j * p.ldc] = __uint_as_float(r[j]);
         } else if (EPI == EPI_GATED) {
           // Lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features (feature =
           // (weight row block of 32) * 16 + lane % 16).  Columns are taken in pairs: the lower lanes
@@ -467,7 +461,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
     }
     __syncwarp();
-    cluster_sync_all();        // nobody's shared memory goes away while rank 0 reads it
+    cluster_sync_all();        // nobody's shared memory goes away while another rank reads it
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -630,9 +624,8 @@ RB_EXPORT int rb_read_error_flag(int* value, int reset) {
 // C (+)= X W^T on the tensor cores.
 //   epilogue 0: C[tokens, n_out] = product, c_dtype float32 or bfloat16
 //   epilogue 1: C (float32) += product
-//   (epilogues 0 and 1 with 2..8 splits: the CTAs of a tile form a cluster and the first adds
-//    the parts up through distributed shared memory, in split order; token tile <= 64)
-//   epilogue 2: C is [splits][tokens][ldc] float32 slices; slice z holds the product over its part of K
+//   (epilogues 0 and 1 with 2..8 splits: the CTAs of a tile form a cluster and each adds up a share
+//    of the token columns through distributed shared memory, in split order; token tile <= 64)
 //   epilogue 3: W holds, for every 16 output features, 16 gate rows followed by their 16 up rows
 //               (n_out rows in all, a multiple of 32); C[tokens, n_features] = silu(gate)*up
 // Requirements (refused otherwise): bfloat16 X and W, K a multiple of 8, row strides multiples of 8
@@ -645,7 +638,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
   RB_REQUIRE(splits >= 1, "rb_gemm_tc: splits %d", splits);
   RB_REQUIRE(epilogue != EPI_GATED || splits == 1, "rb_gemm_tc: the gated product cannot split K");
-  RB_REQUIRE(epilogue == EPI_PARTIAL || splits <= 8, "rb_gemm_tc: at most 8 splits are summed on the device (%d asked)", splits);
+  RB_REQUIRE(splits <= 8, "rb_gemm_tc: at most 8 splits are summed on the device (%d asked)", splits);
   const int nkb = (K + BK - 1) / BK;
   RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
   int bn = token_tile;
@@ -656,14 +649,14 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   if (rb_get_tensor_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
   if (rb_get_tensor_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
   GemmParams p;
-  p.C = C; p.ldc = ldc; p.slice = (int64_t)n_tokens * ldc; p.n_tokens = n_tokens; p.n_out = n_out; p.K = K;
+  p.C = C; p.ldc = ldc; p.n_tokens = n_tokens; p.n_out = n_out; p.K = K;
   p.n_features = n_features; p.kb_per_split = (nkb + splits - 1) / splits;
   RB_REQUIRE((int64_t)(splits - 1) * p.kb_per_split < nkb, "rb_gemm_tc: a split of K would be empty");
   const int n_w_tiles = (n_out + BM - 1) / BM, n_t_tiles = (n_tokens + bn - 1) / bn;
   const long long items = (long long)n_w_tiles * n_t_tiles * splits;
   RB_REQUIRE(items < (1ll << 30), "rb_gemm_tc: too many tiles");
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
-  p.cluster = (splits > 1 && epilogue != EPI_PARTIAL) ? 1 : 0;
+  p.cluster = splits > 1 ? 1 : 0;
   RB_REQUIRE(!p.cluster || bn <= 64, "rb_gemm_tc: K is split only for token tiles of at most 64");
   if (epilogue == EPI_QKV) {
     RB_REQUIRE(tail != nullptr && p.cluster, "rb_gemm_tc: the q/k/v tail wants K split into a cluster");
@@ -673,7 +666,6 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   if (epilogue == EPI_STORE && c_dtype == RB_BF16) return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, stream);
   if (epilogue == EPI_STORE && c_dtype == RB_F32) return dispatch<EPI_STORE, float>(bn, tw, tx, p, stream);
   if (epilogue == EPI_ADD && c_dtype == RB_F32) return dispatch<EPI_ADD, float>(bn, tw, tx, p, stream);
-  if (epilogue == EPI_PARTIAL && c_dtype == RB_F32) return dispatch<EPI_PARTIAL, float>(bn, tw, tx, p, stream);
   if (epilogue == EPI_GATED && c_dtype == RB_BF16) return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, p, stream);
   RB_FAIL("rb_gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, c_dtype);
 }
@@ -681,7 +673,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
 RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
                          int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
                          int token_tile, cudaStream_t stream) {
-  RB_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_GATED, "rb_gemm_tc: unknown epilogue %d", epilogue);
+  RB_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_ADD || epilogue == EPI_GATED, "rb_gemm_tc: unknown epilogue %d", epilogue);
   return gemm_tc(C, ldc, c_dtype, X, ldx, n_tokens, W, ldw, w_rows, n_out, K, epilogue, n_features, splits, token_tile,
                  nullptr, stream);
 }

@@ -16,9 +16,8 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 _SIGNATURES = {
     "rb_abi_version": [],
     "rb_embed": [P, P, I, P, I, I, I, P],
-    "rb_rmsnorm": [P, I, P, P, P, I, I, I, F, P],
-    "rb_rotate_append": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, L, P],
-    "rb_add_partials": [P, P, I, L, P],
+    "rb_rmsnorm": [P, I, P, P, I, I, F, P],
+    "rb_rotate_append": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
     "rb_silu_mul": [P, P, I, I, I, I, L, I, P],
     "rb_gather_rows": [P, P, P, I, I, P],
     "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, P],

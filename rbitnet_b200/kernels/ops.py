@@ -122,14 +122,11 @@ class CudaOps:
         self.lib.call("rb_embed", _ptr(out), _ptr(table), _CODE[table.dtype], _ptr(ids), T, E, V, self._stream())
         return out
 
-    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, partials=None,
-                out_dtype=None) -> torch.Tensor:
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype=None) -> torch.Tensor:
         self._check(x, torch.float32, "rmsnorm input")
         T, E = x.shape
         out = torch.empty((T, E), dtype=out_dtype or self.dtype, device=self.device)
-        n_part = 0 if partials is None else partials.shape[0]
-        self.lib.call("rb_rmsnorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), _ptr(partials), n_part,
-                      T, E, float(eps), self._stream())
+        self.lib.call("rb_rmsnorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), T, E, float(eps), self._stream())
         return out
 
     def linear(self, x: torch.Tensor, weight: LinearWeight, out_dtype=None,
@@ -201,7 +198,6 @@ class CudaOps:
         """Rotates q (and k) by position, appends k and v to the cache; returns q [T, H, D]."""
         D, Kh = view.head_dim, view.n_kv_heads
         T, width = qkv.shape
-        src, stride, n_slices, slice_stride, in_code = qkv, qkv.stride(0), 1, 0, self.code
         if rotary is None:
             inv_freq, interleaved, rot_dim = self._zeros_freq(D), False, D
         else:
@@ -210,10 +206,10 @@ class CudaOps:
         if width != want:
             raise KernelError(f"rotate_append: rows of {width} values, expected {want}")
         q = torch.empty((T, n_heads, D), dtype=self.dtype, device=self.device)
-        self.lib.call("rb_rotate_append", _ptr(q), _ptr(src), stride, self.code, _ptr(inv_freq),
+        self.lib.call("rb_rotate_append", _ptr(q), _ptr(qkv), qkv.stride(0), self.code, _ptr(inv_freq),
                       _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k), _ptr(view.v), _ptr(view.page_table),
                       view.max_pages, view.page_size, T, n_heads, Kh, D, 1 if view.writes else 0, rot_dim,
-                      1 if interleaved else 0, in_code, n_slices, slice_stride, self._stream())
+                      1 if interleaved else 0, self._stream())
         return q
 
     def project_rotate_append(self, h: torch.Tensor, weight: LinearWeight, rotary, meta, view,

@@ -52,7 +52,7 @@ class Part:
 class Norm(Part):
     role = "norm"
 
-    def forward(self, ctx, x: torch.Tensor, partials=None) -> torch.Tensor:
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 

@@ -20,8 +20,8 @@ class RMSNorm(Norm):
         # exact in float32 whatever the stored dtype
         self.weight = weights["weight"].to(torch.float32).contiguous()
 
-    def forward(self, ctx, x, partials=None):
-        return ctx.ops.rmsnorm(x, self.weight, self.eps, partials=partials)
+    def forward(self, ctx, x):
+        return ctx.ops.rmsnorm(x, self.weight, self.eps)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -52,13 +52,6 @@ def test_rmsnorm(ops32, ops16, E, T, eps):
     ref = (x.double() * w.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + eps))
     assert _rel(ops32.rmsnorm(x.clone(), w, eps), ref) < 2e-6
     assert _rel(ops16.rmsnorm(x.clone(), w, eps), ref) < 5e-3
-    # with slices of a split product folded in: x += sum(slices), then the norm
-    parts = torch.randn(3, T, E, device="cuda", generator=g)
-    x2 = x.clone()
-    y = ops32.rmsnorm(x2, w, eps, partials=parts)
-    xs = x.double() + parts.double().sum(0)
-    assert _rel(x2, xs) < 1e-6
-    assert _rel(y, xs * w.double() / torch.sqrt((xs ** 2).mean(-1, keepdim=True) + eps)) < 2e-6
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 7, 5), (3, 100, 33), (70, 130, 257), (5, 48, 176)])
@@ -403,46 +396,6 @@ def test_product_split_along_the_inner_dimension(ops16, T, N, K):
     ops16.linear(x, lw, accumulate_into=acc)
     assert _rel(acc, want) < 2e-5
     ops16.check_errors()
-
-
-def test_slices_of_a_split_product_can_be_written_and_folded(ops16):
-    """The product can also leave its parts as float32 slices; the norm folds slices in slice order
-    while it reads a row, and the rotation kernel reads slices directly."""
-    from ctypes import c_void_p
-    from rbitnet_b200.cache import CacheLayerView
-    g = torch.Generator(device="cuda").manual_seed(15)
-    T, N, K, S = 8, 512, 2048, 4
-    x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
-    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
-    slices = torch.zeros(S, T, N, device="cuda")
-    P = lambda t: c_void_p(t.data_ptr())
-    st = c_void_p(torch.cuda.current_stream().cuda_stream)
-    ops16.lib.call("rb_gemm_tc", P(slices), N, 0, P(x), K, T, P(w), K, N, N, K, 2, 0, S, 0, st)
-    ref = x.double() @ w.double().T
-    assert _rel(slices.sum(0), ref) < 2e-5 and float(slices[S - 1].abs().max()) > 0
-    acc = torch.randn(T, N, device="cuda", generator=g)
-    want = acc.double() + ref
-    h = ops16.rmsnorm(acc, torch.ones(N, device="cuda"), 1e-5, partials=slices, out_dtype=F32)
-    assert _rel(acc, want) < 2e-5
-    assert _rel(h, want / torch.sqrt((want ** 2).mean(-1, keepdim=True) + 1e-5)) < 2e-5
-    # rotation from slices equals rotation from their (once more rounded) sum
-    H, Kh, D, page = 4, 2, 32, 64
-    rows = [(0, 3), (1, 70), (0, 4)]
-    sl = torch.randn(3, len(rows), (H + 2 * Kh) * D, device="cuda", generator=g)
-    whole = sl.sum(0).to(BF16)
-    inv = (1.0 / torch.pow(torch.tensor(10000.0), 2.0 * torch.arange(D // 2, dtype=torch.float32) / D)).cuda()
-    meta = _meta(rows)
-    outs = []
-    for src, in_code, n_sl, sl_stride, stride in ((sl, 0, 3, sl.stride(0), sl.stride(1)), (whole, 1, 1, 0, whole.stride(0))):
-        k = torch.zeros(4, Kh, page, D, device="cuda", dtype=BF16)
-        v = torch.zeros_like(k)
-        table = torch.tensor([[0, 1], [2, 3]], dtype=torch.int32, device="cuda")
-        q = torch.empty(len(rows), H, D, device="cuda", dtype=BF16)
-        ops16.lib.call("rb_rotate_append", P(q), P(src), stride, 1, P(inv), P(meta.tok_pos), P(meta.tok_slot), P(k), P(v),
-                       P(table), 2, page, len(rows), H, Kh, D, 1, D, 0, in_code, n_sl, sl_stride, st)
-        outs.append((q, k, v))
-    for a_, b_ in zip(outs[0], outs[1]):
-        assert _rel(a_, b_.double()) < 8e-3
 
 
 @pytest.mark.parametrize("H,Kh,D,interleaved", [(4, 2, 16, True), (3, 1, 48, False), (8, 2, 128, False), (2, 2, 256, True)])
