@@ -162,9 +162,6 @@ class SequenceCache:
         return CacheLayerView(grp.pool[i, 0], grp.pool[i, 1], grp.table, self.max_pages, self.page_size,
                               grp.need.n_kv_heads, grp.need.head_dim, writes, g)
 
-    def has_view(self, entry: int) -> bool:
-        return entry in self._where
-
     def state(self, entry: int) -> Optional[torch.Tensor]:
         return self.states.get(entry)
 
