@@ -180,13 +180,28 @@ def test_greedy_generation_through_the_entry_point(engines, name, dtype):
 
 # Mid-size configurations: head sizes 64 and 128 and widths of several tiles, so that the engine runs
 # the tensor-core product over many tiles, the tcgen05 prefill attention and the split decode kernels
-# (the tiny configurations have head sizes 16 and 32, which take the other attention kernels).
+# (the tiny configurations have head sizes 16 and 32, which take the other attention kernels); then
+# other head sizes, group sizes and a window, which take the remaining kernels and their masks.
 MID = {
     "M64": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=512, num_attention_heads=8,
                 num_key_value_heads=2, head_dim=64, intermediate_size=1432, vocab_size=1000, rope_theta=10000.0,
                 rms_norm_eps=1e-5, max_position_embeddings=1024, tie_word_embeddings=False, rope_pairing="half"),
     "M128": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=768, num_attention_heads=6,
                  num_key_value_heads=3, head_dim=128, intermediate_size=1048, vocab_size=777, rope_theta=500000.0,
+                 rms_norm_eps=1e-6, max_position_embeddings=1024, tie_word_embeddings=True,
+                 rope_pairing="interleaved"),
+    # head size 96, three query heads a group, an odd inner size: the mma.sync attention kernels
+    "M96": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, hidden_size=576, num_attention_heads=6,
+                num_key_value_heads=2, head_dim=96, intermediate_size=1111, vocab_size=900, rope_theta=1e6,
+                rms_norm_eps=1e-5, max_position_embeddings=1024, tie_word_embeddings=False, rope_pairing="half"),
+    # five query heads a group and a window of 100 keys in the tcgen05 prefill and the TMA-fed decode
+    "M128w": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=1280, num_attention_heads=10,
+                  num_key_value_heads=2, head_dim=128, intermediate_size=2056, vocab_size=1000, rope_theta=10000.0,
+                  rms_norm_eps=1e-5, max_position_embeddings=1024, tie_word_embeddings=False, rope_pairing="half",
+                  sliding_window=100),
+    # the largest head size
+    "M256": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, hidden_size=768, num_attention_heads=3,
+                 num_key_value_heads=1, head_dim=256, intermediate_size=304, vocab_size=300, rope_theta=10000.0,
                  rms_norm_eps=1e-6, max_position_embeddings=1024, tie_word_embeddings=True,
                  rope_pairing="interleaved"),
 }
