@@ -52,6 +52,7 @@ struct Params {
   float* part_o;            // [B, H, n_splits, D]
   float* part_ml;           // [B, H, n_splits, 2]
   int n_splits;
+  int cluster;              // 1: the parts of a (sequence, kv head) are a thread-block cluster and merge on chip
 };
 
 // NS: stages of keys and values.  Two stages let three CTAs share an SM, three stages two: the
@@ -69,6 +70,9 @@ template <int D, int NS> struct Smem {
   static constexpr int KV_BYTES = 2 * NS * TILE_BYTES;
   // the merge of the four warps reuses the tile buffers: [4 warps][16 rows][D] floats, then max and sum
   static constexpr int MERGE_BYTES = (WARPS_D * 16 * D + 2 * WARPS_D * 16) * 4;
+  // behind it, what this CTA shows the other parts of its cluster: [16 rows][D] floats, max and sum
+  static constexpr int SHOW_BYTES = (16 * D + 2 * 16) * 4;
+  static_assert(MERGE_BYTES + SHOW_BYTES <= OFF_Q, "the merge areas lie inside the tile buffers");
   static constexpr int BYTES = (MERGE_BYTES > OFF_BAR ? MERGE_BYTES : OFF_BAR) + 64 + 1024;   // + room to align
 };
 
@@ -263,29 +267,81 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
     }
   }
   __syncthreads();
-  if (failed) return;
-  for (int idx = threadIdx.x; idx < G * D; idx += WARPS_D * 32) {
-    const int r = idx / D, d = idx % D;
-    float m = -INFINITY;
+  if (failed && !p.cluster) return;
+  // what the other parts of the cluster read: this part's sums, maximum and normaliser per row
+  float* sO = reinterpret_cast<float*>(smem + S::MERGE_BYTES);
+  float* sM = sO + 16 * D;
+  float* sL = sM + 16;
+  if (!failed) {
+    for (int idx = threadIdx.x; idx < G * D; idx += WARPS_D * 32) {
+      const int r = idx / D, d = idx % D;
+      float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < WARPS_D; ++w) m = fmaxf(m, mM[w * 16 + r]);
-    const float mu = m == -INFINITY ? 0.f : m;
-    float acc = 0.f, l = 0.f;
+      for (int w = 0; w < WARPS_D; ++w) m = fmaxf(m, mM[w * 16 + r]);
+      const float mu = m == -INFINITY ? 0.f : m;
+      float acc = 0.f, l = 0.f;
 #pragma unroll
-    for (int w = 0; w < WARPS_D; ++w) {
-      const float f = exp2f(mM[w * 16 + r] - mu);
-      acc += mO[(w * 16 + r) * D + d] * f;
-      l += mL[w * 16 + r] * f;
-    }
-    const int head = kvh * G + r;
-    if (p.n_splits > 1) {
-      const int64_t base = ((int64_t)tok0 * H + head) * p.n_splits + blockIdx.z;
-      p.part_o[base * D + d] = acc;
-      if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
-    } else {
-      p.out[((int64_t)tok0 * H + head) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      for (int w = 0; w < WARPS_D; ++w) {
+        const float f = exp2f(mM[w * 16 + r] - mu);
+        acc += mO[(w * 16 + r) * D + d] * f;
+        l += mL[w * 16 + r] * f;
+      }
+      const int head = kvh * G + r;
+      if (p.cluster) {
+        sO[r * D + d] = acc;
+        if (d == 0) { sM[r] = m; sL[r] = l; }
+      } else if (p.n_splits > 1) {
+        const int64_t base = ((int64_t)tok0 * H + head) * p.n_splits + blockIdx.z;
+        p.part_o[base * D + d] = acc;
+        if (d == 0) { p.part_ml[base * 2] = m; p.part_ml[base * 2 + 1] = l; }
+      } else {
+        p.out[((int64_t)tok0 * H + head) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      }
     }
   }
+  if (!p.cluster) return;
+  // ---- the parts of this (sequence, kv head) are one cluster: every CTA finishes a share of the
+  // output values from all parts, read through distributed shared memory and merged in part
+  // order.  Every thread of every CTA passes both barriers, also after a wait that gave up.
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (!failed) {
+    uint32_t my;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my));
+    const int parts = p.n_splits;                 // 2, 4 or 8
+    for (int idx = (int)my * WARPS_D * 32 + threadIdx.x; idx < G * D; idx += parts * WARPS_D * 32) {
+      const int r = idx / D, d = idx % D;
+      float m[8], l[8], o[8];
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {               // all loads first
+        m[z] = -INFINITY; l[z] = 0.f; o[z] = 0.f;
+        if (z < parts) {
+          uint32_t am, al, ao;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(am) : "r"(smem_u32(sM + r)), "r"((uint32_t)z));
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(al) : "r"(smem_u32(sL + r)), "r"((uint32_t)z));
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ao) : "r"(smem_u32(sO + r * D + d)), "r"((uint32_t)z));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(m[z]) : "r"(am));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l[z]) : "r"(al));
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(o[z]) : "r"(ao));
+        }
+      }
+      float mg = -INFINITY;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) mg = fmaxf(mg, m[z]);
+      const float mu = mg == -INFINITY ? 0.f : mg;
+      float acc = 0.f, ls = 0.f;
+#pragma unroll
+      for (int z = 0; z < 8; ++z) {
+        const float w = exp2f(m[z] - mu);          // 0 for a part without keys and beyond the last part
+        ls += l[z] * w;
+        acc += o[z] * w;
+      }
+      p.out[((int64_t)tok0 * H + kvh * G + r) * D + d] = __float2bfloat16_rn(ls > 0.f ? acc / ls : 0.f);
+    }
+  }
+  // nobody's shared memory goes away while another part reads it
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 template <int D, int NS>
@@ -296,6 +352,24 @@ int launch_ns(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int
   if (!configured) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
+  }
+  if (p.cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(B, Kh, p.n_splits);
+    cfg.blockDim = dim3(WARPS_D * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.n_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = rb_pdl_enabled() ? 2 : 1;
+    RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tk, tv, p));
+    return 0;
   }
   RB_LAUNCH("rb_attention_decode_tma", (kernel), dim3(B, Kh, p.n_splits), WARPS_D * 32, smem, stream, tk, tv, p);
   return 0;

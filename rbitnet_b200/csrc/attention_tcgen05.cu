@@ -480,15 +480,21 @@ RB_EXPORT int rb_attention_decode_tma_supports(int H, int Kh, int D, int page_si
 }
 
 // The number of parts to cut the keys of a decode into, for `pairs` = sequences x kv heads and
-// `tiles` 64-key tiles of the longest context: as many as fill one wave of two CTAs per SM (the
-// three-stage kernel) when the pairs fit such a wave; one when they fit a wave of three per SM; else
-// the count (up to 16) that fills whole waves of three per SM best.
+// `tiles` 64-key tiles of the longest context.  When the pairs fit one wave of two CTAs per SM (the
+// three-stage kernel): 1, 2, 4 or 8, as many as still fit that wave; the parts of a pair are then
+// a thread-block cluster and merge on chip.  One when the pairs fit a wave of three per SM.  Else
+// the count (up to 16) that fills whole waves of three per SM best; a second kernel merges those
+// (clusters in a grid of several waves ran slower than free CTAs).
 RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
   if (pairs <= 0 || tiles <= 0) return 1;
   const int two = decode_tma::places(2), three = decode_tma::places(3);
-  const int most = tiles < 16 ? tiles : 16;
-  if (pairs <= two) { const int s = two / pairs; return s < 1 ? 1 : (s > most ? most : s); }
+  if (pairs <= two) {
+    int s = 1;
+    while (s * 2 <= tiles && s < 8 && pairs * s * 2 <= two) s *= 2;
+    return s;
+  }
   if (pairs <= three) return 1;
+  const int most = tiles < 16 ? tiles : 16;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= most; ++s) {
@@ -497,6 +503,12 @@ RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
     if (eff > best_eff + 0.02) { best = s; best_eff = eff; }
   }
   return best;
+}
+
+// Whether `parts` parts of `pairs` pairs merge on chip (no scratch, no second kernel): 2, 4 or 8
+// parts in a grid that fits one wave of two CTAs per SM.
+RB_EXPORT int rb_attention_decode_tma_on_chip(int pairs, int parts) {
+  return (parts == 2 || parts == 4 || parts == 8) && (long long)pairs * parts <= decode_tma::places(2);
 }
 
 // Decode: one token per sequence (batch row b is sequence b's token), keys and values by TMA.  With
@@ -511,7 +523,10 @@ RB_EXPORT int rb_attention_decode_tma(void* out, const void* q, const void* cach
   RB_REQUIRE(rb_attention_decode_tma_supports(H, Kh, D, page_size),
              "rb_attention_decode_tma: sizes H=%d Kh=%d D=%d page=%d not supported", H, Kh, D, page_size);
   RB_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 2147483647, "rb_attention_decode_tma: n_splits %d", n_splits);
-  RB_REQUIRE(n_splits == 1 || (part_o && part_ml), "rb_attention_decode_tma: split decode needs scratch");
+  // the parts are a thread-block cluster and merge on chip, or they leave their results in the
+  // scratch and a second kernel merges them
+  const bool cluster = rb_attention_decode_tma_on_chip(B * Kh, n_splits) != 0;
+  RB_REQUIRE(n_splits == 1 || cluster || (part_o && part_ml), "rb_attention_decode_tma: split decode needs scratch");
   CUtensorMap tk, tv;
   const long long rows = n_pages * Kh * page_size;
   if (rb_get_tensor_map(&tk, cache_k, rows, D, D, decode_tma::TILE) != 0) return -1;
@@ -521,10 +536,10 @@ RB_EXPORT int rb_attention_decode_tma(void* out, const void* q, const void* cach
   p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size; p.n_kv_heads = Kh;
   p.tok_pos = tok_pos; p.tok_slot = tok_slot; p.H = H; p.G = H / Kh;
   p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
-  p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits;
+  p.part_o = part_o; p.part_ml = part_ml; p.n_splits = n_splits; p.cluster = cluster ? 1 : 0;
   const int rc = D == 64 ? decode_tma::launch<64>(tk, tv, p, B, Kh, stream) : decode_tma::launch<128>(tk, tv, p, B, Kh, stream);
   if (rc != 0) return rc;
-  if (n_splits > 1) return rb_attention_combine(out, part_o, part_ml, B, H, D, n_splits, stream);
+  if (n_splits > 1 && !cluster) return rb_attention_combine(out, part_o, part_ml, B, H, D, n_splits, stream);
   return 0;
 }
 

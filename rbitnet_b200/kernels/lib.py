@@ -55,6 +55,7 @@ class KernelLibrary:
         self.declare("rb_gemm_tc_qkv_supports", [I, I, I])
         self.declare("rb_attention_decode_tma_supports", [I, I, I, I])
         self.declare("rb_attention_decode_tma_parts", [I, I])
+        self.declare("rb_attention_decode_tma_on_chip", [I, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

@@ -256,7 +256,9 @@ class CudaOps:
             else:
                 n_splits = self._decode_splits(T, Kh, meta.max_context)
             part_o = part_ml = None
-            if n_splits > 1:
+            # a small grid of 2, 4 or 8 parts: they are a cluster and merge on chip
+            on_chip = on_tma and bool(self.lib.raw("rb_attention_decode_tma_on_chip")(T * Kh, n_splits))
+            if n_splits > 1 and not on_chip:
                 part_o = torch.empty((T, H, n_splits, D), dtype=torch.float32, device=self.device)
                 part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=self.device)
             if on_tma:
@@ -265,7 +267,7 @@ class CudaOps:
                               view.k.shape[0], _ptr(view.page_table), view.max_pages, view.page_size,
                               _ptr(meta.tok_pos), _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win,
                               _ptr(part_o), _ptr(part_ml), n_splits, self._stream(),
-                              launches=2 if n_splits > 1 else 1)
+                              launches=2 if n_splits > 1 and not on_chip else 1)
             else:
                 self.lib.call("rb_attention_decode", _ptr(out), _ptr(q), _ptr(view.k), _ptr(view.v),
                               _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),

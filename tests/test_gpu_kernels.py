@@ -199,10 +199,11 @@ def test_attention_over_the_paged_cache(ops32, ops16, H, Kh, D, page, window):
 
 
 @pytest.mark.parametrize("H,Kh,D,page,window", ATTN_CASES)
-@pytest.mark.parametrize("max_context", [64, 700])
+@pytest.mark.parametrize("max_context", [64, 128, 256, 512, 700])
 def test_decode_attention_with_split_keys(ops16, H, Kh, D, page, window, max_context):
     """One token per sequence at the end of sequences of very different lengths; the keys are cut
-    into parts (how many depends on the batch and on max_context) and merged."""
+    into parts (how many depends on the batch and on max_context: here 1, 2, 4, 8 and 11) and merged:
+    2, 4 and 8 parts of the TMA-fed kernel inside a thread-block cluster, other counts by a second kernel."""
     lens = [1, 700, 64, 65, 333]
     scale = 1.3 / math.sqrt(D)
     view, ks, vs = _paged(ops16, len(lens), -(-704 // page), page, Kh, D, lens, seed=12)
@@ -212,6 +213,24 @@ def test_decode_attention_with_split_keys(ops16, H, Kh, D, page, window, max_con
     got = ops16.attention(q, _meta(rows, single_token=True, max_context=max_context), view, H, scale, window)
     for i, (s, p) in enumerate(rows):
         assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, window)) < 8e-3, (i, s, p)
+
+
+@pytest.mark.parametrize("H,Kh,D", [(6, 3, 64), (8, 4, 128)])
+def test_decode_attention_of_many_sequences(ops16, H, Kh, D):
+    """More (sequence, kv head) pairs than run at once: the keys are then cut into a number of parts
+    that fills whole waves, and a second kernel merges them."""
+    lens = [1 + (37 * i) % 250 for i in range(150)]
+    scale = 1.1 / math.sqrt(D)
+    view, ks, vs = _paged(ops16, len(lens), 4, 64, Kh, D, lens, seed=21)
+    rows = [(s, n - 1) for s, n in enumerate(lens)]
+    parts = ops16.lib.raw("rb_attention_decode_tma_parts")(len(rows) * Kh, 4)
+    assert parts > 1 and not ops16.lib.raw("rb_attention_decode_tma_on_chip")(len(rows) * Kh, parts)
+    g = torch.Generator(device="cuda").manual_seed(22)
+    q = torch.randn(len(rows), H, D, device="cuda", generator=g).to(BF16) * 2
+    got = ops16.attention(q, _meta(rows, single_token=True, max_context=250), view, H, scale, None)
+    for i, (s, p) in enumerate(rows):
+        if i % 5 == 0 or p < 3:
+            assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, None)) < 8e-3, (i, s, p)
 
 
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops32):
