@@ -308,12 +308,12 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
   if (!failed) {
     uint32_t my;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(my));
-    const int parts = p.n_splits;                 // 2, 4 or 8
+    const int parts = p.n_splits;                 // 2, 4, 8 or 16
     for (int idx = (int)my * WARPS_D * 32 + threadIdx.x; idx < G * D; idx += parts * WARPS_D * 32) {
       const int r = idx / D, d = idx % D;
-      float m[8], l[8], o[8];
+      float m[16], l[16], o[16];
 #pragma unroll
-      for (int z = 0; z < 8; ++z) {               // all loads first
+      for (int z = 0; z < 16; ++z) {              // all loads first
         m[z] = -INFINITY; l[z] = 0.f; o[z] = 0.f;
         if (z < parts) {
           uint32_t am, al, ao;
@@ -327,11 +327,11 @@ __global__ void __launch_bounds__(WARPS_D * 32) attn_decode_tma_kernel(const __g
       }
       float mg = -INFINITY;
 #pragma unroll
-      for (int z = 0; z < 8; ++z) mg = fmaxf(mg, m[z]);
+      for (int z = 0; z < 16; ++z) mg = fmaxf(mg, m[z]);
       const float mu = mg == -INFINITY ? 0.f : mg;
       float acc = 0.f, ls = 0.f;
 #pragma unroll
-      for (int z = 0; z < 8; ++z) {
+      for (int z = 0; z < 16; ++z) {
         const float w = exp2f(m[z] - mu);          // 0 for a part without keys and beyond the last part
         ls += l[z] * w;
         acc += o[z] * w;
@@ -354,6 +354,11 @@ int launch_ns(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int
     configured = true;
   }
   if (p.cluster) {
+    static bool large_allowed = false;
+    if (p.n_splits > 8 && !large_allowed) {      // clusters of more than 8 CTAs have to be asked for
+      RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+      large_allowed = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(B, Kh, p.n_splits);
     cfg.blockDim = dim3(WARPS_D * 32, 1, 1);
@@ -384,6 +389,34 @@ inline int places(int per_sm) {
       sms = 148;
   }
   return sms * per_sm;
+}
+
+// Whether clusters of 16 CTAs of the three-stage kernel can run on this device (asked once).
+inline bool cluster_of_16_runs() {
+  static int answer = -1;
+  if (answer < 0) {
+    answer = 0;
+    auto kernel = attn_decode_tma_kernel<128, 3>;
+    constexpr int smem = Smem<128, 3>::BYTES;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(1, 1, 16);
+      cfg.blockDim = dim3(WARPS_D * 32, 1, 1);
+      cfg.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 16;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n >= 1) answer = 1;
+    }
+    (void)cudaGetLastError();      // a refusal above is an answer, not an error of a later launch
+  }
+  return answer == 1;
 }
 
 template <int D>

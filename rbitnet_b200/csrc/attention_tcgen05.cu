@@ -481,8 +481,9 @@ RB_EXPORT int rb_attention_decode_tma_supports(int H, int Kh, int D, int page_si
 
 // The number of parts to cut the keys of a decode into, for `pairs` = sequences x kv heads and
 // `tiles` 64-key tiles of the longest context.  When the pairs fit one wave of two CTAs per SM (the
-// three-stage kernel): 1, 2, 4 or 8, as many as still fit that wave; the parts of a pair are then
-// a thread-block cluster and merge on chip.  One when the pairs fit a wave of three per SM.  Else
+// three-stage kernel): 1, 2, 4, 8 or 16, as many as still fit that wave; the parts of a pair are
+// then a thread-block cluster and merge on chip (16 where the device runs such clusters, else they
+// are free CTAs with a merge kernel).  One when the pairs fit a wave of three per SM.  Else
 // the count (up to 16) that fills whole waves of three per SM best; a second kernel merges those
 // (clusters in a grid of several waves ran slower than free CTAs).
 RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
@@ -490,7 +491,7 @@ RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
   const int two = decode_tma::places(2), three = decode_tma::places(3);
   if (pairs <= two) {
     int s = 1;
-    while (s * 2 <= tiles && s < 8 && pairs * s * 2 <= two) s *= 2;
+    while (s * 2 <= tiles && s < 16 && pairs * s * 2 <= two) s *= 2;
     return s;
   }
   if (pairs <= three) return 1;
@@ -505,10 +506,12 @@ RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
   return best;
 }
 
-// Whether `parts` parts of `pairs` pairs merge on chip (no scratch, no second kernel): 2, 4 or 8
-// parts in a grid that fits one wave of two CTAs per SM.
+// Whether `parts` parts of `pairs` pairs merge on chip (no scratch, no second kernel): 2, 4, 8 or
+// 16 parts in a grid that fits one wave of two CTAs per SM.
 RB_EXPORT int rb_attention_decode_tma_on_chip(int pairs, int parts) {
-  return (parts == 2 || parts == 4 || parts == 8) && (long long)pairs * parts <= decode_tma::places(2);
+  if ((long long)pairs * parts > decode_tma::places(2)) return 0;
+  if (parts == 16) return decode_tma::cluster_of_16_runs() ? 1 : 0;
+  return parts == 2 || parts == 4 || parts == 8;
 }
 
 // Decode: one token per sequence (batch row b is sequence b's token), keys and values by TMA.  With

@@ -256,7 +256,7 @@ class CudaOps:
             else:
                 n_splits = self._decode_splits(T, Kh, meta.max_context)
             part_o = part_ml = None
-            # a small grid of 2, 4 or 8 parts: they are a cluster and merge on chip
+            # the parts of a small grid are a thread-block cluster and merge on chip
             on_chip = on_tma and bool(self.lib.raw("rb_attention_decode_tma_on_chip")(T * Kh, n_splits))
             if n_splits > 1 and not on_chip:
                 part_o = torch.empty((T, H, n_splits, D), dtype=torch.float32, device=self.device)

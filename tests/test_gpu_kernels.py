@@ -199,11 +199,12 @@ def test_attention_over_the_paged_cache(ops32, ops16, H, Kh, D, page, window):
 
 
 @pytest.mark.parametrize("H,Kh,D,page,window", ATTN_CASES)
-@pytest.mark.parametrize("max_context", [64, 128, 256, 512, 700])
+@pytest.mark.parametrize("max_context", [64, 128, 256, 700, 1100])
 def test_decode_attention_with_split_keys(ops16, H, Kh, D, page, window, max_context):
     """One token per sequence at the end of sequences of very different lengths; the keys are cut
-    into parts (how many depends on the batch and on max_context: here 1, 2, 4, 8 and 11) and merged:
-    2, 4 and 8 parts of the TMA-fed kernel inside a thread-block cluster, other counts by a second kernel."""
+    into parts (how many depends on the batch and on max_context: here 1, 2, 4, 8 and 16 for the
+    TMA-fed kernel, some of them without keys) and merged, inside a thread-block cluster or by a
+    second kernel."""
     lens = [1, 700, 64, 65, 333]
     scale = 1.3 / math.sqrt(D)
     view, ks, vs = _paged(ops16, len(lens), -(-704 // page), page, Kh, D, lens, seed=12)
