@@ -199,6 +199,10 @@ MID = {
                   num_key_value_heads=2, head_dim=128, intermediate_size=2056, vocab_size=1000, rope_theta=10000.0,
                   rms_norm_eps=1e-5, max_position_embeddings=1024, tie_word_embeddings=False, rope_pairing="half",
                   sliding_window=100),
+    # one layer with the layer sizes of Llama-3-8B (the vocabulary is kept small: the plain model runs on the CPU)
+    "L8B": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, hidden_size=4096, num_attention_heads=32,
+                num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=1000, rope_theta=500000.0,
+                rms_norm_eps=1e-5, max_position_embeddings=1024, tie_word_embeddings=False, rope_pairing="half"),
     # the largest head size
     "M256": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=1, hidden_size=768, num_attention_heads=3,
                  num_key_value_heads=1, head_dim=256, intermediate_size=304, vocab_size=300, rope_theta=10000.0,
@@ -214,7 +218,9 @@ def test_mid_size_prefill_chunks_and_decode(tmp_path, name, dtype):
     then tokens one by one for all; against the plain model."""
     from rbitnet_b200 import Engine, StepEntry
     cfg = MID[name]
-    folder = make_model_dir(tmp_path / "m", cfg, 11, store=dtype, factor=2.0)   # scores spread with a deviation of about one
+    # q and k weights are scaled so that scores spread with a deviation of about one (it is
+    # (0.02 * factor)^2 * hidden_size): a factor of 2 at widths of 512 to 1280, 0.78 at 4096
+    folder = make_model_dir(tmp_path / "m", cfg, 11, store=dtype, factor=0.78 if name == "L8B" else 2.0)
     ref = PlainModel(folder)
     eng = Engine.load_path(folder, dtype=dtype, max_tokens=4096)
     V = cfg["vocab_size"]

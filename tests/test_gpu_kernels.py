@@ -86,6 +86,45 @@ def test_tensor_core_product(ops16, T, N, K):
     ops16.check_errors()
 
 
+@pytest.mark.parametrize("T", [1, 8, 64, 2048])
+def test_products_at_the_layer_sizes_of_llama_3_8b(ops16, T):
+    """The products of one layer and the head at hidden 4096, inner 14336, vocabulary 128256: more
+    tiles than CTAs run at once (each CTA takes several, its two accumulators in turn), K cut into
+    clusters for few tokens, the widest token tile for many."""
+    g = torch.Generator(device="cuda").manual_seed(40 + T)
+    E, F, V, QKV = 4096, 14336, 128256, 6144
+    x = torch.randn(T, E, device="cuda", generator=g).to(BF16)
+
+    def weight(n, k):
+        return (torch.randn(n, k, device="cuda", generator=g) / math.sqrt(k)).to(BF16)
+
+    def ref(a, w):
+        return a.double() @ w.double().T
+
+    w = weight(QKV, E)
+    assert _rel(ops16.linear(x, ops16.prepare_linear([w])), ref(x, w)) < 5e-3
+    w = weight(E, E)
+    acc = torch.randn(T, E, device="cuda", generator=g)
+    want = acc.double() + ref(x, w)
+    ops16.linear(x, ops16.prepare_linear([w]), accumulate_into=acc)
+    assert _rel(acc, want) < 2e-5
+    wg, wu = weight(F, E) * 2, weight(F, E)
+    gate, up = ref(x, wg), ref(x, wu)
+    t = ops16.gated_linear(x, ops16.prepare_gate_up(wg, wu))
+    assert _rel(t, gate / (1 + torch.exp(-gate)) * up) < 6e-3
+    del wg, wu, gate, up
+    w = weight(E, F)
+    acc = torch.randn(T, E, device="cuda", generator=g)
+    want = acc.double() + ref(t, w)
+    ops16.linear(t, ops16.prepare_linear([w]), accumulate_into=acc)
+    assert _rel(acc, want) < 2e-5
+    del w
+    rows = x[:min(T, 64)].contiguous()                     # the head sees the wanted rows only
+    w = weight(V, E)
+    assert _rel(ops16.linear(rows, ops16.prepare_linear([w]), out_dtype=F32), ref(rows, w)) < 2e-5
+    ops16.check_errors()
+
+
 def test_product_refuses_to_guess_for_odd_inner_sizes(ops16):
     """An inner size TMA cannot address goes to the plain product, with the same result."""
     g = torch.Generator(device="cuda").manual_seed(5)
