@@ -273,6 +273,30 @@ def test_decode_attention_of_many_sequences(ops16, H, Kh, D):
             assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, None)) < 8e-3, (i, s, p)
 
 
+@pytest.mark.parametrize("window", [None, 1000])
+def test_attention_at_a_context_of_2100(ops16, window):
+    """Heads as in Llama-3-8B, a sequence of 2,100 positions beside a short one: its whole prompt in
+    one step (17 key tiles of 128 for the last rows), then one token each (33 tiles of 64 cut into
+    16 parts)."""
+    H, Kh, D, page = 32, 8, 128, 64
+    lens = [2100, 300]
+    scale = 1.0 / math.sqrt(D)
+    view, ks, vs = _paged(ops16, 2, -(-2112 // page), page, Kh, D, lens, seed=31)
+    rows = [(0, p) for p in range(2100)] + [(1, p) for p in range(300)]
+    g = torch.Generator(device="cuda").manual_seed(32)
+    q = torch.randn(len(rows), H, D, device="cuda", generator=g).to(BF16) * 2
+    got = ops16.attention(q, _meta(rows, max_context=2100), view, H, scale, window)
+    for i in [0, 63, 64, 127, 128, 999, 1000, 1001, 2047, 2048, 2099, 2100, 2399]:
+        s, p = rows[i]
+        assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, window)) < 8e-3, (i, s, p)
+    last = [(0, 2099), (1, 299)]
+    q1 = torch.randn(2, H, D, device="cuda", generator=g).to(BF16) * 2
+    got = ops16.attention(q1, _meta(last, single_token=True, max_context=2100), view, H, scale, window)
+    for i, (s, p) in enumerate(last):
+        assert _rel(got[i], _attn_ref(q1[i], ks[s], vs[s], p, scale, window)) < 8e-3, (i, s, p)
+    ops16.check_errors()
+
+
 def test_attention_finds_one_far_key_and_respects_the_window_edge(ops32):
     """One key matches the query strongly.  Inside the mask it must dominate the output; one
     position outside the window it must not be seen at all."""
