@@ -380,14 +380,20 @@ int launch_ns(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int
   return 0;
 }
 
-// CTAs that run together when each SM takes two (the three-stage kernel) and three (two stages).
-inline int places(int per_sm) {
+// CTAs of the kernel with `stages` stages that run together: what shared memory lets an SM hold
+// (227 KB, 1 KB of it per CTA for the system), at most 4 (128 threads of up to 128 registers).
+// Head size 128: 2 per SM with three stages, 3 with two.  Head size 64: 4 either way.
+inline int places(int D, int stages) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
   }
+  const int bytes = D == 64 ? (stages == 3 ? Smem<64, 3>::BYTES : Smem<64, 2>::BYTES)
+                            : (stages == 3 ? Smem<128, 3>::BYTES : Smem<128, 2>::BYTES);
+  int per_sm = (227 * 1024) / (bytes + 1024);
+  if (per_sm > 4) per_sm = 4;
   return sms * per_sm;
 }
 
@@ -421,7 +427,9 @@ inline bool cluster_of_16_runs() {
 
 template <int D>
 int launch(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B, int Kh, cudaStream_t stream) {
-  if ((long long)B * Kh * p.n_splits <= places(2)) return launch_ns<D, 3>(tk, tv, p, B, Kh, stream);
+  // the deeper ring when the whole grid runs at once with it, or when the shallower one holds no more CTAs
+  if ((long long)B * Kh * p.n_splits <= places(D, 3) || places(D, 2) <= places(D, 3))
+    return launch_ns<D, 3>(tk, tv, p, B, Kh, stream);
   return launch_ns<D, 2>(tk, tv, p, B, Kh, stream);
 }
 

@@ -479,37 +479,37 @@ RB_EXPORT int rb_attention_decode_tma_supports(int H, int Kh, int D, int page_si
   return (D == 64 || D == 128) && page_size % decode_tma::TILE == 0 && H / Kh <= 16;
 }
 
-// The number of parts to cut the keys of a decode into, for `pairs` = sequences x kv heads and
-// `tiles` 64-key tiles of the longest context.  When the pairs fit one wave of two CTAs per SM (the
-// three-stage kernel): 1, 2, 4, 8 or 16, as many as still fit that wave; the parts of a pair are
-// then a thread-block cluster and merge on chip (16 where the device runs such clusters, else they
-// are free CTAs with a merge kernel).  One when the pairs fit a wave of three per SM.  Else
-// the count (up to 16) that fills whole waves of three per SM best; a second kernel merges those
-// (clusters in a grid of several waves ran slower than free CTAs).
-RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles) {
+// The number of parts to cut the keys of a decode into, for `pairs` = sequences x kv heads, `tiles`
+// 64-key tiles of the longest context and head size D.  When the pairs fit one wave of the
+// three-stage kernel (two CTAs per SM at head size 128, four at 64): 1, 2, 4, 8 or 16, as many as
+// still fit that wave; the parts of a pair are then a thread-block cluster and merge on chip (16
+// where the device runs such clusters, else they are free CTAs with a merge kernel).  One when the
+// pairs fit a wave of the two-stage kernel.  Else the count (up to 16) that fills whole such waves
+// best; a second kernel merges those (clusters in a grid of several waves ran slower than free CTAs).
+RB_EXPORT int rb_attention_decode_tma_parts(int pairs, int tiles, int D) {
   if (pairs <= 0 || tiles <= 0) return 1;
-  const int two = decode_tma::places(2), three = decode_tma::places(3);
-  if (pairs <= two) {
+  const int deep = decode_tma::places(D, 3), shallow = decode_tma::places(D, 2) > deep ? decode_tma::places(D, 2) : deep;
+  if (pairs <= deep) {
     int s = 1;
-    while (s * 2 <= tiles && s < 16 && pairs * s * 2 <= two) s *= 2;
+    while (s * 2 <= tiles && s < 16 && pairs * s * 2 <= deep) s *= 2;
     return s;
   }
-  if (pairs <= three) return 1;
+  if (pairs <= shallow) return 1;
   const int most = tiles < 16 ? tiles : 16;
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= most; ++s) {
     const long long ctas = (long long)pairs * s;
-    const double eff = (double)ctas / (double)(((ctas + three - 1) / three) * three);
+    const double eff = (double)ctas / (double)(((ctas + shallow - 1) / shallow) * shallow);
     if (eff > best_eff + 0.02) { best = s; best_eff = eff; }
   }
   return best;
 }
 
 // Whether `parts` parts of `pairs` pairs merge on chip (no scratch, no second kernel): 2, 4, 8 or
-// 16 parts in a grid that fits one wave of two CTAs per SM.
-RB_EXPORT int rb_attention_decode_tma_on_chip(int pairs, int parts) {
-  if ((long long)pairs * parts > decode_tma::places(2)) return 0;
+// 16 parts in a grid that fits one wave of the three-stage kernel.
+RB_EXPORT int rb_attention_decode_tma_on_chip(int pairs, int parts, int D) {
+  if ((long long)pairs * parts > decode_tma::places(D, 3)) return 0;
   if (parts == 16) return decode_tma::cluster_of_16_runs() ? 1 : 0;
   return parts == 2 || parts == 4 || parts == 8;
 }
@@ -528,7 +528,7 @@ RB_EXPORT int rb_attention_decode_tma(void* out, const void* q, const void* cach
   RB_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 2147483647, "rb_attention_decode_tma: n_splits %d", n_splits);
   // the parts are a thread-block cluster and merge on chip, or they leave their results in the
   // scratch and a second kernel merges them
-  const bool cluster = rb_attention_decode_tma_on_chip(B * Kh, n_splits) != 0;
+  const bool cluster = rb_attention_decode_tma_on_chip(B * Kh, n_splits, D) != 0;
   RB_REQUIRE(n_splits == 1 || cluster || (part_o && part_ml), "rb_attention_decode_tma: split decode needs scratch");
   CUtensorMap tk, tv;
   const long long rows = n_pages * Kh * page_size;

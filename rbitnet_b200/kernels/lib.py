@@ -54,8 +54,8 @@ class KernelLibrary:
         self.declare("rb_attention_prefill_tc_supports", [I, I, I, I])
         self.declare("rb_gemm_tc_qkv_supports", [I, I, I])
         self.declare("rb_attention_decode_tma_supports", [I, I, I, I])
-        self.declare("rb_attention_decode_tma_parts", [I, I])
-        self.declare("rb_attention_decode_tma_on_chip", [I, I])
+        self.declare("rb_attention_decode_tma_parts", [I, I, I])
+        self.declare("rb_attention_decode_tma_on_chip", [I, I, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

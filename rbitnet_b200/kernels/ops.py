@@ -252,12 +252,12 @@ class CudaOps:
                 self.lib.raw("rb_attention_tiled_supports")(H, Kh, D, view.page_size, 1):
             on_tma = self.decode_on_tma and self.lib.raw("rb_attention_decode_tma_supports")(H, Kh, D, view.page_size)
             if on_tma:
-                n_splits = self.lib.raw("rb_attention_decode_tma_parts")(T * Kh, max(1, -(-meta.max_context // 64)))
+                n_splits = self.lib.raw("rb_attention_decode_tma_parts")(T * Kh, max(1, -(-meta.max_context // 64)), D)
             else:
                 n_splits = self._decode_splits(T, Kh, meta.max_context)
             part_o = part_ml = None
             # the parts of a small grid are a thread-block cluster and merge on chip
-            on_chip = on_tma and bool(self.lib.raw("rb_attention_decode_tma_on_chip")(T * Kh, n_splits))
+            on_chip = on_tma and bool(self.lib.raw("rb_attention_decode_tma_on_chip")(T * Kh, n_splits, D))
             if n_splits > 1 and not on_chip:
                 part_o = torch.empty((T, H, n_splits, D), dtype=torch.float32, device=self.device)
                 part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=self.device)

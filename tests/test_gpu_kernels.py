@@ -255,7 +255,7 @@ def test_decode_attention_with_split_keys(ops16, H, Kh, D, page, window, max_con
         assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, window)) < 8e-3, (i, s, p)
 
 
-@pytest.mark.parametrize("H,Kh,D", [(6, 3, 64), (8, 4, 128)])
+@pytest.mark.parametrize("H,Kh,D", [(8, 4, 64), (8, 4, 128)])
 def test_decode_attention_of_many_sequences(ops16, H, Kh, D):
     """More (sequence, kv head) pairs than run at once: the keys are then cut into a number of parts
     that fills whole waves, and a second kernel merges them."""
@@ -263,8 +263,8 @@ def test_decode_attention_of_many_sequences(ops16, H, Kh, D):
     scale = 1.1 / math.sqrt(D)
     view, ks, vs = _paged(ops16, len(lens), 4, 64, Kh, D, lens, seed=21)
     rows = [(s, n - 1) for s, n in enumerate(lens)]
-    parts = ops16.lib.raw("rb_attention_decode_tma_parts")(len(rows) * Kh, 4)
-    assert parts > 1 and not ops16.lib.raw("rb_attention_decode_tma_on_chip")(len(rows) * Kh, parts)
+    parts = ops16.lib.raw("rb_attention_decode_tma_parts")(len(rows) * Kh, 4, D)
+    assert parts > 1 and not ops16.lib.raw("rb_attention_decode_tma_on_chip")(len(rows) * Kh, parts, D)
     g = torch.Generator(device="cuda").manual_seed(22)
     q = torch.randn(len(rows), H, D, device="cuda", generator=g).to(BF16) * 2
     got = ops16.attention(q, _meta(rows, single_token=True, max_context=250), view, H, scale, None)
