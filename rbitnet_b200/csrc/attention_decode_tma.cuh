@@ -3,9 +3,12 @@
 // The arithmetic is that of the decode mode of attention_tiled.cu: one CTA works for ONE kv head of
 // ONE sequence on a part of its keys; its rows are the token's G query heads (G <= 16, padded to the
 // 16 rows of mma.sync m16n8k16); keys and values come in tiles of 64 positions, of which each of the
-// four warps takes 16 keys; the warps are merged at the end and the CTA writes an unnormalised
-// partial (max, sum, O) that attn_combine_kernel merges, or the result itself when the keys are not
-// split.  crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound, P V), :102-114.
+// four warps takes 16 keys; the warps are merged at the end.  When the keys are not split the CTA
+// writes the result itself.  When they are, the parts of a (sequence, kv head) are either a
+// thread-block cluster (2, 4, 8 or 16 CTAs of a grid that runs as one wave) that merges through
+// distributed shared memory, or free CTAs that write unnormalised partials (max, sum, O) for
+// attn_combine_kernel.  crates/bitnet-core/src/llama/model.rs:260-289 (scores, mask by loop bound,
+// P V), :102-114.
 //
 // What differs is how a tile gets into shared memory.  There, every thread issues 32 cp.async of 16
 // bytes per tile, which costs the four warps about a third of a tile's time; here one thread asks
