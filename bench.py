@@ -285,6 +285,9 @@ def main():
                     help="with --phase prefill: the prompt's length (up to 8,000), for profiling other lengths")
     ap.add_argument("--timeline", action="store_true",
                     help="print when each kernel of one decode step ran inside the captured graph, and exit")
+    ap.add_argument("--shape", default="llama3_8b", choices=["llama3_8b", "llama2_7b", "tinyllama_1b"],
+                    help="layer sizes of the decode and prefill measurements (default: the headline's; the others "
+                         "are those of the generation workloads and are named in metric and config)")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the other generation workloads end to end instead (one short line)")
     args = ap.parse_args()
@@ -304,13 +307,18 @@ def main():
     import torch
     from rbitnet_b200 import Engine
     pk = peaks()
-    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    shape_name, model = {"llama3_8b": ("Llama-3-8B shape", MODEL),
+                         "llama2_7b": ("Llama-2-7B shape", WORKLOADS["llama2_7b_unequal"]["model"]),
+                         "tinyllama_1b": ("TinyLlama-1.1B shape", WORKLOADS["tinyllama_b64_sampling"]["model"])}[args.shape]
+    full_layers, max_seq = model["num_hidden_layers"], model["max_position_embeddings"]
+    layers = full_layers if args.layers == FULL_LAYERS else min(args.layers, full_layers)
+    cfg = dict(model, num_hidden_layers=layers)
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     room = steps + warmup + 16
-    ctx = max(1, min(8192 - room, args.context))
+    ctx = max(1, min(max_seq - room, args.context))
     max_tokens = max(b * (-(-(max(ctx, PROMPT_LEN) + room) // 64) * 64) for b in batches) + 64 * 64
     t_build = time.time()
-    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seq=8192, max_batch=64)
+    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seq=max_seq, max_batch=64)
     for g in engine.cache.groups:                   # random cache content; finite values, no work depends on it
         g.pool.normal_(0.0, 1.0)
     torch.cuda.synchronize()
@@ -322,7 +330,7 @@ def main():
     if args.phase == "prefill":
         n_tok = max(1, min(8000, args.prefill_tokens))
         pf_ms = time_prefill(engine, n_tok, reps=max(1, min(3, steps)))
-        print(json.dumps({"phase": "prefill", "tokens": n_tok, "layers": args.layers, "ms": round(pf_ms, 3),
+        print(json.dumps({"phase": "prefill", "tokens": n_tok, "layers": layers, "ms": round(pf_ms, 3),
                           "tokens_per_s": round(n_tok / pf_ms * 1e3, 1)}))
         return 0
 
@@ -339,7 +347,7 @@ def main():
                     pms, _, _ = time_decode(engine, b, ctx, max(8, steps // 2), warmup)
                     points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
             pf_ms = time_prefill(engine, PROMPT_LEN)
-            flops = prefill_flops(cfg, args.layers, PROMPT_LEN)
+            flops = prefill_flops(cfg, layers, PROMPT_LEN)
             prefill = {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
                        "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
                        "peak_tflops": pk["bf16_tflops_sustained"], "peak": f"bf16 sustained, {pk['source']}"}
@@ -347,19 +355,22 @@ def main():
         sampler.stop()
 
     nbytes = decode_bytes(engine, args.batch, ctx)
+    metric = METRIC.replace("Llama-3-8B shape", shape_name).replace("batch 8", f"batch {args.batch}")
+    if ctx != PROMPT_LEN:
+        metric = metric.replace("2048-token", f"{ctx}-token")
     achieved = nbytes / (ms * 1e-3) / 1e9
     value = args.batch / ms * 1e3
     line = {
-        "metric": METRIC if ctx == PROMPT_LEN else METRIC.replace("2048-token", f"{ctx}-token"), "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "metric": metric, "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, random token ids, random cache)",
         "impl": "ours",
-        "config": {"model": "Llama-3-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
+        "config": {"model": shape_name, "layers": layers, "layers_full": full_layers,
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "rope_theta": cfg["rope_theta"], "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False,
-                   "global_batch": args.batch, "seq_len": ctx, "max_context": 8192,
+                   "global_batch": args.batch, "seq_len": ctx, "max_context": max_seq,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights read once per step)",
                    "step": "one decode token per sequence, CUDA graph, sampled on device"},
         "e2e": {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
