@@ -1,0 +1,62 @@
+"""Host-side choices the kernel library makes, asked without a GPU: into how many parts the keys of a
+decode are cut and when those parts merge on chip, which sizes each kernel says it takes, and which
+requests are refused with a message.  The library is built by nvcc where it is missing (no device is
+needed to build or to load it); without nvcc these tests are skipped."""
+import shutil
+
+import pytest
+
+if shutil.which("nvcc") is None:
+    pytest.skip("nvcc is not installed here", allow_module_level=True)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from rbitnet_b200.kernels.lib import load
+    return load(verbose=False)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_parts_of_a_decode(lib, D):
+    parts, on_chip = lib.raw("rb_attention_decode_tma_parts"), lib.raw("rb_attention_decode_tma_on_chip")
+    for pairs in (1, 7, 8, 32, 64, 100, 256, 300, 512, 600, 1024, 5000):
+        for tiles in (1, 2, 3, 5, 16, 33, 128):
+            s = parts(pairs, tiles, D)
+            assert 1 <= s <= min(16, tiles), (pairs, tiles, s)          # no part without a tile to start from
+            if on_chip(pairs, s, D):
+                assert s in (2, 4, 8, 16)                               # cluster sizes
+        assert parts(pairs, 1, D) == 1
+    # a small batch is cut as far as its context allows, and merges on chip (up to 8 parts on any device)
+    assert parts(8, 4, D) == 4 and on_chip(8, 4, D)
+    assert parts(64, 32, 128) == 4 and on_chip(64, 4, 128)
+    assert parts(0, 5, D) == 1 and parts(5, 0, D) == 1
+    # more CTAs fit an SM at head size 64, so more pairs still count as a small grid
+    assert parts(256, 32, 64) == 2 and parts(256, 32, 128) == 1
+    assert not on_chip(600, 4, D)
+
+
+def test_sizes_the_kernels_take(lib):
+    assert lib.raw("rb_attention_decode_tma_supports")(32, 8, 128, 64)
+    assert not lib.raw("rb_attention_decode_tma_supports")(32, 8, 96, 64)      # head size
+    assert not lib.raw("rb_attention_decode_tma_supports")(32, 8, 128, 16)     # pages of 16 positions
+    assert not lib.raw("rb_attention_decode_tma_supports")(34, 2, 128, 64)     # 17 query heads a group
+    assert lib.raw("rb_attention_prefill_tc_supports")(32, 8, 64, 128)
+    assert not lib.raw("rb_attention_prefill_tc_supports")(7, 2, 128, 64)      # heads that are no multiple of the groups
+    assert lib.raw("rb_attention_tiled_supports")(6, 2, 96, 64, 1)
+    assert not lib.raw("rb_attention_tiled_supports")(6, 2, 100, 64, 1)
+    assert lib.raw("rb_gemm_tc_qkv_supports")(8, 128, 4)
+    assert not lib.raw("rb_gemm_tc_qkv_supports")(8, 128, 1)                   # K has to be split
+    assert not lib.raw("rb_gemm_tc_qkv_supports")(17, 128, 4)                  # few tokens only
+    assert not lib.raw("rb_gemm_tc_qkv_supports")(8, 96, 4)                    # a head may not straddle two tiles
+
+
+def test_requests_are_refused_with_a_message(lib):
+    from rbitnet_b200.kernels.lib import KernelError
+    with pytest.raises(KernelError, match="multiple of 8"):
+        lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 0)
+    with pytest.raises(KernelError, match="cannot split K"):
+        lib.call("rb_gemm_tc", 0, 64, 1, 0, 64, 8, 0, 64, 64, 64, 128, 3, 32, 2, 0, 0)
+    with pytest.raises(KernelError, match="at most 8 splits"):
+        lib.call("rb_gemm_tc", 0, 64, 1, 0, 1024, 8, 0, 1024, 64, 64, 1024, 0, 0, 9, 0, 0)
+    with pytest.raises(KernelError, match="head_dim"):
+        lib.call("rb_rotate_append", 0, 0, 0, 1, 0, 0, 0, 0, 0, 0, 1, 64, 1, 2, 1, 7, 1, 7, 0, 0)
