@@ -147,8 +147,8 @@ class CudaOps:
             # few tokens and few weight tiles: K is cut into parts so that every SM streams a piece
             # of W; the parts of a tile are one thread-block cluster and are summed on chip
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0), T,
-                          _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, self._k_splits(T, N, K), 0,
-                          self._stream())
+                          _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, self._k_splits(T, N, K),
+                          64 if 64 < T <= 256 else 0, self._stream())
         else:
             self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
                           _ptr(weight.w), weight.w.stride(0), self.code, T, N, K, acc, self._stream())
@@ -156,12 +156,13 @@ class CudaOps:
 
     @staticmethod
     def _k_splits(T: int, N: int, K: int) -> int:
-        """Parts to cut the inner dimension into: only for at most 64 tokens (the product is then
-        bound by reading W) and only when the 128-row tiles of W are fewer than the CTAs that run
-        together (two per SM); at most 8, the size of a cluster."""
-        if T > 64:
+        """Parts to cut the inner dimension into.  Up to 256 tokens a product is bound by reading W,
+        so it wants every SM to stream a piece of it: the tokens go in tiles of at most 64, and when
+        the 128-row tiles of W times the token tiles are fewer than the CTAs that run together (two
+        per SM), K is cut as well; at most 8 parts, the size of a cluster.  Beyond 256 tokens: one."""
+        if T > 256:
             return 1
-        tiles = -(-N // 128)
+        tiles = -(-N // 128) * -(-T // 64)
         blocks = -(-K // 64)
         want = 1
         while want * 2 <= min(8, 296 // tiles, blocks // 4):      # 1, 2, 4 or 8: the sizes clusters schedule well

@@ -69,7 +69,11 @@ def test_plain_product_is_true_float32(ops32, T, N, K):
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 128, 64), (5, 200, 96), (17, 1000, 176), (64, 384, 520), (100, 130, 4096),
-                                   (129, 257, 72), (300, 520, 1032), (700, 96, 48)])
+                                   (129, 257, 72), (300, 520, 1032), (700, 96, 48),
+                                   # 65 to 256 tokens: token tiles of 64, several of them, with K cut or not
+                                   (130, 4096, 4096), (200, 1000, 14336), (256, 6144, 1024), (250, 28000, 512),
+                                   # 257 to 1024 tokens: tiles of 128 or 256, whichever needs fewer rounds of the SMs
+                                   (500, 4096, 1032), (512, 28672, 256), (1000, 6144, 512), (1024, 4096, 520)])
 def test_tensor_core_product(ops16, T, N, K):
     g = torch.Generator(device="cuda").manual_seed(4)
     x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
