@@ -10,7 +10,8 @@
 //
 // Roles in a CTA of 192 threads: warp 0 issues TMA loads into a ring of stages, warp 1 owns the
 // tensor memory and issues tcgen05.mma (one lane), warps 2..5 read the accumulators back with
-// tcgen05.ld and write the result.  For at most 64 tokens K may be cut into 2..8 parts: the CTAs
+// tcgen05.ld and write the result.  With token tiles of at most 64 (which the caller asks for up
+// to 256 tokens, where a product is bound by reading W) K may be cut into 2..8 parts: the CTAs
 // of a tile then form a thread-block cluster, and after their products each of them adds up a
 // share of the token columns from all parts, in part order, through distributed shared memory.
 //
