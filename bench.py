@@ -103,7 +103,7 @@ def fill_cache(engine, batch, context, room):
 def decode_bytes(engine, batch, context):
     """What a decode step has to read: every weight it uses once, and the live sequences' cache."""
     w = engine.model.weight_bytes()      # every matrix a step multiplies by (the embedding table is only gathered from)
-    per_token = sum(2 * g.need.n_kv_heads * g.need.head_dim * g.pool.element_size() * len(g.entries)
+    per_token = sum(g.bytes_per_position()
                     for g in engine.cache.groups)
     return w + batch * context * per_token
 
@@ -320,7 +320,8 @@ def main():
     t_build = time.time()
     engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens, max_seq=max_seq, max_batch=64)
     for g in engine.cache.groups:                   # random cache content; finite values, no work depends on it
-        g.pool.normal_(0.0, 1.0)
+        for pool in g.pools:
+            pool.normal_(0.0, 1.0)
     torch.cuda.synchronize()
     build_s = time.time() - t_build
 

@@ -8,10 +8,16 @@ cache for one sequence and zero-fills it per request
 (crates/bitnet-core/src/llama/model.rs:29-51, runtime.rs:40); here giving a
 slot back is O(pages) and nothing is cleared, because no kernel reads past a
 sequence's length.
+
+A group whose layers see only the last ``window`` keys gives a sequence's pages
+back as soon as they lie wholly behind the window of the sequence's next token
+(the attention kernels start at the page that holds the first visible key), so
+a long sequence holds about ``window / page_size + 2`` pages of such a group,
+whatever its length.  The released places of a page list hold -1.
 """
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 
 class CacheFull(RuntimeError):
@@ -57,12 +63,17 @@ class FreeList:
 class SlotBook:
     """Slots, their lengths and their pages in every group."""
 
-    def __init__(self, n_slots: int, pages_per_group: List[int], page_size: int, max_seq: int):
+    def __init__(self, n_slots: int, pages_per_group: List[int], page_size: int, max_seq: int,
+                 windows: Optional[List[Optional[int]]] = None):
         self.page_size, self.max_seq = page_size, max_seq
         self.slots = FreeList(n_slots)
         self.pools = [FreeList(n) for n in pages_per_group]
+        #: per group, how many of the last keys its layers see (None: all of them)
+        self.windows = list(windows) if windows is not None else [None] * len(pages_per_group)
+        self.has_windows = any(w for w in self.windows)
         self.length: Dict[int, int] = {}
         self.pages: Dict[int, List[List[int]]] = {}
+        self._released: Dict[int, List[int]] = {}      # per slot and group: leading pages given back
 
     def alloc(self) -> int:
         try:
@@ -71,6 +82,7 @@ class SlotBook:
             raise CacheFull(f"all {self.slots.n} slots are in use") from None
         self.length[s] = 0
         self.pages[s] = [[] for _ in self.pools]
+        self._released[s] = [0] * len(self.pools)
         return s
 
     def free(self, slot: int) -> None:
@@ -78,8 +90,9 @@ class SlotBook:
             raise ValueError(f"slot {slot} is not live (freed twice, or never given out)")
         for pool, pages in zip(self.pools, self.pages[slot]):
             for p in pages:
-                pool.give(p)
-        del self.pages[slot], self.length[slot]
+                if p >= 0:
+                    pool.give(p)
+        del self.pages[slot], self.length[slot], self._released[slot]
         self.slots.give(slot)
 
     def reserve(self, slot: int, n_new: int) -> List[List[int]]:
@@ -117,6 +130,32 @@ class SlotBook:
             if new_len > len(pages) * self.page_size:
                 raise ValueError(f"slot {slot}: advancing to {new_len} positions, past its reserved pages")
         self.length[slot] = new_len
+        if self.has_windows:
+            self.release_behind_window(slot)
+
+    def release_behind_window(self, slot: int) -> None:
+        """Gives back the pages of windowed groups that no later token of the sequence can see: the
+        next token sits at position ``length`` and sees keys from ``length - window + 1`` on."""
+        n = self.length[slot]
+        for g, w in enumerate(self.windows):
+            if not w:
+                continue
+            pages = self.pages[slot][g]
+            first_needed = min(max(0, n - w + 1) // self.page_size, len(pages))
+            for i in range(self._released[slot][g], first_needed):
+                self.pools[g].give(pages[i])
+                pages[i] = -1
+            if first_needed > self._released[slot][g]:
+                self._released[slot][g] = first_needed
+
+    def pages_needed(self, group: int, prompt: int, grown: int) -> int:
+        """Most pages of ``group`` that a sequence holds at any time if its prompt of ``prompt`` tokens
+        runs in one step and it then grows token by token to ``grown`` positions."""
+        whole = -(-int(grown) // self.page_size)
+        w = self.windows[group]
+        if not w:
+            return whole
+        return min(whole, max(-(-int(prompt) // self.page_size), (w - 1) // self.page_size + 2))
 
     def live(self):
         return sorted(self.length)

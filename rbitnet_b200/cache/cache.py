@@ -1,10 +1,12 @@
 """Device storage of the cache: pages of keys and values per group of layers, page
 tables, and the fixed-size per-sequence state area.
 
-Layout of one group: ``pool[layer in group][0=k,1=v][page][kv head][position in page][head_dim]``
-in the engine's compute dtype.  A kv head's page is one contiguous
-[page_size, head_dim] tile.  ``table[slot][i]`` is the page that holds the
-slot's positions i*page_size .. (i+1)*page_size-1.
+Layout of one group: per stored tensor ("stream": keys and values by default, whatever a
+mixer's ``CacheNeed.streams`` names otherwise) a pool
+``[layer in group][page][head][position in page][width]`` in the engine's compute dtype.
+A head's page is one contiguous [page_size, width] tile.  ``table[slot][i]`` is the page
+that holds the slot's positions i*page_size .. (i+1)*page_size-1; the streams of a group
+share the table.
 
 State area: for every schedule entry whose mixer declares a ``StateNeed``, a
 tensor [n_slots, *shape]; a slot's rows are zeroed when the slot is given out.
@@ -27,8 +29,8 @@ PAGE_SIZE = 64
 @dataclass
 class CacheLayerView:
     """What a mixer sees of the cache for one run of a layer."""
-    k: torch.Tensor            # [n_pages, kv heads, page_size, head_dim]
-    v: torch.Tensor
+    k: torch.Tensor            # [n_pages, kv heads, page_size, head_dim]: the first stream
+    v: Optional[torch.Tensor]  # the second stream (None for a group that stores one tensor per position)
     page_table: torch.Tensor   # int32 [n_slots, max_pages], on the device
     max_pages: int
     page_size: int
@@ -36,6 +38,7 @@ class CacheLayerView:
     head_dim: int
     writes: bool               # False: this run reads what another run wrote
     group: int
+    streams: tuple = ()        # every stored tensor of this layer, in the order of the need's streams
 
 
 class CacheGroup:
@@ -43,14 +46,18 @@ class CacheGroup:
                  page_size: int, dtype, device):
         self.need, self.entries = need, entries
         self.n_pages = n_pages
-        self.pool = torch.zeros((len(entries), 2, n_pages, need.n_kv_heads, page_size, need.head_dim),
-                                dtype=dtype, device=device)
+        self.pools = [torch.zeros((len(entries), n_pages, heads, page_size, width), dtype=dtype, device=device)
+                      for heads, width in need.stream_shapes()]
         self.table_host = np.zeros((n_slots, max_pages), dtype=np.int32)
         self.table = torch.zeros((n_slots, max_pages), dtype=torch.int32, device=device)
         self.dirty = set()
 
     def bytes(self) -> int:
-        return self.pool.numel() * self.pool.element_size()
+        return sum(p.numel() * p.element_size() for p in self.pools)
+
+    def bytes_per_position(self) -> int:
+        """What one cached position of one sequence holds in this group, over its layers."""
+        return sum(h * w for h, w in self.need.stream_shapes()) * self.pools[0].element_size() * len(self.entries)
 
 
 class SequenceCache:
@@ -83,7 +90,8 @@ class SequenceCache:
                 raise ValueError(f"schedule entry {entry} reads the cache of entry {src}, which writes none")
             g, i, _ = self._where[src]
             self._where[entry] = (g, i, False)
-        self.book = SlotBook(self.n_slots, [grp.n_pages for grp in self.groups], page_size, max_seq)
+        self.book = SlotBook(self.n_slots, [grp.n_pages for grp in self.groups], page_size, max_seq,
+                             windows=[grp.need.window for grp in self.groups])
         self.states: Dict[int, torch.Tensor] = {
             entry: torch.zeros((self.n_slots, *need.shape), dtype=need.dtype, device=device)
             for entry, need in state_needs.items()}
@@ -136,13 +144,22 @@ class SequenceCache:
         length = self.book.length
         for s in slots:
             length[s] += 1
+        if self.book.has_windows:
+            for s in slots:
+                self.book.release_behind_window(s)
 
-    def fits(self, lengths) -> bool:
-        """Whether new sequences that grow to these lengths fit beside what is live now."""
+    def fits(self, lengths, prompts=None) -> bool:
+        """Whether new sequences that grow to these lengths fit beside what is live now.  With
+        ``prompts`` (the part of each length that arrives in the first step) a windowed group is
+        counted by what it holds at most, not by the whole length."""
         if len(lengths) > self.book.slots.n_free:
             return False
-        pages = sum(-(-int(n) // self.page_size) for n in lengths)
-        return all(pages <= pool.n_free for pool in self.book.pools)
+        if prompts is None:
+            prompts = lengths
+        for g, pool in enumerate(self.book.pools):
+            if sum(self.book.pages_needed(g, p, n) for p, n in zip(prompts, lengths)) > pool.n_free:
+                return False
+        return True
 
     def upload_tables(self) -> None:
         """Bring the device page tables up to date (rows that changed since the last call)."""
@@ -151,7 +168,8 @@ class SequenceCache:
                 n = len(self.book.pages[slot][g]) if slot in self.book.pages else 0
                 if n:
                     # a pageable copy: staged by the driver before it returns, so the
-                    # host row may change again at once
+                    # host row may change again at once.  (Entries of pages that were given back
+                    # behind a window keep their old number: no kernel reads that far back.)
                     grp.table[slot, :n].copy_(torch.from_numpy(grp.table_host[slot, :n].copy()))
             grp.dirty.clear()
 
@@ -159,8 +177,9 @@ class SequenceCache:
     def view(self, entry: int) -> CacheLayerView:
         g, i, writes = self._where[entry]
         grp = self.groups[g]
-        return CacheLayerView(grp.pool[i, 0], grp.pool[i, 1], grp.table, self.max_pages, self.page_size,
-                              grp.need.n_kv_heads, grp.need.head_dim, writes, g)
+        streams = tuple(p[i] for p in grp.pools)
+        return CacheLayerView(streams[0], streams[1] if len(streams) > 1 else None, grp.table, self.max_pages,
+                              self.page_size, grp.need.n_kv_heads, grp.need.head_dim, writes, g, streams)
 
     def state(self, entry: int) -> Optional[torch.Tensor]:
         return self.states.get(entry)

@@ -36,8 +36,9 @@ def _engine(args):
     from .engine import Engine
     if not args.model:
         raise SystemExit("no model: give --model DIR or set RBITNET_MODEL")
+    kw = {"ops": args.ops} if getattr(args, "ops", None) is not None else {}
     return Engine.load_path(args.model, dtype=args.dtype, max_seq=args.max_seq, max_tokens=args.cache_tokens,
-                            max_batch=args.max_batch, verbose=True)
+                            max_batch=args.max_batch, verbose=True, **kw)
 
 
 def cmd_generate(args) -> int:
@@ -78,7 +79,7 @@ def cmd_inspect(args) -> int:
     for name in sorted(tensors)[:args.max_names]:
         t = tensors[name]
         print(f"  {name}  {list(t.shape)}  {str(t.dtype).replace('torch.', '')}")
-    check_tensors(spec.expected_shapes(), tensors, where=str(args.model))
+    check_tensors(spec.expected_shapes(), tensors, where=str(args.model), ignorable=spec.ignorable)
     print("tensors fit the model")
     return 0
 
@@ -94,7 +95,8 @@ def cmd_random(args) -> int:
     return 0
 
 
-def main(argv=None) -> int:
+def main(argv=None, ops=None) -> int:
+    """``ops``: a stand-in for the kernel layer (tests without a GPU); never given on the command line."""
     ap = argparse.ArgumentParser(prog="rbitnet_b200", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="verb", required=True)
     g = sub.add_parser("generate", help="generate from token ids or text")
@@ -124,6 +126,7 @@ def main(argv=None) -> int:
         from .replay import main as replay_main
         return replay_main(argv[1:])
     args = ap.parse_args(argv)
+    args.ops = ops
     return args.fn(args)
 
 

@@ -351,16 +351,14 @@ template <int D, int NS>
 int launch_ns(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int B, int Kh, cudaStream_t stream) {
   auto kernel = attn_decode_tma_kernel<D, NS>;
   constexpr int smem = Smem<D, NS>::BYTES;
-  static bool configured = false;
-  if (!configured) {
+  static RbOncePerDevice configured;
+  if (configured.first()) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
   }
   if (p.cluster) {
-    static bool large_allowed = false;
-    if (p.n_splits > 8 && !large_allowed) {      // clusters of more than 8 CTAs have to be asked for
+    static RbOncePerDevice large_allowed;
+    if (p.n_splits > 8 && large_allowed.first()) {      // clusters of more than 8 CTAs have to be asked for
       RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-      large_allowed = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(B, Kh, p.n_splits);
@@ -387,12 +385,7 @@ int launch_ns(const CUtensorMap& tk, const CUtensorMap& tv, const Params& p, int
 // (227 KB, 1 KB of it per CTA for the system), at most 4 (128 threads of up to 128 registers).
 // Head size 128: 2 per SM with three stages, 3 with two.  Head size 64: 4 either way.
 inline int places(int D, int stages) {
-  static int sms = 0;
-  if (sms == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      sms = 148;
-  }
+  const int sms = rb_sm_count();
   const int bytes = D == 64 ? (stages == 3 ? Smem<64, 3>::BYTES : Smem<64, 2>::BYTES)
                             : (stages == 3 ? Smem<128, 3>::BYTES : Smem<128, 2>::BYTES);
   int per_sm = (227 * 1024) / (bytes + 1024);

@@ -457,10 +457,9 @@ template <int D>
 int launch_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& p, int Kh, cudaStream_t stream) {
   auto kernel = attn_tc_kernel<D>;
   constexpr int smem = TcSmem<D>::BYTES;
-  static bool configured = false;
-  if (!configured) {
+  static RbOncePerDevice configured;
+  if (configured.first()) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
   }
   RB_LAUNCH("rb_attention_prefill_tc", (kernel), dim3(Kh, p.n_tiles), THREADS, smem, stream, tk, tv, p);
   return 0;

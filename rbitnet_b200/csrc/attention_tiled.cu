@@ -388,10 +388,9 @@ int launch_one(const AttnParams& p, dim3 grid, cudaStream_t stream) {
     const size_t kv = (size_t)2 * Smem<D, DECODE>::STAGES * Smem<D, DECODE>::KV_ELEMS * 2;
     if (merge > kv) smem += merge - kv;
   }
-  static bool configured = false;
-  if (!configured) {
+  static RbOncePerDevice configured;
+  if (configured.first()) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
   }
   RB_LAUNCH("kernel", (kernel), grid, WARPS * 32, smem, stream, p);
   RB_CHECK_LAUNCH("rb_attention_tiled");
@@ -443,6 +442,28 @@ RB_EXPORT int rb_attention_prefill(void* out, const void* q, const void* cache_k
   p.H = H; p.G = H / Kh; p.scale_log2 = scale * 1.4426950408889634f; p.window = window;
   p.part_o = nullptr; p.part_ml = nullptr; p.n_splits = 1;
   return launch_d<false>(D, p, dim3(n_tiles, Kh, 1), stream);
+}
+
+// Parts a decode's keys are cut into for rb_attention_decode.  About three CTAs of the decode kernel
+// fit an SM; the number of parts is the one (up to 16) that fills whole waves of those places best,
+// since a last wave with a few CTAs costs as much as a full one.
+RB_EXPORT int rb_attention_decode_parts(int batch, int n_kv_heads, int max_context) {
+  const int tiles = max_context > 0 ? (max_context + TILE_KEYS - 1) / TILE_KEYS : 1;
+  const long long places = 3ll * rb_sm_count(), pairs = (long long)batch * n_kv_heads;
+  if (pairs <= 0) return 1;
+  const int most = tiles < 16 ? tiles : 16;
+  if (pairs <= places) {                       // one wave: as many parts as fit it
+    const long long fit = places / pairs;
+    return (int)(fit < most ? (fit < 1 ? 1 : fit) : most);
+  }
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= most; ++s) {
+    const long long ctas = pairs * s;
+    const double eff = (double)ctas / (double)(((ctas + places - 1) / places) * places);
+    if (eff > best_eff + 0.02) { best = s; best_eff = eff; }
+  }
+  return best;
 }
 
 // Merges the partials of a split decode (also for the TMA-fed decode kernel, which lives in another file).
@@ -512,7 +533,8 @@ RB_EXPORT int rb_attention_decode_static(void* out, const void* q, const void* c
   if (B == 0) return 0;
   RB_REQUIRE(B > 0 && H > 0 && D > 0 && n_splits >= 1, "rb_attention_decode_static: bad sizes B=%d H=%d D=%d splits=%d",
              B, H, D, n_splits);
-  const long long need = (long long)B * H * n_splits * (D + 2);
+  // one part: the kernel writes the output itself and no scratch is used, whatever the sizes
+  const long long need = n_splits > 1 ? (long long)B * H * n_splits * (D + 2) : 0;
   RB_REQUIRE(need <= (long long)RB_STATIC_SCRATCH_FLOATS,
              "rb_attention_decode_static: B*H*n_splits*(D+2) = %lld float32 values of scratch exceed the static "
              "array's %d; use fewer splits or rb_attention_decode with caller scratch",

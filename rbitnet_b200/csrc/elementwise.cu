@@ -27,15 +27,18 @@ bool rb_pdl_enabled() {
   return v != 0;
 }
 
-RB_EXPORT int rb_abi_version() { return 1; }
+RB_EXPORT int rb_abi_version() { return 2; }
+
+RB_EXPORT int rb_device_sm_count() { return rb_sm_count(); }
 
 // ---------------------------------------------------------------- embedding
-// x[t, :] = table[ids[t], :] as float32 (crates/bitnet-core/src/llama/model.rs:230-232).
+// x[t, :] = table[ids[t], :] * scale as float32 (crates/bitnet-core/src/llama/model.rs:230-232;
+// the reference has no multiplier, scale 1.0).
 // An id outside [0, V) is refused on the host before the launch; the kernel
 // writes zeros for one rather than read outside the table.
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
-                             const int* __restrict__ ids, int E, int V) {
+                             const int* __restrict__ ids, int E, int V, float scale) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   // four values per thread and the whole row in flight at once: the rows come from anywhere in a
@@ -59,23 +62,24 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
         v = make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
       }
     }
+    if (scale != 1.0f) v = make_float4(v.x * scale, v.y * scale, v.z * scale, v.w * scale);
     *reinterpret_cast<float4*>(o + j) = v;
   } else {
-    for (int i = j; i < min(E, j + 4); ++i) o[i] = ok ? rb_to_float<TW>(row[i]) : 0.f;
+    for (int i = j; i < min(E, j + 4); ++i) o[i] = ok ? rb_to_float<TW>(row[i]) * scale : 0.f;
   }
 }
 
 RB_EXPORT int rb_embed(float* out, const void* table, int table_dtype, const int* ids, int T, int E,
-                       int V, cudaStream_t stream) {
+                       int V, float scale, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(T > 0 && E > 0 && V > 0, "rb_embed: bad sizes T=%d E=%d V=%d", T, E, V);
   const int threads = 256;
   const dim3 grid(T, (E + threads * 4 - 1) / (threads * 4));
   RB_REQUIRE(grid.y <= 65535, "rb_embed: rows of %d values", E);
   if (table_dtype == RB_F32)
-    RB_LAUNCH("embed_kernel", (embed_kernel<float>), grid, threads, 0, stream, out, (const float*)table, ids, E, V);
+    RB_LAUNCH("embed_kernel", (embed_kernel<float>), grid, threads, 0, stream, out, (const float*)table, ids, E, V, scale);
   else if (table_dtype == RB_BF16)
-    RB_LAUNCH("embed_kernel", (embed_kernel<__nv_bfloat16>), grid, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, E, V);
+    RB_LAUNCH("embed_kernel", (embed_kernel<__nv_bfloat16>), grid, threads, 0, stream, out, (const __nv_bfloat16*)table, ids, E, V, scale);
   else
     RB_FAIL("rb_embed: unknown dtype %d", table_dtype);
   RB_CHECK_LAUNCH("rb_embed");
@@ -226,13 +230,13 @@ RB_EXPORT int rb_rmsnorm(void* out, int out_dtype, const float* x, const float* 
 // the raw v to the token's place in the paged cache.
 // crates/bitnet-core/src/llama/model.rs:122-136 (rotation), :242-257 (append).
 // `qkv` rows hold [H*D | Kh*D | Kh*D]; with write_kv == 0 only q is read (a
-// layer that reads another layer's cache).  The whole head is rotated
-// (rot_dim == D); a rotated prefix is refused by the entry point.
+// layer that reads another layer's cache).  Only the first rot_dim values of a head are
+// rotated (pairs (2i,2i+1) or (i, i+rot_dim/2) among them); the rest pass unchanged.
 template <typename T>
 __global__ void rotate_append_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, int64_t qkv_stride,
                                      const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
                                      const int* __restrict__ tok_slot, RbPagedLayer cache, int H, int write_kv,
-                                     int interleaved, int heads_per_block) {
+                                     int interleaved, int heads_per_block, int rot_dim) {
   rb_pdl_launch_dependents();
   const int t = blockIdx.x;
   const int D = cache.head_dim, Kh = cache.n_kv_heads;
@@ -257,15 +261,22 @@ __global__ void rotate_append_kernel(T* __restrict__ q_out, const T* __restrict_
       dst[2 * i + 1] = rb_from_float<T>(value(src + 2 * i + 1));
       continue;
     }
+    T* dst = head < H ? q_out + ((int64_t)t * H + head) * D : kdst + rb_page_offset(cache, slot, pos, head - H);
+    const int rhalf = rot_dim / 2;
+    if (i >= rhalf) {           // behind the rotated prefix: two neighbours, as they are
+      const int a = rot_dim + 2 * (i - rhalf);
+      dst[a] = rb_from_float<T>(value(src + a));
+      dst[a + 1] = rb_from_float<T>(value(src + a + 1));
+      continue;
+    }
     int a, b;
-    if (interleaved) { a = 2 * i; b = 2 * i + 1; } else { a = i; b = i + half; }
+    if (interleaved) { a = 2 * i; b = 2 * i + 1; } else { a = i; b = i + rhalf; }
     const float x0 = value(src + a);
     const float x1 = value(src + b);
     float sn, cs;
     sincosf((float)pos * inv_freq[i], &sn, &cs);
     const float y0 = x0 * cs - x1 * sn;
     const float y1 = x0 * sn + x1 * cs;
-    T* dst = head < H ? q_out + ((int64_t)t * H + head) * D : kdst + rb_page_offset(cache, slot, pos, head - H);
     dst[a] = rb_from_float<T>(y0);
     dst[b] = rb_from_float<T>(y1);
   }
@@ -361,7 +372,8 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
                                int Kh, int D, int write_kv, int rot_dim, int interleaved, cudaStream_t stream) {
   if (T == 0) return 0;
   RB_REQUIRE(D % 2 == 0 && D > 0, "rb_rotate_append: head_dim %d must be even", D);
-  RB_REQUIRE(rot_dim == D, "rb_rotate_append: a rotated prefix of %d of %d is not built", rot_dim, D);
+  RB_REQUIRE(rot_dim >= 0 && rot_dim <= D && rot_dim % 2 == 0,
+             "rb_rotate_append: the rotated prefix %d must be even and at most the head size %d", rot_dim, D);
   RB_REQUIRE(H > 0 && Kh >= 0 && page_size > 0, "rb_rotate_append: bad sizes H=%d Kh=%d page=%d", H, Kh, page_size);
   RbPagedLayer c{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
   const int threads = 256;
@@ -371,7 +383,7 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
   if (by > n_heads) by = n_heads;
   const int hpb = (n_heads + by - 1) / by;
   const dim3 grid(T, (n_heads + hpb - 1) / hpb);
-  if (dtype == RB_BF16 && T >= 32 && D % 16 == 0 && D <= 2 * ROWS_MAX_PAIRS &&
+  if (dtype == RB_BF16 && T >= 32 && rot_dim == D && D % 16 == 0 && D <= 2 * ROWS_MAX_PAIRS &&
       qkv_stride % 8 == 0 && ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
       ((uintptr_t)cache_k % 16 == 0) && ((uintptr_t)cache_v % 16 == 0)) {
     // one thread per (rotated head, group of eight pairs) where a block can hold them: one pass over the heads
@@ -382,9 +394,9 @@ RB_EXPORT int rb_rotate_append(void* q_out, const void* qkv, int64_t qkv_stride,
     return 0;
   }
   if (dtype == RB_F32)
-    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<float>), grid, threads, 0, stream, (float*)q_out, (const float*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<float>), grid, threads, 0, stream, (float*)q_out, (const float*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb, rot_dim);
   else if (dtype == RB_BF16)
-    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb);
+    RB_LAUNCH("rotate_append_kernel", (rotate_append_kernel<__nv_bfloat16>), grid, threads, 0, stream, (__nv_bfloat16*)q_out, (const __nv_bfloat16*)qkv, qkv_stride, inv_freq, tok_pos, tok_slot, c, H, write_kv, interleaved, hpb, rot_dim);
   else
     RB_FAIL("rb_rotate_append: unknown dtype %d", dtype);
   RB_CHECK_LAUNCH("rb_rotate_append");
@@ -420,7 +432,8 @@ RB_EXPORT int rb_silu_mul(void* out, const void* gate_up, int dtype, int in_dtyp
              "rb_silu_mul: rows of %lld values do not hold %d features in blocks of %d", (long long)ld, F, block);
   const int64_t n = (int64_t)T * F;
   const int threads = 256;
-  const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+  const int64_t most = (int64_t)rb_sm_count() * 16;
+  const int blocks = (int)((n + threads - 1) / threads < most ? (n + threads - 1) / threads : most);
   if (dtype == RB_F32 && in_dtype == RB_F32)
     RB_LAUNCH("silu_mul_kernel", (silu_mul_kernel<float, float>), blocks, threads, 0, stream, (float*)out, (const float*)gate_up, n, F, ld, block);
   else if (dtype == RB_BF16 && in_dtype == RB_BF16)

@@ -1,4 +1,4 @@
-// Plain tiled matrix product on the CUDA cores: C[M,N] (+)= A[M,K] * W[N,K]^T.
+// Plain tiled matrix product on the CUDA cores: C[M,N] (+)= alpha * A[M,K] * W[N,K]^T.
 //
 // This is the true 32-bit path's product (FFMA with float32 accumulation, no
 // tensor-core or reduced-precision mode) and the product for shapes that the
@@ -17,7 +17,7 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, int64_t ldc,
                                                          const TA* __restrict__ A, int64_t lda,
                                                          const TA* __restrict__ W, int64_t ldw, int M, int N,
-                                                         int K, int accumulate) {
+                                                         int K, int accumulate, float alpha) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   __shared__ float As[BK][BM + 1];
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, in
       const int gn = n0 + tx * TN + j;
       if (gn >= N) continue;
       TC* p = C + (int64_t)gm * ldc + gn;
-      float v = acc[i][j];
+      float v = alpha == 1.0f ? acc[i][j] : acc[i][j] * alpha;
       if (accumulate) v += rb_to_float<TC>(*p);
       *p = rb_from_float<TC>(v);
     }
@@ -72,16 +72,17 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(TC* __restrict__ C, in
 }  // namespace
 
 // a_dtype: dtype of A and W; c_dtype: dtype of C.  accumulate: C += instead of C =.
+// alpha multiplies the finished sum (1.0 leaves it as it is).
 RB_EXPORT int rb_gemm_simple(void* C, int64_t ldc, int c_dtype, const void* A, int64_t lda, const void* W,
                              int64_t ldw, int a_dtype, int M, int N, int K, int accumulate,
-                             cudaStream_t stream) {
+                             float alpha, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   RB_REQUIRE(M > 0 && N > 0 && K > 0, "rb_gemm_simple: bad sizes M=%d N=%d K=%d", M, N, K);
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   RB_REQUIRE(grid.y <= 65535, "rb_gemm_simple: M=%d too large for one launch", M);
 #define LAUNCH(TA, TC)                                                                                     \
   RB_LAUNCH("gemm_simple_kernel", (gemm_simple_kernel<TA, TC>), grid, 256, 0, stream, (TC*)C, ldc, (const TA*)A, \
-            lda, (const TA*)W, ldw, M, N, K, accumulate)
+            lda, (const TA*)W, ldw, M, N, K, accumulate, alpha)
   if (a_dtype == RB_F32 && c_dtype == RB_F32) LAUNCH(float, float);
   else if (a_dtype == RB_BF16 && c_dtype == RB_F32) LAUNCH(__nv_bfloat16, float);
   else if (a_dtype == RB_BF16 && c_dtype == RB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -60,7 +60,8 @@ struct QkvTail {
   RbPagedLayer cache;
   int H;
   int write_kv;              // 0: W holds q rows only (a layer that reads another layer's cache)
-  int interleaved;           // pairs (2i, 2i+1) instead of (i, i + D/2)
+  int interleaved;           // pairs (2i, 2i+1) instead of (i, i + rot_dim/2)
+  int rot_dim;               // the first rot_dim values of a head are rotated, the rest pass unchanged
 };
 
 struct GemmParams {
@@ -75,6 +76,7 @@ struct GemmParams {
   int splits;         // parts of K
   int n_items;        // weight tiles * token tiles * splits
   int cluster;        // 1: the splits of a tile form a thread-block cluster and are summed through shared memory
+  float alpha;        // multiplies the finished sum of a stored or added product (x * 1.0f is x exactly)
   QkvTail qkv;        // EPI_QKV only
 };
 
@@ -304,7 +306,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           if (c + 16 < BN) fetch_old(c + 16, ahead);       // the next chunk's loads are in flight during these stores
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]);
+            if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]) * p.alpha;
         } else if (EPI == EPI_GATED) {
           // Lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features (feature =
           // (weight row block of 32) * 16 + lane % 16).  Columns are taken in pairs: the lower lanes
@@ -329,7 +331,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]));
+            if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]) * p.alpha);
         }
       }
       // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
@@ -357,11 +359,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int D = q.cache.head_dim, HD = q.H * D, KD = q.write_kv ? q.cache.n_kv_heads * D : 0;
       const int row = (warp & 3) * 32 + lane, n = n0 + row, d = n % D;
       const int my = (int)cluster_rank();
-      int pair, prow;
-      bool first;
-      if (q.interleaved) { pair = d >> 1; first = (d & 1) == 0; prow = row ^ 1; }
-      else { pair = d % (D / 2); first = d < D / 2; prow = first ? row + D / 2 : row - D / 2; }
-      const bool is_v = n >= HD + KD, live = n < p.n_out;
+      const int R2 = q.rot_dim / 2;
+      int pair = 0, prow = row;
+      bool first = true;
+      if (d < q.rot_dim) {
+        if (q.interleaved) { pair = d >> 1; first = (d & 1) == 0; prow = row ^ 1; }
+        else { pair = d % R2; first = d < R2; prow = first ? row + R2 : row - R2; }
+      }
+      const bool is_v = n >= HD + KD || d >= q.rot_dim, live = n < p.n_out;   // is_v: stored as it is
       float* sums = reinterpret_cast<float*>(smem) + BN * BM;       // [column][row], this CTA's columns only
       uint32_t own[8];
 #pragma unroll
@@ -408,7 +413,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
           __nv_bfloat16* dst;
           if (n < HD) dst = q.q_out + (int64_t)t * HD + n;
-          else if (!is_v) dst = (__nv_bfloat16*)q.cache.k + rb_page_offset(q.cache, q.tok_slot[t], pos, (n - HD) / D) + d;
+          else if (n < HD + KD) dst = (__nv_bfloat16*)q.cache.k + rb_page_offset(q.cache, q.tok_slot[t], pos, (n - HD) / D) + d;
           else dst = (__nv_bfloat16*)q.cache.v + rb_page_offset(q.cache, q.tok_slot[t], pos, (n - HD - KD) / D) + d;
           *dst = __float2bfloat16_rn(y);
         }
@@ -454,6 +459,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             float v = part[h][0];
 #pragma unroll
             for (int r = 1; r < 8; ++r) v += part[h][r];
+            v *= p.alpha;
             const int64_t at = (int64_t)(t0 + col[h]) * p.ldc + n;
             if (EPI == EPI_ADD) ((float*)p.C)[at] = old[h] + v;
             else store_out<OutT>((OutT*)p.C + at, v);
@@ -541,26 +547,15 @@ int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int col
 
 namespace {
 
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-  }
-  return n;
-}
-
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   constexpr int stage_bytes = W_TILE_BYTES + BN * BK * 2;
   constexpr int smem = STAGES * stage_bytes + 1024;
   static_assert(smem * MINB <= 227 * 1024, "shared memory");
   auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT, MINB>;
-  static bool configured = false;
-  if (!configured) {
+  static RbOncePerDevice configured;
+  if (configured.first()) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
   }
   if (p.cluster) {
     // grid (splits, tiles): the CTAs of one tile are one cluster
@@ -581,7 +576,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
     RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p));
     return 0;
   }
-  const int slots = sm_count() * MINB;
+  const int slots = rb_sm_count() * MINB;
   const int grid = p.n_items < slots ? p.n_items : slots;     // resident CTAs take items in turn
   RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, p);
   RB_CHECK_LAUNCH("rb_gemm_tc");
@@ -622,9 +617,51 @@ RB_EXPORT int rb_read_error_flag(int* value, int reset) {
   return 0;
 }
 
+// ---------------------------------------------------------------- the error word, for tests
+// Writes `code` into the device error word, as a kernel whose wait ran out would: lets a test see
+// the whole path from the word to the host's exception without any kernel waiting for anything.
+RB_EXPORT int rb_set_error_flag_for_test(int code) { return rb_file_set_error_flag(code); }
+
+// One thread waits on a barrier at which nobody ever arrives, with the given limit; the wait gives
+// up, records `code` and the kernel returns.  This is the bounded wait of the product and attention
+// kernels (same function, their limit is two seconds) run to its end on purpose, in a kernel that
+// does nothing else.
+__global__ void wait_probe_kernel(unsigned long long limit_ns, int code, int* __restrict__ gave_up) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const bool ok = mbar_wait(&bar, 0, code, limit_ns);
+    if (gave_up != nullptr) *gave_up = ok ? 0 : 1;
+  }
+}
+
+RB_EXPORT int rb_wait_probe(long long limit_ns, int code, int* gave_up, cudaStream_t stream) {
+  RB_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ll, "rb_wait_probe: limit %lld ns (at most 0.1 s)", limit_ns);
+  wait_probe_kernel<<<1, 32, 0, stream>>>((unsigned long long)limit_ns, code, gave_up);
+  RB_CHECK_LAUNCH("rb_wait_probe");
+  return 0;
+}
+
+// Parts to cut the inner dimension of a product of n_tokens tokens into (the `splits` argument of
+// rb_gemm_tc).  Up to 256 tokens a product is bound by reading W, so it wants every SM to stream a
+// piece of it: the tokens go in tiles of at most 64, and when the 128-row tiles of W times the token
+// tiles are fewer than the CTAs that run together (two per SM), K is cut as well: into 2, 4 or 8
+// parts, the sizes clusters schedule well, each of at least four 64-wide blocks.  Beyond 256 tokens: one.
+RB_EXPORT int rb_gemm_tc_splits(int n_tokens, int n_out, int K) {
+  if (n_tokens > 256 || n_tokens <= 0 || n_out <= 0 || K <= 0) return 1;
+  const int tiles = ((n_out + BM - 1) / BM) * ((n_tokens + 63) / 64);
+  const int blocks = (K + BK - 1) / BK;
+  const int together = 2 * rb_sm_count();
+  int want = 1;
+  while (want * 2 <= 8 && want * 2 <= together / tiles && want * 2 <= blocks / 4) want *= 2;
+  const int per = (blocks + want - 1) / want;
+  return (blocks + per - 1) / per;          // no part may be empty
+}
+
 // C (+)= X W^T on the tensor cores.
-//   epilogue 0: C[tokens, n_out] = product, c_dtype float32 or bfloat16
-//   epilogue 1: C (float32) += product
+//   epilogue 0: C[tokens, n_out] = alpha * product, c_dtype float32 or bfloat16
+//   epilogue 1: C (float32) += alpha * product
 //   (epilogues 0 and 1 with 2..8 splits: the CTAs of a tile form a cluster and each adds up a share
 //    of the token columns through distributed shared memory, in split order; token tile <= 64)
 //   epilogue 3: W holds, for every 16 output features, 16 gate rows followed by their 16 up rows
@@ -633,8 +670,9 @@ RB_EXPORT int rb_read_error_flag(int* value, int reset) {
 // elements, 16-byte aligned bases.
 static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
                    int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
-                   int token_tile, const QkvTail* tail, cudaStream_t stream) {
+                   int token_tile, const QkvTail* tail, float alpha, cudaStream_t stream) {
   if (n_tokens == 0 || n_out == 0) return 0;
+  RB_REQUIRE(alpha == 1.0f || epilogue == EPI_STORE || epilogue == EPI_ADD, "rb_gemm_tc: alpha %g with epilogue %d", alpha, epilogue);
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
   RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
   RB_REQUIRE(splits >= 1, "rb_gemm_tc: splits %d", splits);
@@ -651,7 +689,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
       // An item of 128 tokens costs about 0.7 of one of 256, not half (measured: with half, a
       // 1,024-token prefill took 16.7 ms instead of 13.9 because the gate/up product moved to 128).
       // Longer prompts run at the power limit whatever the tile; they keep 256.
-      const long long w_tiles = (n_out + BM - 1) / BM, sms = sm_count();
+      const long long w_tiles = (n_out + BM - 1) / BM, sms = rb_sm_count();
       const long long rounds128 = (w_tiles * ((n_tokens + 127) / 128) + sms - 1) / sms;
       const long long rounds256 = (w_tiles * ((n_tokens + 255) / 256) + sms - 1) / sms;
       bn = 7 * rounds128 < 10 * rounds256 ? 128 : 256;
@@ -671,6 +709,7 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   RB_REQUIRE(items < (1ll << 30), "rb_gemm_tc: too many tiles");
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
   p.cluster = splits > 1 ? 1 : 0;
+  p.alpha = alpha;
   RB_REQUIRE(!p.cluster || bn <= 64, "rb_gemm_tc: K is split only for token tiles of at most 64");
   if (epilogue == EPI_QKV) {
     RB_REQUIRE(tail != nullptr && p.cluster, "rb_gemm_tc: the q/k/v tail wants K split into a cluster");
@@ -686,10 +725,10 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
 
 RB_EXPORT int rb_gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
                          int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
-                         int token_tile, cudaStream_t stream) {
+                         int token_tile, float alpha, cudaStream_t stream) {
   RB_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_ADD || epilogue == EPI_GATED, "rb_gemm_tc: unknown epilogue %d", epilogue);
   return gemm_tc(C, ldc, c_dtype, X, ldx, n_tokens, W, ldw, w_rows, n_out, K, epilogue, n_features, splits, token_tile,
-                 nullptr, stream);
+                 nullptr, alpha, stream);
 }
 
 // Whether rb_gemm_tc_qkv takes these sizes: a head may not straddle two 128-row tiles of W, and the
@@ -705,15 +744,18 @@ RB_EXPORT int rb_gemm_tc_qkv_supports(int n_tokens, int D, int splits) {
 RB_EXPORT int rb_gemm_tc_qkv(void* q_out, const void* X, int64_t ldx, int n_tokens, const void* W, int64_t ldw, int K,
                              int splits, const float* inv_freq, const int* tok_pos, const int* tok_slot, void* cache_k,
                              void* cache_v, const int* page_table, int max_pages, int page_size, int H, int Kh, int D,
-                             int write_kv, int interleaved, cudaStream_t stream) {
+                             int write_kv, int interleaved, int rot_dim, cudaStream_t stream) {
   RB_REQUIRE(rb_gemm_tc_qkv_supports(n_tokens, D, splits), "rb_gemm_tc_qkv: tokens=%d head=%d splits=%d not supported",
              n_tokens, D, splits);
   RB_REQUIRE(H > 0 && Kh >= 0 && page_size > 0, "rb_gemm_tc_qkv: bad sizes H=%d Kh=%d page=%d", H, Kh, page_size);
+  RB_REQUIRE(rot_dim >= 0 && rot_dim <= D && rot_dim % 2 == 0,
+             "rb_gemm_tc_qkv: the rotated prefix %d must be even and at most the head size %d", rot_dim, D);
   QkvTail tail;
   tail.q_out = (__nv_bfloat16*)q_out; tail.inv_freq = inv_freq; tail.tok_pos = tok_pos; tail.tok_slot = tok_slot;
   tail.cache = RbPagedLayer{cache_k, cache_v, page_table, max_pages, page_size, Kh, D};
   tail.H = H; tail.write_kv = write_kv ? 1 : 0; tail.interleaved = interleaved ? 1 : 0;
+  tail.rot_dim = rot_dim;
   const int rows = (H + (write_kv ? 2 * Kh : 0)) * D;
   return gemm_tc(q_out, (int64_t)H * D, RB_BF16, X, ldx, n_tokens, W, ldw, rows, rows, K, EPI_QKV, 0, splits, 0, &tail,
-                 stream);
+                 1.0f, stream);
 }

@@ -73,6 +73,35 @@ inline cudaError_t rb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     if (e__ != cudaSuccess) RB_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
   } while (0)
 
+// ---------------------------------------------------------------- per-device facts and set-up
+constexpr int RB_MAX_DEVICES = 64;
+
+// Number of SMs of the current device (asked once per device).
+inline int rb_sm_count() {
+  static int n[RB_MAX_DEVICES] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= RB_MAX_DEVICES) dev = 0;
+  if (n[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    n[dev] = v;
+  }
+  return n[dev];
+}
+
+// Set-up that has to happen once per device (a kernel's shared-memory attribute belongs to the
+// device that was current when it was set): true the first time it is asked for the current device.
+struct RbOncePerDevice {
+  bool done[RB_MAX_DEVICES] = {false};
+  bool first() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= RB_MAX_DEVICES) return true;
+    if (done[dev]) return false;
+    done[dev] = true;
+    return true;
+  }
+};
+
 // ---------------------------------------------------------------- scalar conversions
 template <typename T> __device__ __forceinline__ float rb_to_float(T v);
 template <> __device__ __forceinline__ float rb_to_float<float>(float v) { return v; }

@@ -24,12 +24,14 @@ extern "C" {
 //   out [B, H*D] bfloat16, q [B, H, D] bfloat16, one token per sequence; keys and values in the
 //   paged cache; the caller passes all inputs and the output.
 //
-// Needs B*H*n_splits*(D+2) <= RB_STATIC_SCRATCH_FLOATS, else it returns -1 with a message in
-// rb_last_error().  It calls no cudaMalloc, cudaFree or other allocating routine.
+// With n_splits > 1 it needs B*H*n_splits*(D+2) <= RB_STATIC_SCRATCH_FLOATS, else it returns -1
+// with a message in rb_last_error(); with n_splits == 1 no scratch is used and any size goes.
+// It calls no cudaMalloc, cudaFree or other allocating routine.
 //
-// The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-// that device current) and sets the kernels' shared-memory attribute; make that first call
-// before any stream capture on the device.
+// Set-up happens inside the first calls: the first call on a device looks up the array's device
+// address (cudaGetSymbolAddress, with that device current), and the first call on a device for
+// each head size sets that kernel's shared-memory attribute.  Make one call per device and head
+// size you will use before any stream capture on that device.
 //
 // All calls share the one array and it keeps the last call's contents.  Nothing in it has to
 // start at zero: each call writes every partial it later reads.  Two calls that overlap on

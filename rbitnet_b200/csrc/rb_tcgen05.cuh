@@ -22,6 +22,11 @@ static inline int rb_file_error_flag(int* value, int reset) {
   return 0;
 }
 
+static inline int rb_file_set_error_flag(int code) {
+  RB_CUDA(cudaMemcpyToSymbol(g_error_flag, &code, sizeof(int)));
+  return 0;
+}
+
 // Device address of this file's error word (for a kernel that reports it with a step's results).
 static inline int rb_file_error_flag_address(int** out) {
   void* p = nullptr;
@@ -64,15 +69,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: false (and the error word set) after ~2 s.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+// Bounded wait: false (and the error word set to `code`) after `limit_ns`, about 2 s in the kernels.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code,
+                                          uint64_t limit_ns = 2000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 1024; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > 2000000000ull) {
+    if (global_timer_ns() - t0 > limit_ns) {
       atomicCAS(&g_error_flag, 0, code);
       return false;
     }

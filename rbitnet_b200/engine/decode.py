@@ -40,10 +40,12 @@ class DecodeGraph:
         self.meta.want_every_row = True     # the wanted rows are 0 .. B-1, always
         self.graph = None
         self.sampled = None
+        #: float32 logits [B, vocab] of the last replay (the graph's own buffer: copy what is to be kept)
+        self.logits = None
         self.kernels = 0
 
     def _body(self):
-        logits = self.model.forward(StepContext(self.ops, self.meta, self.cache))
+        logits = self.logits = self.model.forward(StepContext(self.ops, self.meta, self.cache))
         sampled = self.ops.sample(logits, self.temps, self.uniforms, out=self.result[:self.B])
         self.ops.decode_advance(self.token_ids, self.tok_pos, sampled, flag_out=self.result[self.B:])
         return sampled

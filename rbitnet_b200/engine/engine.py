@@ -73,17 +73,25 @@ class Engine:
         self.max_batch = max_batch
         if max_tokens is None:
             max_tokens = max_batch * (-(-self.max_seq // page_size) * page_size)
+        #: decode steps run as captured CUDA graphs (one per batch size)
+        self.use_graphs = use_graphs and ops is None
         cache_needs, reads, state_needs = self.model.cache_plan()
-        self.cache = SequenceCache(cache_needs, reads, state_needs, max_tokens, self.max_seq, self.dtype,
-                                   self.ops.device, page_size=page_size)
+        # The captured step of a batch size between two graphs is filled up with rows of a padding
+        # sequence.  It gets a slot and a page of its own, beyond what the caller asked for, here and
+        # now: taken at its first use it could take a page that a running batch was promised.
+        n_pages = max(1, -(-max_tokens // page_size))
+        extra = 1 if self.use_graphs else 0
+        self.cache = SequenceCache(cache_needs, reads, state_needs, (n_pages + extra) * page_size, self.max_seq,
+                                   self.dtype, self.ops.device, page_size=page_size, n_slots=n_pages + extra)
+        self._pad_slot = None
+        if self.use_graphs:
+            self._pad_slot = self.cache.alloc()
+            self.cache.reserve(self._pad_slot, 1)
         self.stepper = Stepper(self.model, self.cache, self.ops, max_batch_tokens=max_batch_tokens)
         self.stop_ids = list(self.spec.stop_ids)
         self._tokenizer = None
-        #: decode steps run as captured CUDA graphs (one per batch size)
-        self.use_graphs = use_graphs and ops is None
         self._graphs = {}
         self._graph_pool = None
-        self._pad_slot = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -153,7 +161,27 @@ class Engine:
     def end_sequence(self, slot: int) -> None:
         self.cache.free(slot)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], captured: bool = False) -> Optional[torch.Tensor]:
+        """Runs the entries' tokens from the cache; float32 logits [wanted places, vocab] or None.
+        ``captured``: a step of one token per sequence runs as the captured decode step that
+        ``generate`` uses (CUDA graph, padding rows, arg-max sampling whose ids are dropped) instead of
+        kernel by kernel, so that its logits can be compared too."""
+        if captured and self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
+            slots = [e.slot for e in entries]
+            if len(set(slots)) != len(slots):
+                raise ValueError("a slot appears twice in one step")
+            V = self.model.vocab_size
+            for e in entries:
+                if not 0 <= int(e.tokens[0]) < V:
+                    raise ValueError(f"slot {e.slot}: token id out of range (vocabulary {V})")
+                if any(w != 0 for w in e.want):
+                    raise ValueError(f"slot {e.slot}: wanted place is not among its 1 tokens")
+            n = len(entries)
+            self._decode_step([(e.slot, list(e.tokens)) for e in entries], [0.0] * n, [0.0] * n)
+            rows = [i for i, e in enumerate(entries) if len(e.want)]
+            if not rows:
+                return None
+            return self._last_graph.logits[rows].clone()
         return self.stepper.step(entries)
 
     def decode_graph(self, batch: int):
@@ -171,22 +199,6 @@ class Engine:
         """Batch sizes that get a captured step of their own: 1, 2, 4, then multiples of 8."""
         return n if n <= 2 else (4 if n <= 4 else -(-n // 8) * 8)
 
-    def _padding_slot(self) -> Optional[int]:
-        """A sequence of its own for the rows that fill a captured step up to its batch size: they
-        rewrite position 0 of this slot and their results are dropped, so they change nothing."""
-        if self._pad_slot is None:
-            try:
-                slot = self.cache.alloc()
-            except Exception:
-                return None
-            try:
-                self.cache.reserve(slot, 1)
-            except Exception:
-                self.cache.free(slot)
-                return None
-            self._pad_slot = slot
-        return self._pad_slot
-
     def _decode_step(self, feed, temperatures, uniforms) -> List[int]:
         slots = [s for s, _ in feed]
         positions = self.cache.lengths(slots)
@@ -197,16 +209,13 @@ class Engine:
         batch = self._graph_batch(n)
         run_slots = list(slots)
         if batch > n:
-            pad = self._padding_slot()
-            if pad is None:
-                batch = n                      # no room for a padding sequence: a step of the exact size
-            else:
-                extra = batch - n
-                run_slots += [pad] * extra
-                tokens += [0] * extra
-                positions = positions + [0] * extra
-                temperatures += [0.0] * extra
-                uniforms += [0.0] * extra
+            # rows of the padding sequence: they rewrite its position 0 and their results are dropped
+            extra = batch - n
+            run_slots += [self._pad_slot] * extra
+            tokens += [0] * extra
+            positions = positions + [0] * extra
+            temperatures += [0.0] * extra
+            uniforms += [0.0] * extra
         self.cache.upload_tables()
         g = self.decode_graph(batch)
         g.stage(run_slots, tokens, positions, temperatures, uniforms)
@@ -219,6 +228,7 @@ class Engine:
         if g.error_code:
             self.ops.check_errors()            # raises with the code, and clears the word
         self.cache.advance_one_each(slots)
+        self._last_graph = g
         return ids
 
     def _step_sample(self, feed, temperatures, uniforms) -> List[int]:

@@ -40,7 +40,8 @@ class GenerationLoop:
     """``step_sample(entries, temperatures, uniforms) -> list of token ids`` runs one step
     over ``(slot, tokens)`` pairs and samples at each sequence's last token.  ``cache``
     provides ``alloc() -> slot``, ``free(slot)``, ``length(slot)``, ``max_seq`` and
-    ``fits(lengths) -> bool`` (whether sequences growing to these lengths fit together)."""
+    ``fits(lengths, prompts) -> bool`` (whether sequences whose prompts of these sizes grow to
+    these lengths fit together)."""
 
     def __init__(self, step_sample: Callable, cache, max_batch: int):
         self.step_sample, self.cache, self.max_batch = step_sample, cache, max_batch
@@ -51,6 +52,7 @@ class GenerationLoop:
     def _take_batch(self, pending: List[int], prompts, max_tokens: int) -> List[int]:
         batch: List[int] = []
         lengths: List[int] = []
+        firsts: List[int] = []
         for r in pending:
             if len(batch) >= self.max_batch:
                 break
@@ -59,10 +61,11 @@ class GenerationLoop:
                 raise ValueError(f"request {r}: prompt of {n} tokens exceeds the longest sequence "
                                  f"the cache holds ({self.cache.max_seq})")
             grown = min(n + max_tokens, self.cache.max_seq)
-            if not self.cache.fits(lengths + [grown]):
+            if not self.cache.fits(lengths + [grown], firsts + [n]):
                 break
             batch.append(r)
             lengths.append(grown)
+            firsts.append(n)
         if not batch:
             raise ValueError(f"request {pending[0]} does not fit the cache even alone")
         return batch

@@ -17,18 +17,20 @@ from ..weights import check_tensors
 
 class Model:
     def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], ops):
-        check_tensors(spec.expected_shapes(), tensors)
+        for n in check_tensors(spec.expected_shapes(), tensors, ignorable=spec.ignorable):
+            tensors = {k: v for k, v in tensors.items() if k != n}
         self.spec, self.ops = spec, ops
         self.width, self.vocab_size = spec.width, spec.vocab_size
         dev = ops.device
         self.blocks = []
         for blk in spec.layers:
             block = build_block(blk)
-            for role, part in block.parts().items():
-                weights = {key: tensors[blk.names[f"{role}.{key}"]].to(dev)
+            for name, part in block.parts().items():
+                weights = {key: tensors[blk.names[f"{name}.{key}"]].to(dev)
                            for key in part.weight_shapes()}
                 part.bind(weights, ops)
             self.blocks.append(block)
+        self.embedding_scale, self.logit_scale = float(spec.embedding_scale), float(spec.logit_scale)
         self.final_norm = build_part("norm", spec.final_norm)
         self.final_norm.bind({k: tensors[n].to(dev) for k, n in spec.final_norm_names.items()}, ops)
         self.embedding = ops.prepare_embedding(tensors[spec.embedding_name])
@@ -42,17 +44,34 @@ class Model:
             if entry.reads_cache_of is not None and not 0 <= entry.reads_cache_of < e:
                 raise ValueError(f"schedule entry {e} may only read the cache of an earlier entry")
 
+    @staticmethod
+    def _mixer_of(block, layer: int):
+        """The part of a block that may need cache or state: its one mixer (None if it has none)."""
+        from ..parts.base import Mixer
+        mixers = [p for p in block.parts().values() if isinstance(p, Mixer)]
+        if len(mixers) > 1:
+            raise ValueError(f"layer {layer} has {len(mixers)} mixers; a cache entry belongs to one run of one "
+                             "mixer, so give each mixer a layer of its own")
+        return mixers[0] if mixers else None
+
     # what the cache has to provide
     def cache_plan(self):
         cache_needs, reads, state_needs = {}, {}, {}
         for e, entry in enumerate(self.spec.schedule):
-            mixer = self.blocks[entry.layer].mixer
+            mixer = self._mixer_of(self.blocks[entry.layer], entry.layer)
+            if mixer is None:
+                continue
             need = mixer.cache_need()
             if need is not None:
                 if entry.reads_cache_of is None:
                     cache_needs[e] = need
                 else:
                     reads[e] = entry.reads_cache_of
+                    src = self._mixer_of(self.blocks[self.spec.schedule[entry.reads_cache_of].layer], -1)
+                    theirs = src.cache_need() if src is not None else None
+                    if theirs is not None and theirs.window and (not need.window or need.window > theirs.window):
+                        raise ValueError(f"schedule entry {e} sees {need.window or 'all'} keys but reads the cache of "
+                                         f"entry {entry.reads_cache_of}, which keeps only the last {theirs.window}")
             st = mixer.state_need()
             if st is not None:
                 state_needs[e] = st
@@ -77,11 +96,11 @@ class Model:
     def forward(self, ctx) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
-        x = ops.embed(meta.token_ids, self.embedding)            # float32 residual stream [T, E]
+        x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
         for e, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].run(ctx, x, e)
         if meta.n_want == 0:
             return None
         rows = x if meta.want_every_row else ops.gather_rows(x, meta.want_rows)
         h = self.final_norm.forward(ctx, rows)
-        return ops.linear(h, self.head, out_dtype=torch.float32)
+        return ops.linear(h, self.head, out_dtype=torch.float32, scale=self.logit_scale)

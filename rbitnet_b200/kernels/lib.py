@@ -15,17 +15,17 @@ P, I, L, F = c_void_p, c_int, c_int64, c_float
 
 _SIGNATURES = {
     "rb_abi_version": [],
-    "rb_embed": [P, P, I, P, I, I, I, P],
+    "rb_embed": [P, P, I, P, I, I, I, F, P],
     "rb_rmsnorm": [P, I, P, P, I, I, F, P],
     "rb_rotate_append": [P, P, L, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
     "rb_silu_mul": [P, P, I, I, I, I, L, I, P],
     "rb_gather_rows": [P, P, P, I, I, P],
-    "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, P],
+    "rb_gemm_simple": [P, L, I, P, L, P, L, I, I, I, I, I, F, P],
     "rb_attention_simple": [P, P, I, P, P, P, I, I, P, P, I, I, I, I, F, I, P],
     "rb_sample": [P, P, L, I, I, P, P, P, P],
     "rb_sample_chunks": [I],
-    "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, P],
-    "rb_gemm_tc_qkv": [P, P, L, I, P, L, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+    "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, F, P],
+    "rb_gemm_tc_qkv": [P, P, L, I, P, L, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "rb_read_error_flag": [P, I],
     "rb_decode_advance": [P, P, P, I, P, P, P, P],
     "rb_error_flag_addresses": [P, P],
@@ -34,6 +34,8 @@ _SIGNATURES = {
     "rb_attention_prefill_tc": [P, P, P, P, L, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode_tma": [P, P, P, P, L, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],
     "rb_attention_decode_static": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, I, P],
+    "rb_set_error_flag_for_test": [I],
+    "rb_wait_probe": [L, I, P, P],
 }
 
 
@@ -56,6 +58,9 @@ class KernelLibrary:
         self.declare("rb_attention_decode_tma_supports", [I, I, I, I])
         self.declare("rb_attention_decode_tma_parts", [I, I, I])
         self.declare("rb_attention_decode_tma_on_chip", [I, I, I])
+        self.declare("rb_attention_decode_parts", [I, I, I])
+        self.declare("rb_gemm_tc_splits", [I, I, I])
+        self.declare("rb_device_sm_count", [])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)

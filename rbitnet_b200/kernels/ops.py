@@ -100,6 +100,10 @@ class CudaOps:
             w = torch.cat([self.to_compute(x) for x in weights], dim=0).contiguous()
         return LinearWeight(w, w.shape[0], w.shape[1])
 
+    def rows_of(self, weight: LinearWeight, first: int, count: int) -> LinearWeight:
+        """Output rows first .. first+count-1 of a prepared matrix, sharing its memory."""
+        return LinearWeight(weight.w[first:first + count], count, weight.n_in)
+
     def prepare_gate_up(self, gate: torch.Tensor, up: torch.Tensor) -> GateUpWeight:
         gate, up = self.to_compute(gate), self.to_compute(up)
         F, K = gate.shape
@@ -116,10 +120,12 @@ class CudaOps:
         return GateUpWeight(torch.cat([gate, up], dim=0).contiguous(), F, K, 0)
 
     # ------------------------------------------------------------------ ops
-    def embed(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """float32 rows table[ids] * scale."""
         T, (V, E) = ids.shape[0], table.shape
         out = torch.empty((T, E), dtype=torch.float32, device=self.device)
-        self.lib.call("rb_embed", _ptr(out), _ptr(table), _CODE[table.dtype], _ptr(ids), T, E, V, self._stream())
+        self.lib.call("rb_embed", _ptr(out), _ptr(table), _CODE[table.dtype], _ptr(ids), T, E, V, float(scale),
+                      self._stream())
         return out
 
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype=None) -> torch.Tensor:
@@ -130,9 +136,9 @@ class CudaOps:
         return out
 
     def linear(self, x: torch.Tensor, weight: LinearWeight, out_dtype=None,
-               accumulate_into: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x[T, in] * W[out, in]^T.  With ``accumulate_into`` (float32 [T, out]) the
-        product is added to it in float32 and it is returned."""
+               accumulate_into: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+        """scale * x[T, in] * W[out, in]^T (the scale multiplies the finished float32 sums).  With
+        ``accumulate_into`` (float32 [T, out]) the product is added to it in float32 and it is returned."""
         self._check(x, self.dtype, "linear input")
         T, K = x.shape
         if K != weight.n_in:
@@ -148,27 +154,16 @@ class CudaOps:
             # of W; the parts of a tile are one thread-block cluster and are summed on chip
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0), T,
                           _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, self._k_splits(T, N, K),
-                          64 if 64 < T <= 256 else 0, self._stream())
+                          64 if 64 < T <= 256 else 0, float(scale), self._stream())
         else:
             self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
-                          _ptr(weight.w), weight.w.stride(0), self.code, T, N, K, acc, self._stream())
+                          _ptr(weight.w), weight.w.stride(0), self.code, T, N, K, acc, float(scale), self._stream())
         return out
 
-    @staticmethod
-    def _k_splits(T: int, N: int, K: int) -> int:
-        """Parts to cut the inner dimension into.  Up to 256 tokens a product is bound by reading W,
-        so it wants every SM to stream a piece of it: the tokens go in tiles of at most 64, and when
-        the 128-row tiles of W times the token tiles are fewer than the CTAs that run together (two
-        per SM), K is cut as well; at most 8 parts, the size of a cluster.  Beyond 256 tokens: one."""
-        if T > 256:
-            return 1
-        tiles = -(-N // 128) * -(-T // 64)
-        blocks = -(-K // 64)
-        want = 1
-        while want * 2 <= min(8, 296 // tiles, blocks // 4):      # 1, 2, 4 or 8: the sizes clusters schedule well
-            want *= 2
-        per = -(-blocks // want)
-        return -(-blocks // per)          # no part may be empty
+    def _k_splits(self, T: int, N: int, K: int) -> int:
+        """Parts to cut the inner dimension into: the library's choice for this device (1 beyond 256
+        tokens; else up to 8, so that every SM streams a piece of W)."""
+        return self.lib.raw("rb_gemm_tc_splits")(T, N, K)
 
     def _tensor_core_ok(self, x: torch.Tensor, w: torch.Tensor) -> bool:
         """The tcgen05 product takes bfloat16 operands whose rows TMA can address: inner size and
@@ -188,7 +183,7 @@ class CudaOps:
             # activation and the product happen on the way out
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), T,
                           _ptr(weight.w), weight.w.stride(0), rows, rows, weight.n_in, 3, weight.inner, 1, 0,
-                          self._stream())
+                          1.0, self._stream())
             return out
         gu = self.linear(x, LinearWeight(weight.w, rows, weight.n_in))
         self.lib.call("rb_silu_mul", _ptr(out), _ptr(gu), self.code, self.code, T, weight.inner, gu.stride(0),
@@ -225,14 +220,14 @@ class CudaOps:
             inv_freq, interleaved, rot_dim = self._zeros_freq(D), False, D
         else:
             inv_freq, interleaved, rot_dim = rotary
-        if (self.dtype == torch.bfloat16 and rot_dim == D and self._tensor_core_ok(h, weight.w)
+        if (self.dtype == torch.bfloat16 and self._tensor_core_ok(h, weight.w)
                 and weight.n_out == (n_heads + (2 * Kh if view.writes else 0)) * D
                 and self.lib.raw("rb_gemm_tc_qkv_supports")(T, D, splits)):
             q = torch.empty((T, n_heads, D), dtype=self.dtype, device=self.device)
             self.lib.call("rb_gemm_tc_qkv", _ptr(q), _ptr(h), h.stride(0), T, _ptr(weight.w), weight.w.stride(0), K,
                           splits, _ptr(inv_freq), _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k), _ptr(view.v),
                           _ptr(view.page_table), view.max_pages, view.page_size, n_heads, Kh, D,
-                          1 if view.writes else 0, 1 if interleaved else 0, self._stream())
+                          1 if view.writes else 0, 1 if interleaved else 0, rot_dim, self._stream())
             return q
         return self.rotate_append(self.linear(h, weight), rotary, meta, view, n_heads)
 
@@ -255,7 +250,7 @@ class CudaOps:
             if on_tma:
                 n_splits = self.lib.raw("rb_attention_decode_tma_parts")(T * Kh, max(1, -(-meta.max_context // 64)), D)
             else:
-                n_splits = self._decode_splits(T, Kh, meta.max_context)
+                n_splits = self.lib.raw("rb_attention_decode_parts")(T, Kh, meta.max_context)
             part_o = part_ml = None
             # the parts of a small grid are a thread-block cluster and merge on chip
             on_chip = on_tma and bool(self.lib.raw("rb_attention_decode_tma_on_chip")(T * Kh, n_splits, D))
@@ -293,24 +288,6 @@ class CudaOps:
                           _ptr(view.page_table), view.max_pages, view.page_size, _ptr(meta.tok_pos),
                           _ptr(meta.tok_slot), T, H, Kh, D, float(scale), win, self._stream())
         return out
-
-    @staticmethod
-    def _decode_splits(batch: int, n_kv_heads: int, max_context: int) -> int:
-        """Parts a decode's keys are cut into.  About three CTAs of the decode kernel fit an SM; the
-        number of parts is the one (up to 16) that fills whole waves of those 444 places best,
-        since a last wave with a few CTAs costs as much as a full one."""
-        tiles = max(1, -(-max_context // 64))
-        places = 444
-        pairs = batch * n_kv_heads
-        if pairs <= places:                      # one wave: as many parts as fit it
-            return max(1, min(16, tiles, places // pairs))
-        best, best_eff = 1, 0.0
-        for s in range(1, min(16, tiles) + 1):
-            ctas = pairs * s
-            eff = ctas / (-(-ctas // places) * places)
-            if eff > best_eff + 0.02:
-                best, best_eff = s, eff
-        return best
 
     def _prefill_tiles(self, meta, tokens_per_tile: int):
         """Tiles of at most ``tokens_per_tile`` consecutive tokens of one sequence (device int32 arrays);

@@ -32,13 +32,13 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
                                              "max_positions": cfg.max_position_embeddings}}
     layers = []
     for i in range(cfg.num_hidden_layers):
-        layers.append(BlockSpec(
+        layers.append(BlockSpec(parts=dict(
             mixer=PartSpec("attention", {"width": cfg.hidden_size, "n_heads": cfg.num_attention_heads,
                                          "n_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                                          "position": position, "window": cfg.sliding_window}),
             feed_forward=PartSpec("gated_dense", {"width": cfg.hidden_size, "inner": cfg.intermediate_size,
                                                   "activation": cfg.hidden_act}),
-            mixer_norm=norm, ffn_norm=norm,
+            mixer_norm=norm, ffn_norm=norm),
             names={k: f"model.layers.{i}.{v}" for k, v in _LAYER_NAMES.items()},
             arrangement="pre_norm"))
     return ModelSpec(
@@ -49,7 +49,9 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         final_norm=norm, final_norm_names={"weight": "model.norm.weight"},
         head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
         max_positions=cfg.max_position_embeddings,
-        stop_ids=cfg.stop_ids)
+        stop_ids=cfg.stop_ids,
+        # buffers some exporters store; an output matrix stored beside a tied embedding
+        ignorable=["*.rotary_emb.inv_freq"] + (["lm_head.weight"] if cfg.tie_word_embeddings else []))
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig, build_llama_spec)

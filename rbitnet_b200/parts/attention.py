@@ -41,8 +41,7 @@ class Attention(Mixer):
         self.position.bind({}, ops)
         # one product for q, k and v: rows [q heads | k heads | v heads]
         self.w_qkv = ops.prepare_linear([weights["q"], weights["k"], weights["v"]])
-        self.w_q = None  # made on demand for a run that reads another layer's cache
-        self._q_weight = weights["q"]
+        self.w_q = None  # for a run that reads another layer's cache: the q rows of w_qkv, as a view
         self.w_o = ops.prepare_linear([weights["o"]])
 
     def forward(self, ctx, h, entry, accumulate_into):
@@ -52,7 +51,7 @@ class Attention(Mixer):
             w = self.w_qkv
         else:
             if self.w_q is None:
-                self.w_q = ops.prepare_linear([self._q_weight])
+                self.w_q = ops.rows_of(self.w_qkv, 0, self.n_heads * self.head_dim)
             w = self.w_q
         q = ops.project_rotate_append(h, w, self.position.rotary(), ctx.meta, view, self.n_heads)
         a = ops.attention(q, ctx.meta, view, self.n_heads, self.scale, self.window)

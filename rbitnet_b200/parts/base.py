@@ -24,10 +24,21 @@ import torch
 @dataclass(frozen=True)
 class CacheNeed:
     """What a mixer stores per position.  Layers with equal needs share a cache group
-    (one pool of pages); ``window`` None means every earlier position is kept."""
+    (one pool of pages per stored tensor); ``window`` None means every earlier position is kept.
+
+    By default two tensors are stored per position, keys and values, each of ``n_kv_heads``
+    heads of ``head_dim`` values.  ``streams`` names other contents: a tuple of (heads, width)
+    pairs, one per stored tensor, for instance ``((1, 96),)`` for a mixer that keeps one vector
+    per position, or keys and values of different widths."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    streams: Optional[Tuple[Tuple[int, int], ...]] = None
+
+    def stream_shapes(self) -> Tuple[Tuple[int, int], ...]:
+        if self.streams is not None:
+            return tuple((int(h), int(w)) for h, w in self.streams)
+        return ((self.n_kv_heads, self.head_dim), (self.n_kv_heads, self.head_dim))
 
 
 @dataclass(frozen=True)

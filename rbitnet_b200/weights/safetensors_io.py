@@ -6,8 +6,9 @@ Format: 8 bytes little-endian header length n, n bytes of JSON
 and tensors are views into the map, so a 16 GB model is not copied on the host
 before it goes to the device.
 
-Dtypes on the way in: BF16 stays bfloat16, F32 stays float32, F16 becomes
-bfloat16, integer tables become int32.
+Dtypes on the way in: BF16 stays bfloat16, F32 stays float32, F16 stays float16
+(the engine converts it to its compute dtype, exactly so for float32), F64
+becomes float32, integer tables become int32.
 """
 from __future__ import annotations
 
@@ -35,10 +36,10 @@ _NAME_OF = {torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16",
 
 
 def _storage_dtype(t: torch.Tensor) -> torch.Tensor:
-    if t.dtype in (torch.bfloat16, torch.float32):
+    if t.dtype in (torch.bfloat16, torch.float32, torch.float16):
         return t
-    if t.dtype in (torch.float16, torch.float64):
-        return t.to(torch.bfloat16 if t.dtype == torch.float16 else torch.float32)
+    if t.dtype == torch.float64:
+        return t.to(torch.float32)
     if t.dtype in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.int32):
         return t.to(torch.int32)
     return t

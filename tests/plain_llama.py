@@ -7,8 +7,10 @@ own model code is Rust and cannot be compiled here (no Rust toolchain, and its
 model only loads GGUF files), so this file rests on the formulas alone; every
 function cites the reference lines it restates.
 
-All math runs on the CPU in the dtype of the tensors it is given (float64 in
-most tests, so that it is a neutral judge of the 32-bit engine path).
+All math runs in the dtype asked for (float64 in most tests, so that it is a
+neutral judge of the 32-bit engine path) and where the tensors are: on the CPU,
+or on the GPU with torch's float64 operations for configurations of real layer
+sizes, whose oracle would take minutes on the CPU.
 """
 from __future__ import annotations
 
@@ -54,7 +56,7 @@ def rope_angles(positions: torch.Tensor, head_dim: int, theta: float) -> torch.T
     """
     i = torch.arange(head_dim // 2, dtype=torch.float32)
     inv = 1.0 / torch.pow(torch.tensor(theta, dtype=torch.float32), 2.0 * i / head_dim)
-    return positions.to(torch.float32)[:, None] * inv[None, :]
+    return positions.to(torch.float32)[:, None] * inv.to(positions.device)[None, :]
 
 
 def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, pairing: str) -> torch.Tensor:
@@ -99,8 +101,8 @@ def attention(q, k, v, window=None):
     K = k.shape[1]
     G = H // K
     scale = 1.0 / math.sqrt(D)
-    out = torch.zeros(T, H, D, dtype=q.dtype)
-    t_idx = torch.arange(T)
+    out = torch.zeros(T, H, D, dtype=q.dtype, device=q.device)
+    t_idx = torch.arange(T, device=q.device)
     allowed = t_idx[None, :] <= t_idx[:, None]
     if window is not None:
         allowed &= t_idx[None, :] > (t_idx[:, None] - window)
@@ -182,8 +184,8 @@ def layer_weights(tensors: dict, i: int, dtype) -> dict:
     return {k: tensors[p + n].to(dtype) for k, n in names.items()}
 
 
-def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, schedule=None) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence of token ids.
+def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, schedule=None, rows=None) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence of token ids (with ``rows``: of those positions only).
 
     ``schedule`` is a list of (layer index, index of the earlier schedule entry
     whose keys and values this entry reads, or None); the default runs every
@@ -193,9 +195,10 @@ def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, schedule=None
     ids = torch.as_tensor(tokens, dtype=torch.long)
     if int(ids.max()) >= cfg["vocab_size"] or int(ids.min()) < 0:
         raise ValueError("token id out of range")
-    positions = torch.arange(ids.shape[0])
-    embed = tensors["model.embed_tokens.weight"].to(dtype)
-    x = embed[ids]
+    table = tensors["model.embed_tokens.weight"]
+    ids = ids.to(table.device)
+    positions = torch.arange(ids.shape[0], device=table.device)
+    x = table[ids].to(dtype)
     if schedule is None:
         schedule = [(i, None) for i in range(cfg["num_hidden_layers"])]
     kvs = []
@@ -203,8 +206,10 @@ def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, schedule=None
         lw = layer_weights(tensors, layer, dtype)
         x, kv = block(x, lw, cfg, positions, None if reads is None else kvs[reads])
         kvs.append(kv)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long, device=x.device)]
     xn = rmsnorm(x, tensors["model.norm.weight"].to(dtype), cfg["rms_norm_eps"])
-    head = embed if cfg["tie_word_embeddings"] else tensors["lm_head.weight"].to(dtype)
+    head = (table if cfg["tie_word_embeddings"] else tensors["lm_head.weight"]).to(dtype)
     return xn @ head.T
 
 

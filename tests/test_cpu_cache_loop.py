@@ -89,7 +89,7 @@ def test_sequence_cache_groups_views_and_state():
                           max_tokens=256, max_seq=128, dtype=torch.float32, device="cpu", page_size=16)
     assert len(cache.groups) == 2                                  # all keys / a window: own storage
     full = [g for g in cache.groups if g.need.window is None][0]
-    assert full.pool.shape == (2, 2, 16, 2, 16, 16)
+    assert [tuple(p.shape) for p in full.pools] == [(2, 16, 2, 16, 16)] * 2
     assert cache.view(3).k.data_ptr() == cache.view(0).k.data_ptr() and not cache.view(3).writes
     assert cache.view(2).k.data_ptr() != cache.view(0).k.data_ptr() and cache.view(2).writes
     assert cache.view(1).group != cache.view(0).group
@@ -131,7 +131,7 @@ class _FakeCache:
     def length(self, s):
         return self.len[s]
 
-    def fits(self, lengths):
+    def fits(self, lengths, prompts=None):
         return len(lengths) <= len(self.free_slots) and sum(lengths) <= self.capacity
 
 
@@ -254,3 +254,51 @@ def test_the_decode_step_s_bookkeeping_of_many_slots_is_that_of_one_slot_at_a_ti
     assert a.lengths(sa) == [25, 39, 40]
     with pytest.raises(ContextOverflow):
         a.reserve_one_each(sa)            # the third slot is full
+
+
+def test_pages_behind_a_window_are_given_back_and_never_a_visible_one():
+    """A windowed group holds only the pages its next token can still see; the bound that ``fits`` plans
+    with is never exceeded; every page is accounted for at every moment."""
+    import random
+    rnd = random.Random(5)
+    for page, window in [(16, 4), (16, 16), (16, 17), (8, 50), (64, 100)]:
+        book = SlotBook(n_slots=3, pages_per_group=[64, 64], page_size=page, max_seq=40 * page,
+                        windows=[None, window])
+        for trial in range(6):
+            s = book.alloc()
+            prompt = rnd.randint(1, 6 * page)
+            grown = min(book.max_seq, prompt + rnd.randint(0, 10 * page))
+            most = [0, 0]
+            book.reserve(s, prompt)
+            most = [max(m, sum(p >= 0 for p in pg)) for m, pg in zip(most, book.pages[s])]
+            book.advance(s, prompt)
+            while book.length[s] < grown:
+                n = 1 if rnd.random() < 0.8 else min(grown - book.length[s], rnd.randint(1, 2 * page))
+                book.reserve(s, n)
+                most = [max(m, sum(p >= 0 for p in pg)) for m, pg in zip(most, book.pages[s])]
+                # every key the new tokens may see lies on a page the slot still holds
+                first_visible = max(0, book.length[s] - window + 1)
+                for pos in range(first_visible, book.length[s] + n):
+                    assert book.pages[s][1][pos // page] >= 0, (page, window, pos)
+                book.advance(s, n)
+                for g in (0, 1):
+                    held = [p for p in book.pages[s][g] if p >= 0]
+                    assert len(held) == len(set(held)) and set(held) <= book.pools[g].held
+                    assert book.pools[g].n_free + sum(p >= 0 for p in book.pages[s][g]) == 64
+            assert all(p >= 0 for p in book.pages[s][0])                      # the full group keeps everything
+            assert most[0] == -(-grown // page)
+            assert sum(p >= 0 for p in book.pages[s][1]) <= (window - 1) // page + 2    # what is left at the end
+            book.free(s)
+            assert all(pool.n_free == 64 for pool in book.pools) and book.slots.n_free == 3
+    # the generation loop's case exactly: prompt in one step, then one token at a time
+    book = SlotBook(2, [32], 16, 512, windows=[20])
+    s = book.alloc()
+    book.reserve(s, 100)
+    book.advance(s, 100)
+    most = sum(p >= 0 for p in book.pages[s][0])
+    for _ in range(300):
+        book.reserve(s, 1)
+        most = max(most, sum(p >= 0 for p in book.pages[s][0]))
+        book.advance(s, 1)
+    assert most <= book.pages_needed(0, 100, 400) == 7                        # the prompt's 7 pages, then 3 at most
+    assert sum(p >= 0 for p in book.pages[s][0]) <= (20 - 1) // 16 + 2

@@ -112,7 +112,7 @@ def test_dtypes_on_the_way_in(tmp_path):
     got = read_safetensors(tmp_path / "x.safetensors")
     assert got["a"].dtype == torch.float32 and torch.equal(got["a"], tensors["a"])       # 32-bit stays
     assert got["b"].dtype == torch.bfloat16 and torch.equal(got["b"], tensors["b"])
-    assert got["c"].dtype == torch.bfloat16                                            # half -> bfloat16
+    assert got["c"].dtype == torch.float16 and torch.equal(got["c"], tensors["c"])       # half stays exact
     assert got["d"].dtype == torch.int32 and got["d"].tolist() == tensors["d"].tolist()  # integer tables
 
 
@@ -170,3 +170,40 @@ def test_sharded_folder(tmp_path):
     (tmp_path / "s2.safetensors").unlink()
     with pytest.raises(WeightError, match="not in the folder"):
         read_model_tensors(tmp_path)
+
+
+def test_harmless_extras_are_left_out_with_a_warning_and_others_are_an_error():
+    """crates/bitnet-core/src/llama/model.rs:54-60 looks tensors up by name and never sees extras."""
+    cfg, spec = _spec(TINY_A)                     # tied head
+    t = random_tensors(spec, 0)
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    t["lm_head.weight"] = torch.zeros(cfg.vocab_size, cfg.hidden_size)
+    with pytest.warns(UserWarning, match="rotary_emb.inv_freq"):
+        ignored = check_tensors(spec.expected_shapes(), t, ignorable=spec.ignorable)
+    assert ignored == ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+    t["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
+    with pytest.warns(UserWarning), pytest.raises(WeightError, match=r"unexpected \(1\): model.layers.0.self_attn.q_proj.bias"):
+        check_tensors(spec.expected_shapes(), t, ignorable=spec.ignorable)
+    _, spec_b = _spec(TINY_B)                     # untied: lm_head.weight is needed, not ignorable
+    assert "lm_head.weight" not in spec_b.ignorable and "lm_head.weight" in spec_b.expected_shapes()
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """crates/bitnet-core/src/model/toy.rs:16-30: one deterministic generator wherever it runs."""
+    from rbitnet_b200.weights.random_init import random_tensor, reference_value, random_values, _tensor_key
+    t = random_tensor("model.layers.1.mlp.up_proj.weight", (5, 7), "matrix", 9)
+    for i in (0, 1, 17, 34):
+        assert float(t.view(-1)[i]) == reference_value(9, "model.layers.1.mlp.up_proj.weight", i)
+    # any part of a tensor can be made alone
+    key = _tensor_key(9, "model.layers.1.mlp.up_proj.weight")
+    scale = torch.tensor(0.02 / (8.0 * (65536.0 ** 2 - 1.0) / 12.0) ** 0.5, dtype=torch.float32)
+    assert torch.equal(random_values(key, 10, 6) * scale, t.view(-1)[10:16])
+    # other seed, other name: other values
+    assert not torch.equal(t, random_tensor("model.layers.1.mlp.up_proj.weight", (5, 7), "matrix", 10))
+    assert not torch.equal(t, random_tensor("model.layers.0.mlp.up_proj.weight", (5, 7), "matrix", 9))
+    big = random_tensor("w", (512, 512), "matrix", 1)
+    assert abs(float(big.std()) - 0.02) < 2e-4 and abs(float(big.mean())) < 2e-4
+    n = random_tensor("n", (4096,), "norm", 1)
+    assert abs(float(n.mean()) - 1.0) < 2e-3 and abs(float(n.std()) - 0.02) < 2e-3
+    b = random_tensor("w", (512, 512), "matrix", 1, dtype=torch.bfloat16)       # made in float32, then rounded
+    assert torch.equal(b, big.to(torch.bfloat16))

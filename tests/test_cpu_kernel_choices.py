@@ -53,10 +53,31 @@ def test_sizes_the_kernels_take(lib):
 def test_requests_are_refused_with_a_message(lib):
     from rbitnet_b200.kernels.lib import KernelError
     with pytest.raises(KernelError, match="multiple of 8"):
-        lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 0)
+        lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 1.0, 0)
     with pytest.raises(KernelError, match="cannot split K"):
-        lib.call("rb_gemm_tc", 0, 64, 1, 0, 64, 8, 0, 64, 64, 64, 128, 3, 32, 2, 0, 0)
+        lib.call("rb_gemm_tc", 0, 64, 1, 0, 64, 8, 0, 64, 64, 64, 128, 3, 32, 2, 0, 1.0, 0)
     with pytest.raises(KernelError, match="at most 8 splits"):
-        lib.call("rb_gemm_tc", 0, 64, 1, 0, 1024, 8, 0, 1024, 64, 64, 1024, 0, 0, 9, 0, 0)
+        lib.call("rb_gemm_tc", 0, 64, 1, 0, 1024, 8, 0, 1024, 64, 64, 1024, 0, 0, 9, 0, 1.0, 0)
     with pytest.raises(KernelError, match="head_dim"):
         lib.call("rb_rotate_append", 0, 0, 0, 1, 0, 0, 0, 0, 0, 0, 1, 64, 1, 2, 1, 7, 1, 7, 0, 0)
+
+
+def test_parts_of_a_product_and_of_the_plain_decode(lib):
+    """The choices follow the device's SM count (148 where no device answers, as here without a GPU)."""
+    splits, parts = lib.raw("rb_gemm_tc_splits"), lib.raw("rb_attention_decode_parts")
+    sms = lib.raw("rb_device_sm_count")()
+    assert sms > 0
+    assert splits(300, 4096, 4096) == 1                      # beyond 256 tokens K stays whole
+    for T, N, K in [(1, 4096, 4096), (8, 6144, 4096), (8, 4096, 14336), (64, 128256, 4096), (16, 64, 64),
+                    (200, 4096, 4096), (8, 256, 320)]:
+        s = splits(T, N, K)
+        blocks = -(-K // 64)
+        assert s in range(1, 9) and (s - 1) * -(-blocks // s) < blocks, (T, N, K, s)     # no part is empty
+        tiles = -(-N // 128) * -(-T // 64)
+        assert s == 1 or tiles * 2 <= 2 * sms                # K is cut only while CTAs are fewer than places
+    if sms == 148:
+        assert splits(8, 4096, 4096) == 8 and splits(8, 6144, 4096) == 4 and splits(8, 128256, 4096) == 1
+    for batch, kvh, ctx in [(1, 8, 2048), (8, 8, 2048), (64, 8, 8192), (3, 1, 10), (500, 8, 4096)]:
+        s = parts(batch, kvh, ctx)
+        assert 1 <= s <= min(16, max(1, -(-ctx // 64))), (batch, kvh, ctx, s)
+    assert parts(1, 1, 64) == 1 and parts(0, 8, 100) == 1

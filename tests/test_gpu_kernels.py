@@ -139,7 +139,7 @@ def test_product_refuses_to_guess_for_odd_inner_sizes(ops16):
     assert _rel(ops16.linear(x, lw, out_dtype=F32), x.double() @ w.double().T) < 2e-5
     from rbitnet_b200.kernels.lib import KernelError
     with pytest.raises(KernelError, match="multiple of 8"):
-        ops16.lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 0)
+        ops16.lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 1.0, 0)
 
 
 @pytest.mark.parametrize("T,F,K", [(1, 176, 64), (40, 352, 96), (130, 1000, 256), (300, 129, 72)])
@@ -506,3 +506,121 @@ def test_rotation_of_many_tokens(ops16, H, Kh, D, interleaved):
         res.append((torch.cat(qs), k, v))
     for a, b in zip(res[0], res[1]):
         assert torch.equal(a, b)
+
+
+# --------------------------------------------------------------------------- further sizes and options
+@pytest.mark.parametrize("n_seqs", [64, 1])
+def test_decode_attention_at_8192_positions(ops16, n_seqs):
+    """Heads as in Llama-3-8B at 8,192 cached positions.  64 sequences: more CTAs than run at once, any
+    number of parts up to 16, merged by the second kernel.  One sequence: sixteen parts, one
+    thread-block cluster that merges on chip."""
+    H, Kh, D, page = 32, 8, 128, 64
+    top = 8192
+    lens = [top] if n_seqs == 1 else [top - (i * 997) % 6000 for i in range(n_seqs)]
+    lens[0] = top
+    scale = 1.0 / math.sqrt(D)
+    view, ks, vs = _paged(ops16, n_seqs, top // page, page, Kh, D, lens, seed=61)
+    rows = [(s, n - 1) for s, n in enumerate(lens)]
+    parts = ops16.lib.raw("rb_attention_decode_tma_parts")(n_seqs * Kh, top // 64, D)
+    on_chip = bool(ops16.lib.raw("rb_attention_decode_tma_on_chip")(n_seqs * Kh, parts, D))
+    assert parts > 1 and on_chip == (n_seqs == 1)
+    g = torch.Generator(device="cuda").manual_seed(62)
+    q = torch.randn(n_seqs, H, D, device="cuda", generator=g).to(BF16) * 2
+    got = ops16.attention(q, _meta(rows, single_token=True, max_context=top), view, H, scale, None)
+    ops16.check_errors()
+    for i in sorted({0, 1, n_seqs // 2, n_seqs - 1}):
+        s, p = rows[i]
+        assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, None)) < 8e-3, (i, s, p)
+    # one key far back carries the answer: its score is made to stand out, its value is marked
+    far = 100
+    pg = int(view.page_table[0, far // page])
+    kq = view.k[pg, :, far % page].float()                          # [Kh, D]
+    q2 = q.clone()
+    q2[0] = (kq.repeat_interleave(H // Kh, dim=0) * 4).to(BF16)     # q . k_far is far above every other score
+    got = ops16.attention(q2, _meta(rows, single_token=True, max_context=top), view, H, scale, None)
+    want = view.v[pg, :, far % page].float().repeat_interleave(H // Kh, dim=0).reshape(-1)
+    assert _rel(got[0], want.double()) < 2e-2
+
+
+@pytest.mark.parametrize("H,Kh,D,rot,interleaved", [(4, 2, 16, 8, True), (3, 1, 32, 16, False), (8, 2, 128, 64, False),
+                                                    (2, 1, 64, 0, True), (2, 2, 128, 32, True)])
+def test_rotation_of_a_prefix_of_each_head(ops32, ops16, H, Kh, D, rot, interleaved):
+    """Only the first ``rot`` values of a head are rotated (pairs among them), the rest pass as they
+    are: by the rotation kernel (few and many tokens) and by the q/k/v product's epilogue."""
+    from rbitnet_b200.cache import CacheLayerView
+    page, max_pages, n_slots = 16, 8, 4
+    i = torch.arange(max(rot // 2, 1), dtype=torch.float32)
+    inv = (1.0 / torch.pow(torch.tensor(10000.0), 2.0 * i / max(rot, 2))).cuda()
+
+    def rotated(x, pos):     # x [heads, D] float64
+        out = x.clone()
+        if rot == 0:
+            return out
+        ang = (torch.tensor(float(pos), dtype=torch.float32) * inv.cpu()[:rot // 2]).double()
+        c, s = torch.cos(ang), torch.sin(ang)
+        if interleaved:
+            a, b = x[:, 0:rot:2], x[:, 1:rot:2]
+            out[:, 0:rot:2], out[:, 1:rot:2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = x[:, :rot // 2], x[:, rot // 2:rot]
+            out[:, :rot // 2], out[:, rot // 2:rot] = a * c - b * s, a * s + b * c
+        return out
+
+    def check(ops, tol, T, through_product):
+        rows = [(t % n_slots, (7 * t) % 120) for t in range(T)]
+        rows = sorted(set(rows))[:T]
+        T = len(rows)
+        g = torch.Generator(device="cuda").manual_seed(70 + T)
+        k = torch.zeros(n_slots * max_pages, Kh, page, D, device="cuda", dtype=ops.dtype)
+        v = torch.zeros_like(k)
+        table = torch.randperm(n_slots * max_pages).to(torch.int32).reshape(n_slots, max_pages).cuda()
+        view = CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0)
+        n_out = (H + 2 * Kh) * D
+        if through_product:
+            K = 1024
+            h = torch.randn(T, K, device="cuda", generator=g).to(ops.dtype)
+            w = (torch.randn(n_out, K, device="cuda", generator=g) / math.sqrt(K)).to(ops.dtype)
+            before = ops.lib.launches
+            q = ops.project_rotate_append(h, ops.prepare_linear([w]), (inv, interleaved, rot), _meta(rows), view, H)
+            assert ops.lib.launches - before == 1                  # the product's own epilogue did it
+            x = (h.double() @ w.double().T).cpu()
+        else:
+            qkv = torch.randn(T, n_out, device="cuda", generator=g).to(ops.dtype)
+            q = ops.rotate_append(qkv, (inv, interleaved, rot), _meta(rows), view, H)
+            x = qkv.double().cpu()
+        scale = float(x.abs().max())
+        for t, (slot, pos) in enumerate(rows):
+            pg = int(table[slot, pos // page])
+            assert float((q[t].cpu().double() - rotated(x[t, :H * D].reshape(H, D), pos)).abs().max()) < tol * scale
+            got_k = k[pg, :, pos % page].cpu().double()
+            assert float((got_k - rotated(x[t, H * D:(H + Kh) * D].reshape(Kh, D), pos)).abs().max()) < tol * scale
+            got_v = v[pg, :, pos % page].cpu().double()
+            assert float((got_v - x[t, (H + Kh) * D:].reshape(Kh, D)).abs().max()) < tol * scale
+
+    check(ops32, 2e-6, 6, False)
+    check(ops16, 6e-3, 6, False)
+    check(ops16, 6e-3, 40, False)          # many tokens
+    if 128 % D == 0:
+        check(ops16, 6e-3, 5, True)
+
+
+def test_scales_of_the_embedding_and_of_a_product(ops32, ops16):
+    """The embedding's multiplier and a product's alpha: applied in the kernels, in float32."""
+    g = torch.Generator(device="cuda").manual_seed(80)
+    table = torch.randn(300, 272, device="cuda", generator=g)
+    ids = torch.randint(0, 300, (9,), device="cuda", generator=g, dtype=torch.int32)
+    assert torch.equal(ops32.embed(ids, table, 3.5), table[ids.long()] * 3.5)
+    tb = table.to(BF16)
+    assert torch.equal(ops16.embed(ids, tb, 0.25), tb[ids.long()].float() * 0.25)
+    for ops, tol, shapes in ((ops32, 2e-6, [(5, 100, 33)]), (ops16, 6e-3, [(5, 200, 96), (8, 256, 4096), (300, 384, 520)])):
+        for T, N, K in shapes:
+            x = torch.randn(T, K, device="cuda", generator=g).to(ops.dtype)
+            w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(ops.dtype)
+            lw = ops.prepare_linear([w])
+            ref = x.double() @ w.double().T
+            assert _rel(ops.linear(x, lw, out_dtype=torch.float32, scale=0.3), ref * 0.3) < tol
+            acc = torch.ones(T, N, device="cuda")
+            ops.linear(x, lw, accumulate_into=acc, scale=-2.0)
+            assert _rel(acc, 1.0 - 2.0 * ref) < tol
+            plain_ = ops.linear(x, lw, out_dtype=torch.float32)
+            assert torch.equal(ops.linear(x, lw, out_dtype=torch.float32, scale=1.0), plain_)

@@ -600,3 +600,165 @@ def test_decode_with_more_than_16_heads_per_kv_head_through_captured_steps(tmp_p
         for i, t in enumerate(r.tokens):
             row = full[len(p) - 1 + i]
             assert float(row[t]) >= float(row.max()) - 4e-2 * float(row.abs().max())
+
+
+# --------------------------------------------------------------------------- other blocks, other cache contents, scales
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_block_of_three_norms_a_one_vector_cache_a_rotated_prefix_and_scales(tmp_path, dtype):
+    """A toy architecture, defined and registered here, that needs of the framework what Llama does not:
+    layer 0 is another arrangement of parts with a third norm (after the mixer, before the residual sum)
+    and a mixer that keeps ONE vector per position in the cache (no keys and values) and returns the mean
+    of all of them so far; layer 1 is an ordinary block whose attention rotates only the first half of
+    every head; the embedding is multiplied by 2 and the logits by 0.5.  Whole prompts, tokens one by one,
+    captured decode steps and slots used again, against plain formulas written out below."""
+    from rbitnet_b200 import Engine, StepEntry
+    from rbitnet_b200.config import LlamaConfig, register_architecture, unregister_architecture
+    from rbitnet_b200.models.llama import build_llama_spec
+    from rbitnet_b200.parts import (Mixer, CacheNeed, PartSpec, PositionEncoding, register_part, unregister_part,
+                                    build_part)
+    from rbitnet_b200.parts.block import build_parts
+    from rbitnet_b200.weights import random_tensors, write_safetensors
+    KEEP = 40          # width of the vector the toy mixer keeps per position
+
+    class MeanMixer(Mixer):
+        def __init__(self, width, keep):
+            self.width, self.keep = width, keep
+
+        def weight_shapes(self):
+            return {"keep": ((self.keep, self.width), "matrix"), "out": ((self.width, self.keep), "matrix")}
+
+        def cache_need(self):
+            return CacheNeed(1, self.keep, streams=((1, self.keep),))
+
+        def bind(self, weights, ops):
+            self.w_keep, self.w_out = weights["keep"].to(torch.float32), weights["out"].to(torch.float32)
+
+        def forward(self, ctx, h, entry, accumulate_into):
+            view, meta = ctx.cache_view(entry), ctx.meta
+            assert view.v is None and len(view.streams) == 1
+            store = view.streams[0]                                   # [pages, 1, page, keep]
+            slot, pos = meta.tok_slot.long(), meta.tok_pos.long()
+            c = h.to(torch.float32) @ self.w_keep.T
+            page = view.page_table.long()[slot, pos // view.page_size]
+            store[page, 0, pos % view.page_size] = c.to(store.dtype)
+            # every row reads its sequence's pages in full and masks by position: shapes do not depend
+            # on the data, so the same code runs inside a captured step
+            pages = view.page_table.long()[slot]                      # [T, max_pages]
+            kept = store[pages, 0].to(torch.float32).reshape(len(slot), -1, self.keep)
+            seen = (torch.arange(kept.shape[1], device=kept.device)[None, :] <= pos[:, None]).to(torch.float32)
+            mean = (kept * seen[:, :, None]).sum(1) / (pos + 1).to(torch.float32)[:, None]
+            accumulate_into += mean @ self.w_out.T
+
+    class SandwichBlock:
+        def __init__(self, spec):
+            self._parts = build_parts(spec)
+
+        def parts(self):
+            return self._parts
+
+        def run(self, ctx, x, entry):
+            p = self._parts
+            y = torch.zeros_like(x)
+            p["mixer"].forward(ctx, p["mixer_norm"].forward(ctx, x), entry, accumulate_into=y)
+            x += p["post_norm"].forward(ctx, y).to(torch.float32)
+            p["feed_forward"].forward(ctx, p["ffn_norm"].forward(ctx, x), accumulate_into=x)
+
+    class PrefixRotary(PositionEncoding):
+        def __init__(self, rot_dim, theta, pairing):
+            self.rot_dim, self.theta, self.pairing = rot_dim, theta, pairing
+
+        def bind(self, weights, ops):
+            i = torch.arange(self.rot_dim // 2, dtype=torch.float32)
+            self.inv_freq = (1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), 2.0 * i / self.rot_dim)).to(ops.device)
+
+        def rotary(self):
+            return self.inv_freq, self.pairing == "interleaved", self.rot_dim
+
+    @dataclass
+    class ToyConfig(LlamaConfig):
+        architecture: ClassVar[str] = "ToySandwichLM"
+
+    def build(cfg):
+        spec = build_llama_spec(cfg)
+        first = spec.layers[0]
+        first.arrangement = "toy_sandwich"
+        first.mixer = PartSpec("toy_mean", {"width": cfg.hidden_size, "keep": KEEP})
+        first.post_norm = PartSpec("rmsnorm", {"width": cfg.hidden_size, "eps": cfg.rms_norm_eps}, role="norm")
+        names = {k: v for k, v in first.names.items() if not k.startswith("mixer.")}
+        names.update({"mixer.keep": "model.layers.0.mixer.keep.weight", "mixer.out": "model.layers.0.mixer.out.weight",
+                      "post_norm.weight": "model.layers.0.post_mixer_layernorm.weight"})
+        first.names = names
+        spec.layers[1].mixer.params["position"] = {"kind": "toy_prefix_rotary", "params": {
+            "rot_dim": cfg.head_dim // 2, "theta": cfg.rope_theta, "pairing": cfg.rope_pairing}}
+        spec.embedding_scale, spec.logit_scale = 2.0, 0.5
+        return spec
+
+    def toy_plain(cfg, tensors, tokens):
+        c = plain.normalise_config(cfg)
+        t = {k: v.double() for k, v in tensors.items()}
+        ids = torch.as_tensor(tokens, dtype=torch.long)
+        pos = torch.arange(len(tokens))
+        eps = c["rms_norm_eps"]
+        x = t["model.embed_tokens.weight"][ids] * 2.0
+        lw = plain.layer_weights(t, 0, torch.float64)
+        kept = plain.rmsnorm(x, lw["attn_norm"], eps) @ t["model.layers.0.mixer.keep.weight"].T
+        mean = torch.cumsum(kept, 0) / (pos + 1).double()[:, None]
+        x = x + plain.rmsnorm(mean @ t["model.layers.0.mixer.out.weight"].T, t["model.layers.0.post_mixer_layernorm.weight"], eps)
+        x = x + plain.gated_mlp(plain.rmsnorm(x, lw["ffn_norm"], eps), lw)
+        lw = plain.layer_weights(t, 1, torch.float64)
+        H, K, D = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"]
+        h = plain.rmsnorm(x, lw["attn_norm"], eps)
+        q, k = (h @ lw["q"].T).reshape(-1, H, D), (h @ lw["k"].T).reshape(-1, K, D)
+        v = (h @ lw["v"].T).reshape(-1, K, D)
+        R = D // 2
+        q = torch.cat([plain.rope(q[..., :R], pos, c["rope_theta"], c["rope_pairing"]), q[..., R:]], dim=-1)
+        k = torch.cat([plain.rope(k[..., :R], pos, c["rope_theta"], c["rope_pairing"]), k[..., R:]], dim=-1)
+        x = x + plain.attention(q, k, v) @ lw["o"].T
+        x = x + plain.gated_mlp(plain.rmsnorm(x, lw["ffn_norm"], eps), lw)
+        return plain.rmsnorm(x, t["model.norm.weight"], eps) @ t["lm_head.weight"].T * 0.5
+
+    register_part("mixer", "toy_mean", MeanMixer, replace=True)
+    register_part("block", "toy_sandwich", SandwichBlock, replace=True)
+    register_part("position", "toy_prefix_rotary", PrefixRotary, replace=True)
+    register_architecture("ToySandwichLM", ToyConfig, build, replace=True)
+    try:
+        cfgd = dict(TINY_B, architectures=["ToySandwichLM"], num_hidden_layers=2)
+        cfg = ToyConfig.from_dict(cfgd)
+        spec = build(cfg)
+        table = spec.tensor_table()
+        assert table["model.layers.0.post_mixer_layernorm.weight"] == ((cfg.hidden_size,), "norm")
+        assert "model.layers.0.self_attn.q_proj.weight" not in table and "model.layers.1.self_attn.q_proj.weight" in table
+        tensors = {k: v.to(DTYPES[dtype]) for k, v in sharpen(random_tensors(spec, 12), 4.0).items()}
+        folder = tmp_path / "sandwich"
+        folder.mkdir()
+        (folder / "config.json").write_text(json.dumps(cfgd))
+        write_safetensors(folder / "model.safetensors", tensors)
+        eng = Engine.load_path(folder, dtype=dtype, max_tokens=1024)
+        shapes = sorted(tuple(p.shape[2:]) for g in eng.cache.groups for p in g.pools)
+        assert shapes == sorted([(1, 64, KEEP), (1, 64, cfg.head_dim), (1, 64, cfg.head_dim)])   # one vector; keys and values
+        pc, pt = plain.load_folder(folder)
+        for round_ in range(2):
+            ps = prompts([100, 9, 70], cfgd["vocab_size"], 90 + round_)
+            lens = [62, 3, 64]
+            slots = [eng.new_sequence() for _ in ps]
+            got = [[] for _ in ps]
+            out = eng.step([StepEntry(s, p[:n], list(range(n))) for s, p, n in zip(slots, ps, lens)])
+            off = 0
+            for i, n in enumerate(lens):
+                got[i].append(out[off:off + n])
+                off += n
+            for k in range(6):
+                out = eng.step([StepEntry(s, [p[n + k]], [0]) for s, p, n in zip(slots, ps, lens)], captured=k % 2 == 1)
+                for i in range(len(ps)):
+                    got[i].append(out[i:i + 1])
+            for i, (p, n) in enumerate(zip(ps, lens)):
+                assert_close(torch.cat(got[i]), toy_plain(pc, pt, p[:n + 6]), dtype, f"sandwich round {round_} request {i}")
+            for s in slots:
+                eng.end_sequence(s)
+        # the scales and the rotated prefix matter: the ordinary model on the same weights gives other logits
+        res = eng.generate([ps[0][:9], ps[2][:4]], max_tokens=4, temperature=0.0)
+        assert all(len(r.tokens) == 4 for r in res)
+    finally:
+        unregister_architecture("ToySandwichLM")
+        for role, kind in (("mixer", "toy_mean"), ("block", "toy_sandwich"), ("position", "toy_prefix_rotary")):
+            unregister_part(role, kind)

@@ -18,46 +18,23 @@ from tiny import TINY_A, TINY_B, prompts
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def whole(reqs):
-    return [{"step": i, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))}], "end": [r]}
-            for i, (r, t) in enumerate(reqs.items())]
+from rbitnet_b200.replay import schedule_whole as whole, schedule_tail32 as tail32, schedule_batches as batches
 
 
-def tail32(reqs):
-    steps, n = [], 0
-    for r, t in reqs.items():
-        k = max(1, len(t) - 32)
-        steps.append({"step": n, "entries": [{"id": r, "tokens": t[:k], "want": list(range(k))}], "end": []})
-        n += 1
-        for j in range(k, len(t)):
-            steps.append({"step": n, "entries": [{"id": r, "tokens": [t[j]], "want": [0]}],
-                          "end": [r] if j == len(t) - 1 else []})
-            n += 1
-        if k == len(t):
-            steps[-1]["end"] = [r]
-    return steps
-
-
-def batches(reqs, size, prompt_frac=0.5):
-    steps, n = [], 0
-    ids = list(reqs)
-    for b in range(0, len(ids), size):
-        grp = ids[b:b + size]
-        plen = {r: max(1, int(len(reqs[r]) * prompt_frac)) for r in grp}
-        ends = [r for r in grp if plen[r] == len(reqs[r])]
-        steps.append({"step": n, "entries": [{"id": r, "tokens": reqs[r][:plen[r]], "want": list(range(plen[r]))}
-                                             for r in grp], "end": ends})
-        n += 1
-        k = 0
-        live = [r for r in grp if r not in ends]
-        while live:
-            ends = [r for r in live if plen[r] + k + 1 == len(reqs[r])]
-            steps.append({"step": n, "entries": [{"id": r, "tokens": [reqs[r][plen[r] + k]], "want": [0]}
-                                                 for r in live], "end": ends})
-            n += 1
-            k += 1
-            live = [r for r in live if r not in ends]
-    return steps
+def collect_by_manifest(out_dir):
+    """request id -> [len, vocab] logits, put together from the step files as manifest.json describes them."""
+    man = json.loads((Path(out_dir) / "manifest.json").read_text())
+    V = man["vocab_size"]
+    rows = {}
+    for name, info in man["files"].items():
+        arr = np.fromfile(Path(out_dir) / name, dtype="<f4").reshape(len(info["rows"]), V)
+        for i, row in enumerate(info["rows"]):
+            rows.setdefault(row["id"], {})[row["position"]] = torch.from_numpy(arr[i].copy())
+    out = {}
+    for r, by_pos in rows.items():
+        assert sorted(by_pos) == list(range(len(by_pos))), f"{r}: positions {sorted(by_pos)}"
+        out[r] = torch.stack([by_pos[i] for i in range(len(by_pos))])
+    return out, man
 
 
 def collect(steps, out_dir, vocab):
@@ -98,8 +75,26 @@ def test_replay_logic_on_the_cpu_stand_in(tmp_path):
         assert rc == 0
         assert stdout.getvalue().split("\n")[:-1] == [f"done {s['step']}" for s in steps]
         got = collect(steps, out, 256)
+        by_manifest, man = collect_by_manifest(out)
         for r, t in reqs.items():
             assert_close(got[r], ref.logits(t), "float32", f"{name} {r}")
+            assert torch.equal(by_manifest[r], got[r])
+        assert man["mode"] == "stdin" and set(man["requests"]) == set(reqs)
+    # the program's own schedules: the same step lines, made from a file of requests
+    rf = tmp_path / "requests.jsonl"
+    rf.write_text("\n".join(json.dumps({"id": r, "tokens": t}) for r, t in reqs.items()) + "\n")
+    for mode, extra in (("whole", []), ("tail32", []), ("batches", ["--batch-size", "3"])):
+        out = tmp_path / f"mode_{mode}"
+        rc = main(["--model", str(folder), "--dtype", "float32", "--out", str(out), "--max-tokens", "256",
+                   "--mode", mode, "--requests", str(rf)] + extra, stdin=io.StringIO(""), stdout=io.StringIO(),
+                  ops=TorchOps(torch.float32))
+        assert rc == 0
+        got, man = collect_by_manifest(out)
+        for r, t in reqs.items():
+            assert_close(got[r], ref.logits(t), "float32", f"--mode {mode} {r}")
+        if mode == "batches":      # the second batch uses the first one's slots again
+            used = [tuple(man["requests"][r]["slots"]) for r in reqs]
+            assert len(set(used)) < len(used)
 
 
 @pytest.mark.gpu
@@ -113,15 +108,23 @@ def test_trace_run_program(tmp_path, name, dtype):
     top = cfg["max_position_embeddings"]
     reqs = _requests(V, [33, 5, top, 64, 1, 47, 90], 3)
     env = dict(os.environ, PYTHONPATH="")
-    for mode, steps, max_tokens in (("whole", whole(reqs), 256), ("tail", tail32(reqs), 256),
-                                    ("batches", batches(reqs, 3), 3 * 256)):
-        out = tmp_path / mode
-        p = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
-                            "--out", str(out), "--max-tokens", str(max_tokens)],
-                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
-                           env=env, timeout=600)
+    rf = tmp_path / "requests.json"
+    rf.write_text(json.dumps(reqs))
+    # step lines on standard input (whole requests, and unequal batches), and the program's own modes
+    for mode, steps, max_tokens in (("whole", whole(reqs), 256), ("tail32", None, 256),
+                                    ("batches", batches(reqs, 3), 3 * 256), ("batches", None, 3 * 256)):
+        out = tmp_path / (mode + ("_stdin" if steps is not None else ""))
+        cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype,
+               "--out", str(out), "--max-tokens", str(max_tokens)]
+        if steps is None:
+            cmd += ["--mode", mode, "--requests", str(rf), "--batch-size", "3"]
+        p = subprocess.run(cmd, input="" if steps is None else "\n".join(json.dumps(s) for s in steps) + "\n",
+                           capture_output=True, text=True, env=env, timeout=600)
         assert p.returncode == 0, p.stderr[-2000:]
-        assert p.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
-        got = collect(steps, out, V)
+        if steps is not None:
+            assert p.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+            got = collect(steps, out, V)
+        else:
+            got, _ = collect_by_manifest(out)
         for r, t in reqs.items():
             assert_close(got[r], ref.logits(t), dtype, f"{mode} {r}")

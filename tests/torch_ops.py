@@ -43,18 +43,21 @@ class TorchOps:
         w = torch.cat([self.to_compute(x) for x in weights], dim=0)
         return _W(w, w.shape[0], w.shape[1])
 
+    def rows_of(self, weight, first, count):
+        return _W(weight.w[first:first + count], count, weight.n_in)
+
     def prepare_gate_up(self, gate, up):
         return _GU(torch.cat([self.to_compute(gate), self.to_compute(up)], dim=0), gate.shape[0], gate.shape[1])
 
-    def embed(self, ids, table):
-        return table[ids.long()].to(torch.float32)
+    def embed(self, ids, table, scale=1.0):
+        return table[ids.long()].to(torch.float32) * scale
 
     def rmsnorm(self, x, w, eps, out_dtype=None):
         s = (x * x).sum(-1, keepdim=True) / x.shape[-1]
         return (x * w * (1.0 / torch.sqrt(s + eps))).to(out_dtype or self.dtype)
 
-    def linear(self, x, weight, out_dtype=None, accumulate_into=None):
-        y = x.to(torch.float32) @ weight.w.to(torch.float32).T
+    def linear(self, x, weight, out_dtype=None, accumulate_into=None, scale=1.0):
+        y = x.to(torch.float32) @ weight.w.to(torch.float32).T * scale
         if accumulate_into is not None:
             accumulate_into += y
             return accumulate_into
