@@ -267,6 +267,139 @@ def print_timeline(engine, batch, context):
         engine.end_sequence(s_)
 
 
+class KernelTimer:
+    """Times every operation of a step with CUDA events around its launch(es), by wrapping the methods
+    of the engine's kernel layer.  The step must run kernel by kernel (not as a captured graph).  An
+    event between two launches ends the overlap that programmatic dependent launch gives neighbours,
+    so these are the times of the kernels alone, each starting on an idle GPU: their sum is above the
+    step's own time, and a kernel's share of its roofline here is a lower bound of what it reaches
+    inside the step."""
+    OPS = ("embed", "rmsnorm", "linear", "gated_linear", "project_rotate_append", "rotate_append", "attention",
+           "gather_rows", "sample", "decode_advance")
+
+    def __init__(self, ops):
+        self.ops, self.records, self._depth, self._saved = ops, [], 0, {}
+
+    def __enter__(self):
+        import torch
+        for name in self.OPS:
+            fn = getattr(self.ops, name)
+            self._saved[name] = fn
+
+            def wrapped(*a, _fn=fn, _name=name, **kw):
+                if self._depth:                        # an operation made of others is timed as a whole
+                    return _fn(*a, **kw)
+                self._depth += 1
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                try:
+                    out = _fn(*a, **kw)
+                finally:
+                    self._depth -= 1
+                e1.record()
+                self.records.append((_name, self._describe(_name, a, kw), e0, e1))
+                return out
+            setattr(self.ops, name, wrapped)
+        return self
+
+    def __exit__(self, *exc):
+        for name, fn in self._saved.items():
+            setattr(self.ops, name, fn)
+
+    @staticmethod
+    def _describe(name, a, kw):
+        """(label, bytes the operation has to move, flops)."""
+        el = lambda t: t.numel() * t.element_size()
+        if name in ("linear", "gated_linear", "project_rotate_append"):
+            x, w = a[0], a[1]
+            T, K = x.shape
+            N = w.w.shape[0]
+            n_out = getattr(w, "inner", N)
+            out_b = T * n_out * (4 if (kw.get("out_dtype") is not None and kw["out_dtype"].itemsize == 4) else 2)
+            if kw.get("accumulate_into") is not None:
+                out_b = 2 * T * n_out * 4
+            kind = {"linear": "product", "gated_linear": "gate/up product + SiLU*up",
+                    "project_rotate_append": "q/k/v product + rotation + append"}[name]
+            if kw.get("accumulate_into") is not None:
+                kind = "product + residual"
+            return f"{kind} [{T}x{K}]x[{N}x{K}]", el(w.w) + el(x) + out_b, 2.0 * T * N * K
+        if name == "attention":
+            q, meta, view, H = a[0], a[1], a[2], a[3]
+            T, _, D = q.shape
+            keys = sum(c.start + c.n_new for c in meta.seqs) if not meta.single_token else None
+            if keys is None:
+                keys = int(meta.tok_pos.sum()) + T
+            flops = 4.0 * H * D * (int(meta.tok_pos.sum()) + T)
+            return (f"attention {'decode' if meta.single_token else 'prefill'} [{T} tokens, {H}/{view.n_kv_heads} heads of {D}]",
+                    keys * view.n_kv_heads * D * 2 * q.element_size() + 2 * el(q), flops)
+        if name in ("rmsnorm", "embed", "gather_rows", "rotate_append"):
+            t = a[0]
+            return f"{name} [{t.shape[0]} rows]", 2 * el(t) if name != "embed" else t.shape[0] * a[1].shape[1] * 6, 0.0
+        if name == "sample":
+            return f"sample [{a[0].shape[0]} rows of {a[0].shape[1]}]", el(a[0]), 0.0
+        return name, 0, 0.0
+
+    def table(self, pk, reps):
+        """Aggregated over equal labels: [{label, calls per step, us per call, GB/s, TFLOP/s, frac}]."""
+        import torch
+        torch.cuda.synchronize()
+        agg = {}
+        for name, (label, nbytes, flops), e0, e1 in self.records:
+            d = agg.setdefault(label, {"calls": 0, "us": 0.0, "bytes": nbytes, "flops": flops})
+            d["calls"] += 1
+            d["us"] += e0.elapsed_time(e1) * 1e3
+        rows = []
+        for label, d in agg.items():
+            us = d["us"] / d["calls"]
+            bound_us = max(d["bytes"] / (pk["hbm_gbs"] * 1e9), d["flops"] / (pk["bf16_tflops"] * 1e12)) * 1e6
+            rows.append({"kernel": label, "calls_per_step": round(d["calls"] / reps, 2), "us": round(us, 2),
+                         "gb_s": round(d["bytes"] / us / 1e3, 1), "tflop_s": round(d["flops"] / us / 1e6, 2),
+                         "bound": "hbm" if d["bytes"] / (pk["hbm_gbs"] * 1e9) >= d["flops"] / (pk["bf16_tflops"] * 1e12) else "tensor",
+                         "frac": round(bound_us / us, 3) if us > 0 else None,
+                         "share_of_step": None})
+        total = sum(r["us"] * r["calls_per_step"] for r in rows)
+        for r in rows:
+            r["share_of_step"] = round(r["us"] * r["calls_per_step"] / total, 3)
+        rows.sort(key=lambda r: -r["share_of_step"])
+        return rows, total
+
+
+def kernel_tables(engine, batch, ctx, prefill_tokens, pk, reps=5):
+    """Per-kernel times, rates and roofline fractions of one decode step and one prefill step (both run
+    kernel by kernel through the step function; roofline = max(bytes / copy bandwidth, flops / burst
+    tensor rate), both measured)."""
+    import torch
+    from rbitnet_b200 import StepEntry
+    out = {}
+    slots = fill_cache(engine, batch, ctx, reps + 4)
+    feed = [StepEntry(s, [1], [0]) for s in slots]
+    for _ in range(2):
+        engine.step(feed)
+    with KernelTimer(engine.ops) as kt:
+        for _ in range(reps):
+            # the GPU idles for some milliseconds first, so that the host has queued the whole step
+            # by the time the first kernel starts and no event interval holds a wait for the host
+            torch.cuda._sleep(40_000_000)
+            engine.step(feed)
+        rows, total = kt.table(pk, reps)
+    out["decode"] = {"batch": batch, "context": ctx, "sum_of_kernels_us": round(total, 1), "kernels": rows}
+    for s in slots:
+        engine.end_sequence(s)
+    ids = torch.randint(0, engine.config.vocab_size, (prefill_tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+    for r in range(2):
+        s = engine.new_sequence()
+        if r == 0:
+            engine.step([StepEntry(s, ids, [prefill_tokens - 1])])
+        else:
+            with KernelTimer(engine.ops) as kt:
+                torch.cuda._sleep(40_000_000)
+                engine.step([StepEntry(s, ids, [prefill_tokens - 1])])
+                rows, total = kt.table(pk, 1)
+        engine.end_sequence(s)
+    out["prefill"] = {"tokens": prefill_tokens, "sum_of_kernels_us": round(total, 1), "kernels": rows}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -283,6 +416,9 @@ def main():
                          "other values are for further measurements and are named in config.seq_len)")
     ap.add_argument("--prefill-tokens", type=int, default=PROMPT_LEN,
                     help="with --phase prefill: the prompt's length (up to 8,000), for profiling other lengths")
+    ap.add_argument("--kernels", action="store_true",
+                    help="time every kernel of one decode step and one prefill step alone (CUDA events around eager "
+                         "launches) and print, per kernel, time, GB/s, TFLOP/s and the fraction of its roofline")
     ap.add_argument("--timeline", action="store_true",
                     help="print when each kernel of one decode step ran inside the captured graph, and exit")
     ap.add_argument("--shape", default="llama3_8b", choices=["llama3_8b", "llama2_7b", "tinyllama_1b"],
@@ -328,6 +464,17 @@ def main():
     if args.timeline:
         print_timeline(engine, args.batch, ctx)
         return 0
+    if args.kernels:
+        tables = kernel_tables(engine, args.batch, ctx, min(PROMPT_LEN, args.prefill_tokens), pk)
+        print(json.dumps({"kernels_of": shape_name, "layers": layers, "peaks": pk, **tables}))
+        for phase in ("decode", "prefill"):
+            t = tables[phase]
+            print(f"\n{phase}: sum of kernels {t['sum_of_kernels_us']:.1f} us", file=sys.stderr)
+            print(f"{'us':>9} {'calls':>6} {'share':>6} {'GB/s':>8} {'TFLOP/s':>8} {'bound':>6} {'frac':>6}  kernel", file=sys.stderr)
+            for r in t["kernels"]:
+                print(f"{r['us']:9.1f} {r['calls_per_step']:6.1f} {r['share_of_step']:6.3f} {r['gb_s']:8.1f} "
+                      f"{r['tflop_s']:8.2f} {r['bound']:>6} {r['frac']:6.3f}  {r['kernel']}", file=sys.stderr)
+        return 0
     if args.phase == "prefill":
         n_tok = max(1, min(8000, args.prefill_tokens))
         pf_ms = time_prefill(engine, n_tok, reps=max(1, min(3, steps)))
@@ -345,13 +492,15 @@ def main():
                 if b == args.batch:
                     points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
                 else:
-                    pms, _, _ = time_decode(engine, b, ctx, max(8, steps // 2), warmup)
+                    pms, _, _ = time_decode(engine, b, ctx, steps, warmup)
                     points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
             pf_ms = time_prefill(engine, PROMPT_LEN)
             flops = prefill_flops(cfg, layers, PROMPT_LEN)
             prefill = {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
                        "frac": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
-                       "peak_tflops": pk["bf16_tflops_sustained"], "peak": f"bf16 sustained, {pk['source']}"}
+                       "peak_tflops": pk["bf16_tflops_sustained"], "peak": f"bf16 sustained, {pk['source']}",
+                       "frac_burst": round(flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                       "peak_tflops_burst": pk["bf16_tflops"]}
     finally:
         sampler.stop()
 

@@ -12,11 +12,17 @@ from rbitnet_b200.config import config_from_dict
 from rbitnet_b200.config.registry import get_architecture
 from rbitnet_b200.weights import random_tensors, write_safetensors
 
-# Tolerances against the plain implementation run in float64 on the same stored
-# weights.  float32: rounding of float32 sums only.  bfloat16: activations between
-# kernels and the cache are rounded to bfloat16 (8 bits of mantissa) a few times
-# per layer; the residual stream, norms, softmax and sums are float32.
-TOL = {"float32": (1e-5, 1e-4), "bfloat16": (0.0, 2e-2)}
+# Tolerances (absolute, relative to the largest reference value) against the plain
+# implementation run in float64 on the same stored weights.
+# float32: rounding of float32 sums only.  The products add up to 14,336 terms one after the other
+# in float32 (the reference's order, crates/bitnet-core/src/llama/model.rs:72-74), whose rounding
+# errors walk to about sqrt(terms) * 2^-24 of the result: the largest error seen over all tests is
+# 6.4e-6 of the largest logit (the Llama-3-8B layer sizes; the tiny configurations stay below 1e-6),
+# so the band is the reference's own guideline of 1e-5 (docs/GOLDEN_TESTS.md:24) plus twice that.
+# bfloat16: activations between kernels and the cache are rounded to bfloat16 (8 bits of mantissa)
+# nine times per layer; the residual stream, norms, softmax and sums are float32.  See bf16_rtol;
+# the default is its value for the three layers of the deeper tiny configuration.
+TOL = {"float32": (1e-5, 2e-5), "bfloat16": (0.0, 2e-2)}
 
 
 #: largest error seen per dtype, as a fraction of the largest reference value (printed at the end of a run)
@@ -27,7 +33,10 @@ def bf16_rtol(layers: int) -> float:
     """The bfloat16 band for a model of ``layers`` layers, as a fraction of the largest reference
     value.  A layer rounds to bfloat16 at nine places (the normed inputs, q/k/v, the cache, P, the
     attention output, the gated activation), which moves the logits by up to about 1 % of the
-    largest one at any width; the layers' errors are independent and add in quadrature."""
+    largest one at any width when attention scores have a deviation of about one (measured: 0.9 to
+    1.1 % for one and two layers of the Llama-3-8B, Llama-2-7B and TinyLlama layer sizes, 1.8 % for
+    eight layers; scores twice as spread give twice the error, which is why the tests scale q and k
+    by 1 / (0.02 sqrt(width))); the layers' errors are independent and add in quadrature."""
     return 1.2e-2 * max(1.0, float(layers)) ** 0.5
 
 

@@ -528,7 +528,7 @@ def test_decode_attention_at_8192_positions(ops16, n_seqs):
     q = torch.randn(n_seqs, H, D, device="cuda", generator=g).to(BF16) * 2
     got = ops16.attention(q, _meta(rows, single_token=True, max_context=top), view, H, scale, None)
     ops16.check_errors()
-    for i in sorted({0, 1, n_seqs // 2, n_seqs - 1}):
+    for i in sorted({0, min(1, n_seqs - 1), n_seqs // 2, n_seqs - 1}):
         s, p = rows[i]
         assert _rel(got[i], _attn_ref(q[i], ks[s], vs[s], p, scale, None)) < 8e-3, (i, s, p)
     # one key far back carries the answer: its score is made to stand out, its value is marked

@@ -11,7 +11,7 @@ import pytest
 import torch
 
 import plain_llama as plain
-from helpers import assert_close, make_model_dir, PlainModel, sharpen
+from helpers import assert_close, make_model_dir, PlainModel, sharpen, TOL
 from tiny import TINY_A, TINY_B, prompts
 
 pytestmark = pytest.mark.gpu
@@ -344,7 +344,7 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path, dt
             seq = list(p)
             for t in r.tokens:
                 row = _toy_plain(pc, pt, seq)[-1]
-                tol = 2 * ((1e-5 + 1e-4 * float(row.abs().max())) if dtype == "float32" else 2e-2 * float(row.abs().max()))
+                tol = 2 * (TOL[dtype][0] + TOL[dtype][1] * float(row.abs().max()))
                 assert float(row[t]) >= float(row.max()) - tol
                 seq.append(t)
     finally:
@@ -700,7 +700,9 @@ def test_a_block_of_three_norms_a_one_vector_cache_a_rotated_prefix_and_scales(t
         pos = torch.arange(len(tokens))
         eps = c["rms_norm_eps"]
         x = t["model.embed_tokens.weight"][ids] * 2.0
-        lw = plain.layer_weights(t, 0, torch.float64)
+        p0 = "model.layers.0."
+        lw = {"gate": t[p0 + "mlp.gate_proj.weight"], "up": t[p0 + "mlp.up_proj.weight"], "down": t[p0 + "mlp.down_proj.weight"],
+              "attn_norm": t[p0 + "input_layernorm.weight"], "ffn_norm": t[p0 + "post_attention_layernorm.weight"]}
         kept = plain.rmsnorm(x, lw["attn_norm"], eps) @ t["model.layers.0.mixer.keep.weight"].T
         mean = torch.cumsum(kept, 0) / (pos + 1).double()[:, None]
         x = x + plain.rmsnorm(mean @ t["model.layers.0.mixer.out.weight"].T, t["model.layers.0.post_mixer_layernorm.weight"], eps)
