@@ -365,37 +365,45 @@ class KernelTimer:
 
 
 def kernel_tables(engine, batch, ctx, prefill_tokens, pk, reps=5):
-    """Per-kernel times, rates and roofline fractions of one decode step and one prefill step (both run
-    kernel by kernel through the step function; roofline = max(bytes / copy bandwidth, flops / burst
-    tensor rate), both measured)."""
+    """Per-kernel times, rates and roofline fractions of one decode step and one prefill step, both run
+    kernel by kernel (roofline = max(bytes / copy bandwidth, flops / burst tensor rate), both measured).
+    The step's inputs are on the device before the timed run, and the GPU idles for some milliseconds
+    first, so that the host has queued the whole step by the time its first kernel starts and no
+    event interval holds a wait for the host."""
+    import numpy as np
     import torch
-    from rbitnet_b200 import StepEntry
+    from rbitnet_b200.engine.step import SeqChunk, StepContext, build_meta
     out = {}
     slots = fill_cache(engine, batch, ctx, reps + 4)
-    feed = [StepEntry(s, [1], [0]) for s in slots]
+    g = engine.decode_graph(batch)                       # its buffers and its step body, run without capture
+    g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
     for _ in range(2):
-        engine.step(feed)
+        g._body()
+        g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
+    torch.cuda.synchronize()
     with KernelTimer(engine.ops) as kt:
         for _ in range(reps):
-            # the GPU idles for some milliseconds first, so that the host has queued the whole step
-            # by the time the first kernel starts and no event interval holds a wait for the host
             torch.cuda._sleep(40_000_000)
-            engine.step(feed)
+            g._body()
+            g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
         rows, total = kt.table(pk, reps)
     out["decode"] = {"batch": batch, "context": ctx, "sum_of_kernels_us": round(total, 1), "kernels": rows}
     for s in slots:
         engine.end_sequence(s)
-    ids = torch.randint(0, engine.config.vocab_size, (prefill_tokens,), generator=torch.Generator().manual_seed(1)).tolist()
-    for r in range(2):
-        s = engine.new_sequence()
-        if r == 0:
-            engine.step([StepEntry(s, ids, [prefill_tokens - 1])])
-        else:
-            with KernelTimer(engine.ops) as kt:
-                torch.cuda._sleep(40_000_000)
-                engine.step([StepEntry(s, ids, [prefill_tokens - 1])])
-                rows, total = kt.table(pk, 1)
-        engine.end_sequence(s)
+    ids = torch.randint(0, engine.config.vocab_size, (prefill_tokens,), generator=torch.Generator().manual_seed(1))
+    s = engine.new_sequence()
+    engine.cache.reserve(s, prefill_tokens)
+    engine.cache.upload_tables()
+    meta = build_meta([SeqChunk(s, 0, prefill_tokens, 0)], ids.numpy().astype(np.int32),
+                      np.asarray([prefill_tokens - 1], dtype=np.int32), engine.ops.device)
+    ctx_ = StepContext(engine.ops, meta, engine.cache)
+    engine.model.forward(ctx_)                           # also makes the attention's tile lists
+    torch.cuda.synchronize()
+    with KernelTimer(engine.ops) as kt:
+        torch.cuda._sleep(40_000_000)
+        engine.model.forward(ctx_)
+        rows, total = kt.table(pk, 1)
+    engine.end_sequence(s)
     out["prefill"] = {"tokens": prefill_tokens, "sum_of_kernels_us": round(total, 1), "kernels": rows}
     return out
 

@@ -103,3 +103,5 @@ RB_EXPORT int rb_attention_simple(void* out, const void* q, int dtype, const voi
                                  scale, window, stream);
   RB_FAIL("rb_attention_simple: unknown dtype %d", dtype);
 }
+
+RB_CHECK_READER(attention_simple)

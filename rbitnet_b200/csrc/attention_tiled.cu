@@ -546,3 +546,5 @@ RB_EXPORT int rb_attention_decode_static(void* out, const void* q, const void* c
   return rb_attention_decode(out, q, cache_k, cache_v, page_table, max_pages, page_size, tok_pos, tok_slot, B, H,
                              Kh, D, scale, window, part_o, part_ml, n_splits, stream);
 }
+
+RB_CHECK_READER(attention_tiled)

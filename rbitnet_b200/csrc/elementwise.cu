@@ -31,6 +31,15 @@ RB_EXPORT int rb_abi_version() { return 2; }
 
 RB_EXPORT int rb_device_sm_count() { return rb_sm_count(); }
 
+// 1: the library was built with -DRB_CHECKED (cache addresses are checked before they are used).
+RB_EXPORT int rb_is_checked_build() {
+#ifdef RB_CHECKED
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 // ---------------------------------------------------------------- embedding
 // x[t, :] = table[ids[t], :] * scale as float32 (crates/bitnet-core/src/llama/model.rs:230-232;
 // the reference has no multiplier, scale 1.0).
@@ -498,3 +507,5 @@ RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled
   RB_CHECK_LAUNCH("rb_decode_advance");
   return 0;
 }
+
+RB_CHECK_READER(elementwise)

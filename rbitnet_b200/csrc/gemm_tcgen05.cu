@@ -759,3 +759,5 @@ RB_EXPORT int rb_gemm_tc_qkv(void* q_out, const void* X, int64_t ldx, int n_toke
   return gemm_tc(q_out, (int64_t)H * D, RB_BF16, X, ldx, n_tokens, W, ldw, rows, rows, K, EPI_QKV, 0, splits, 0, &tail,
                  1.0f, stream);
 }
+
+RB_CHECK_READER(gemm_tcgen05)

@@ -173,7 +173,43 @@ struct RbPagedLayer {
   int head_dim;
 };
 
+// ---------------------------------------------------------------- the checked build
+// With -DRB_CHECKED (RBITNET_CHECKED=1 when the library is built) every cache address that goes
+// through rb_page_offset is checked first: a slot, position or kv head outside what the layer holds
+// is recorded in a device word (code 21, then the slot, the position and the kv head) and the
+// access goes to offset 0 instead of outside the cache.  Each source file has its own word and
+// exports a reader for it (RB_CHECK_READER); the host asks them all after a step.
+#ifdef RB_CHECKED
+static __device__ int g_check_word[4] = {0, 0, 0, 0};
+#define RB_CHECK_READER(tu)                                                        \
+  RB_EXPORT int rb_check_word_##tu(int* out4, int reset) {                         \
+    RB_CUDA(cudaMemcpyFromSymbol(out4, g_check_word, 4 * sizeof(int)));            \
+    if (reset && out4[0] != 0) {                                                   \
+      int z[4] = {0, 0, 0, 0};                                                     \
+      RB_CUDA(cudaMemcpyToSymbol(g_check_word, z, 4 * sizeof(int)));               \
+    }                                                                              \
+    return 0;                                                                      \
+  }
+#else
+#define RB_CHECK_READER(tu)                                                        \
+  RB_EXPORT int rb_check_word_##tu(int* out4, int reset) {                         \
+    (void)reset;                                                                   \
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;                                     \
+    return 0;                                                                      \
+  }
+#endif
+
 __device__ __forceinline__ int64_t rb_page_offset(const RbPagedLayer& c, int slot, int pos, int kvh) {
+#ifdef RB_CHECKED
+  if (slot < 0 || pos < 0 || pos / c.page_size >= c.max_pages || kvh < 0 || kvh >= c.n_kv_heads) {
+    if (atomicCAS(&g_check_word[0], 0, 21) == 0) {
+      g_check_word[1] = slot;
+      g_check_word[2] = pos;
+      g_check_word[3] = kvh;
+    }
+    return 0;
+  }
+#endif
   const int page = c.page_table[(int64_t)slot * c.max_pages + pos / c.page_size];
   return (((int64_t)page * c.n_kv_heads + kvh) * c.page_size + pos % c.page_size) * c.head_dim;
 }

@@ -26,6 +26,13 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
               "-Xcompiler", "-fvisibility=hidden"]
 
 
+def _flags():
+    """The compile flags; RBITNET_CHECKED=1 in the environment adds -DRB_CHECKED (cache addresses are
+    checked before use and a bad one is recorded instead of used), which makes another library."""
+    extra = ["-DRB_CHECKED"] if os.environ.get("RBITNET_CHECKED", "") in ("1", "true", "yes") else []
+    return NVCC_FLAGS + extra
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -47,7 +54,7 @@ def _key() -> str:
     for p in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + _flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -110,7 +117,7 @@ def library_path(verbose: bool = True, ptxas_info: bool = False) -> Path:
     try:
         def compile_one(src: Path):
             obj = work / (src.stem + ".o")
-            log = _run([nvcc, *ARCH_FLAGS, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)],
+            log = _run([nvcc, *ARCH_FLAGS, *_flags(), *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)],
                        src.name)
             if verbose:
                 _log(f"compiled {src.name} ({time.time() - t0:.0f} s)")
@@ -123,12 +130,17 @@ def library_path(verbose: bool = True, ptxas_info: bool = False) -> Path:
         tmp = out_dir / f".{name}.{os.getpid()}.tmp"
         _run([nvcc, *ARCH_FLAGS, "-shared", "-o", str(tmp), *map(str, objs)], "link")
         os.replace(tmp, out_dir / name)
-        for old in out_dir.glob("librbitnet_b200_*.so"):      # builds of earlier sources
-            if old.name != name:
-                try:
-                    old.unlink()
-                except OSError:
-                    pass
+        keep = {name}
+        for old in sorted(out_dir.glob("librbitnet_b200_*.so"), key=lambda p: p.stat().st_mtime, reverse=True):
+            if old.name in keep:
+                continue
+            if len(keep) < 2:          # the newest other build stays: the plain and the checked library live side by side
+                keep.add(old.name)
+                continue
+            try:
+                old.unlink()
+            except OSError:
+                pass
     finally:
         done.set()
         shutil.rmtree(work, ignore_errors=True)

@@ -39,6 +39,10 @@ _SIGNATURES = {
 }
 
 
+#: source files whose kernels address the cache through the checked function (each has its own word)
+CHECKED_FILES = ("elementwise", "gemm_tcgen05", "attention_simple", "attention_tiled")
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -61,6 +65,9 @@ class KernelLibrary:
         self.declare("rb_attention_decode_parts", [I, I, I])
         self.declare("rb_gemm_tc_splits", [I, I, I])
         self.declare("rb_device_sm_count", [])
+        self.declare("rb_is_checked_build", [])
+        for tu in CHECKED_FILES:
+            self.declare(f"rb_check_word_{tu}", [P, I])
 
     def declare(self, name, argtypes, restype=c_int):
         fn = getattr(self._dll, name)
@@ -85,7 +92,9 @@ _LIB: Optional[KernelLibrary] = None
 
 
 def load(verbose: bool = True) -> KernelLibrary:
+    """The library for the current build flags (RBITNET_CHECKED selects the checked build)."""
     global _LIB
-    if _LIB is None:
-        _LIB = KernelLibrary(library_path(verbose=verbose))
+    path = library_path(verbose=verbose)
+    if _LIB is None or _LIB.path != str(path):
+        _LIB = KernelLibrary(path)
     return _LIB

@@ -84,6 +84,14 @@ class CudaOps:
         if v.value:
             raise KernelError(f"a kernel gave up waiting (code {v.value}: 1 = loader, 2 = tensor-core issuer, "
                               "3 = epilogue); its results are not valid")
+        if self.lib.raw("rb_is_checked_build")():
+            from .lib import CHECKED_FILES
+            w = (ctypes.c_int * 4)()
+            for tu in CHECKED_FILES:
+                self.lib.call(f"rb_check_word_{tu}", w, 1, launches=0)
+                if w[0]:
+                    raise KernelError(f"checked build ({tu}): a kernel asked for slot {w[1]}, position {w[2]}, kv head "
+                                      f"{w[3]}, which lies outside the cache (code {w[0]}); the access was not made")
 
     def to_compute(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(device=self.device, dtype=self.dtype).contiguous()

@@ -292,3 +292,64 @@ def test_a_half_precision_folder_is_exact_in_float32_and_harmless_extras_load(tm
     assert_close(out, want, "float32", "F16 folder in float32")
     rounded = plain.forward(TINY_A, {k: v.to(torch.bfloat16) for k, v in tensors.items()}, p, torch.float64)
     assert float((rounded - want).abs().max()) > 20 * float((out.double().cpu() - want).abs().max())
+
+
+# --------------------------------------------------------------------------- the checked build
+_CHECKED_SCRIPT = r'''
+import sys, json, math, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from rbitnet_b200.kernels.ops import CudaOps
+from rbitnet_b200.kernels.lib import KernelError
+from rbitnet_b200.cache import CacheLayerView
+from rbitnet_b200 import Engine
+import plain_llama as plain
+from tiny import prompts
+
+ops = CudaOps(torch.float32)
+assert ops.lib.raw("rb_is_checked_build")() == 1
+# a whole model runs in the checked build and nothing is recorded
+eng = Engine.load_path(sys.argv[2], dtype="float32", max_tokens=512)
+pc, pt = plain.load_folder(sys.argv[2])
+ps = prompts([5, 70], pc["vocab_size"], seed=3)
+res = eng.generate(ps, max_tokens=6, temperature=0.0, stop_ids=[])
+assert [r.tokens for r in res] == [plain.generate_greedy(pc, pt, p, 6) for p in ps]
+ops.check_errors()
+# one token at a position past its slot's row of the page table: 8 pages of 16 positions, position 128.
+# (Entry 8 of slot 0's row is entry 0 of slot 1's row, so even the unchecked address would lie inside
+# the cache; the checked build records it and does not use it.)
+H, Kh, D, page, max_pages, n_slots = 2, 1, 16, 16, 8, 4
+k = torch.zeros(n_slots * max_pages, Kh, page, D, device="cuda")
+v = torch.zeros_like(k)
+table = torch.arange(n_slots * max_pages, dtype=torch.int32, device="cuda").reshape(n_slots, max_pages)
+view = CacheLayerView(k, v, table, max_pages, page, Kh, D, True, 0)
+class M: pass
+m = M()
+m.tok_slot = torch.tensor([0, 0], dtype=torch.int32, device="cuda")
+m.tok_pos = torch.tensor([5, 128], dtype=torch.int32, device="cuda")
+qkv = torch.ones(2, (H + 2 * Kh) * D, device="cuda")
+inv = torch.zeros(D // 2, device="cuda")
+ops.rotate_append(qkv, (inv, False, D), m, view, H)
+torch.cuda.synchronize()
+try:
+    ops.check_errors()
+    print("NOT RECORDED")
+except KernelError as e:
+    print("RECORDED", e)
+ops.check_errors()                       # cleared
+assert float(k[8].abs().sum()) == 0      # slot 1's first page was not touched
+assert float(k[0, 0, 5].abs().sum()) > 0 # the good token was appended
+print("OK")
+'''
+
+
+def test_checked_build_records_a_bad_cache_address_and_does_not_use_it(folders, tmp_path):
+    """The library built with RBITNET_CHECKED=1 (its own shared object, compiled at first use) runs a
+    model like the plain build, and a position outside a sequence's page-table row is recorded with
+    its slot and position instead of being used."""
+    script = tmp_path / "checked.py"
+    script.write_text(_CHECKED_SCRIPT)
+    env = dict(os.environ, RBITNET_CHECKED="1", PYTHONPATH="")
+    p = subprocess.run([sys.executable, str(script), str(ROOT), str(folders["A", "float32"])], capture_output=True,
+                       text=True, env=env, timeout=900)
+    assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
+    assert "RECORDED" in p.stdout and "slot 0, position 128" in p.stdout and p.stdout.strip().endswith("OK"), p.stdout
