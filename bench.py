@@ -274,11 +274,13 @@ class KernelTimer:
     so these are the times of the kernels alone, each starting on an idle GPU: their sum is above the
     step's own time, and a kernel's share of its roofline here is a lower bound of what it reaches
     inside the step."""
+    decode_context = 0     # cached positions per sequence of the decode step being described without a sync
     OPS = ("embed", "rmsnorm", "linear", "gated_linear", "project_rotate_append", "rotate_append", "attention",
            "gather_rows", "sample", "decode_advance")
 
-    def __init__(self, ops):
-        self.ops, self.records, self._depth, self._saved = ops, [], 0, {}
+    def __init__(self, ops, events=True):
+        """events=False: only note, per operation, what it is and how many kernels it launched."""
+        self.ops, self.records, self._depth, self._saved, self.events = ops, [], 0, {}, events
 
     def __enter__(self):
         import torch
@@ -290,14 +292,20 @@ class KernelTimer:
                 if self._depth:                        # an operation made of others is timed as a whole
                     return _fn(*a, **kw)
                 self._depth += 1
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
+                e0 = e1 = None
+                before = self.ops.lib.launches
+                if self.events:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
                 try:
                     out = _fn(*a, **kw)
                 finally:
                     self._depth -= 1
-                e1.record()
-                self.records.append((_name, self._describe(_name, a, kw), e0, e1))
+                if self.events:
+                    e1.record()
+                    self.records.append((_name, self._describe(_name, a, kw), e0, e1))
+                else:
+                    self.records.append((_name, self._describe(_name, a, kw, sync=False), self.ops.lib.launches - before, None))
                 return out
             setattr(self.ops, name, wrapped)
         return self
@@ -307,8 +315,9 @@ class KernelTimer:
             setattr(self.ops, name, fn)
 
     @staticmethod
-    def _describe(name, a, kw):
-        """(label, bytes the operation has to move, flops)."""
+    def _describe(name, a, kw, sync=True):
+        """(label, bytes the operation has to move, flops).  sync=False: nothing is read back from the
+        device (inside a capture); a decode's keys are then counted from the step's longest context."""
         el = lambda t: t.numel() * t.element_size()
         if name in ("linear", "gated_linear", "project_rotate_append"):
             x, w = a[0], a[1]
@@ -326,10 +335,14 @@ class KernelTimer:
         if name == "attention":
             q, meta, view, H = a[0], a[1], a[2], a[3]
             T, _, D = q.shape
-            keys = sum(c.start + c.n_new for c in meta.seqs) if not meta.single_token else None
-            if keys is None:
-                keys = int(meta.tok_pos.sum()) + T
-            flops = 4.0 * H * D * (int(meta.tok_pos.sum()) + T)
+            if not meta.single_token:
+                keys = sum(c.start + c.n_new for c in meta.seqs)
+                seen = sum(c.n_new * c.start + c.n_new * (c.n_new + 1) // 2 for c in meta.seqs)
+            elif sync:
+                keys = seen = int(meta.tok_pos.sum()) + T
+            else:
+                keys = seen = T * KernelTimer.decode_context
+            flops = 4.0 * H * D * seen
             return (f"attention {'decode' if meta.single_token else 'prefill'} [{T} tokens, {H}/{view.n_kv_heads} heads of {D}]",
                     keys * view.n_kv_heads * D * 2 * q.element_size() + 2 * el(q), flops)
         if name in ("rmsnorm", "embed", "gather_rows", "rotate_append"):
@@ -339,15 +352,16 @@ class KernelTimer:
             return f"sample [{a[0].shape[0]} rows of {a[0].shape[1]}]", el(a[0]), 0.0
         return name, 0, 0.0
 
-    def table(self, pk, reps):
-        """Aggregated over equal labels: [{label, calls per step, us per call, GB/s, TFLOP/s, frac}]."""
+    def table(self, pk, reps, times_us=None):
+        """Aggregated over equal labels: [{label, calls per step, us per call, GB/s, TFLOP/s, frac}].
+        ``times_us``: the operations' times if they were not taken with events."""
         import torch
         torch.cuda.synchronize()
         agg = {}
-        for name, (label, nbytes, flops), e0, e1 in self.records:
+        for i, (name, (label, nbytes, flops), e0, e1) in enumerate(self.records):
             d = agg.setdefault(label, {"calls": 0, "us": 0.0, "bytes": nbytes, "flops": flops})
             d["calls"] += 1
-            d["us"] += e0.elapsed_time(e1) * 1e3
+            d["us"] += times_us[i] if times_us is not None else e0.elapsed_time(e1) * 1e3
         rows = []
         for label, d in agg.items():
             us = d["us"] / d["calls"]
@@ -365,29 +379,60 @@ class KernelTimer:
 
 
 def kernel_tables(engine, batch, ctx, prefill_tokens, pk, reps=5):
-    """Per-kernel times, rates and roofline fractions of one decode step and one prefill step, both run
-    kernel by kernel (roofline = max(bytes / copy bandwidth, flops / burst tensor rate), both measured).
-    The step's inputs are on the device before the timed run, and the GPU idles for some milliseconds
-    first, so that the host has queued the whole step by the time its first kernel starts and no
-    event interval holds a wait for the host."""
+    """Per-kernel times, rates and roofline fractions of one decode step and one prefill step
+    (roofline = max(bytes / copy bandwidth, flops / burst tensor rate), both measured).  The decode
+    step's kernels take microseconds, less than a pair of events costs, so they are timed inside the
+    captured step from CUPTI's records; the prefill step's kernels are timed with CUDA events around
+    each operation (its inputs are on the device before the timed run, and the GPU idles for some
+    milliseconds first, so that the host has queued the whole step by the time its first kernel
+    starts and no event interval holds a wait for the host)."""
     import numpy as np
     import torch
     from rbitnet_b200.engine.step import SeqChunk, StepContext, build_meta
     out = {}
-    slots = fill_cache(engine, batch, ctx, reps + 4)
-    g = engine.decode_graph(batch)                       # its buffers and its step body, run without capture
+    # ---- decode: the captured step as it runs.  The operations are noted (what, how many kernels) while
+    # the step is captured; CUPTI's records of one replay then give, per kernel, how long after the end
+    # of the kernel before it it ended: that is what it adds to the step, overlap included.
+    from torch.profiler import profile, ProfilerActivity
+    slots = fill_cache(engine, batch, ctx, 64)
+    engine._graphs.pop(batch, None)
+    g = engine.decode_graph(batch)
     g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
-    for _ in range(2):
-        g._body()
-        g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
+    KernelTimer.decode_context = ctx
+    g._body()                                           # the trial run, so that the capture below is the only noted run
     torch.cuda.synchronize()
-    with KernelTimer(engine.ops) as kt:
-        for _ in range(reps):
-            torch.cuda._sleep(40_000_000)
-            g._body()
-            g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
-        rows, total = kt.table(pk, reps)
-    out["decode"] = {"batch": batch, "context": ctx, "sum_of_kernels_us": round(total, 1), "kernels": rows}
+    g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
+    with KernelTimer(engine.ops, events=False) as kt:
+        noted = []
+        g.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g.graph, pool=engine._graph_pool):
+            g.sampled = g._body()
+        noted = list(kt.records)
+        g.stage(slots, [1] * batch, [ctx] * batch, [0.0] * batch, [0.5] * batch)
+        for _ in range(5):
+            g.graph.replay()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                g.graph.replay()
+            torch.cuda.synchronize()
+        ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                    key=lambda e: e.time_range.start)
+        n_kernels = sum(r[2] for r in noted)
+        last = ev[-n_kernels:] if len(ev) >= 3 * n_kernels else []
+        times, prev_end, i = [], (last[0].time_range.start if last else 0.0), 0
+        for _, _, n, _ in noted:
+            t = 0.0
+            for e in last[i:i + n]:
+                t += max(0.0, e.time_range.end - prev_end)
+                prev_end = max(prev_end, e.time_range.end)
+            i += n
+            times.append(t)
+        kt.records = noted
+        rows, total = kt.table(pk, 1, times_us=times) if last else ([], 0.0)
+    engine._graphs.pop(batch, None)                     # captured by hand here: not for the engine to use
+    out["decode"] = {"batch": batch, "context": ctx, "step_us": round(total, 1), "kernels_per_step": n_kernels,
+                     "how": "captured step, time each kernel adds after the one before it ended", "kernels": rows}
     for s in slots:
         engine.end_sequence(s)
     ids = torch.randint(0, engine.config.vocab_size, (prefill_tokens,), generator=torch.Generator().manual_seed(1))
@@ -404,7 +449,8 @@ def kernel_tables(engine, batch, ctx, prefill_tokens, pk, reps=5):
         engine.model.forward(ctx_)
         rows, total = kt.table(pk, 1)
     engine.end_sequence(s)
-    out["prefill"] = {"tokens": prefill_tokens, "sum_of_kernels_us": round(total, 1), "kernels": rows}
+    out["prefill"] = {"tokens": prefill_tokens, "sum_of_kernels_us": round(total, 1),
+                      "how": "kernel by kernel, CUDA events around each operation", "kernels": rows}
     return out
 
 
@@ -477,7 +523,7 @@ def main():
         print(json.dumps({"kernels_of": shape_name, "layers": layers, "peaks": pk, **tables}))
         for phase in ("decode", "prefill"):
             t = tables[phase]
-            print(f"\n{phase}: sum of kernels {t['sum_of_kernels_us']:.1f} us", file=sys.stderr)
+            print(f"\n{phase} ({t['how']}): {t.get('step_us', t.get('sum_of_kernels_us')):.1f} us", file=sys.stderr)
             print(f"{'us':>9} {'calls':>6} {'share':>6} {'GB/s':>8} {'TFLOP/s':>8} {'bound':>6} {'frac':>6}  kernel", file=sys.stderr)
             for r in t["kernels"]:
                 print(f"{r['us']:9.1f} {r['calls_per_step']:6.1f} {r['share_of_step']:6.3f} {r['gb_s']:8.1f} "
