@@ -30,6 +30,7 @@ def _flags():
     """The compile flags; RBITNET_CHECKED=1 in the environment adds -DRB_CHECKED (cache addresses are
     checked before use and a bad one is recorded instead of used), which makes another library."""
     extra = ["-DRB_CHECKED"] if os.environ.get("RBITNET_CHECKED", "") in ("1", "true", "yes") else []
+    extra += os.environ.get("RBITNET_NVCC_EXTRA", "").split()       # further flags, for experiments
     return NVCC_FLAGS + extra
 
 
