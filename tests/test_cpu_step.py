@@ -114,3 +114,32 @@ def test_engine_from_env(tmp_path, monkeypatch):
     a = Engine.from_env(ops=TorchOps(torch.float32), dtype="float32", max_tokens=256)
     res = a.generate([[1, 2, 3]], max_tokens=3, temperature=0.0)
     assert len(res[0].tokens) == 3 and res[0].finish_reason == "length"
+
+
+def test_command_line_generate_on_the_stand_in(tmp_path, capsys):
+    """The generate verb's own logic (prompts from arguments and from a file, stop ids, temperature,
+    printed records) with the torch stand-in for the kernels; greedy ids equal the plain model's, and a
+    temperature run repeats for the same seed."""
+    import json
+    import plain_llama as plain
+    from rbitnet_b200.cli import main
+    folder = make_model_dir(tmp_path / "m", TINY_A, 0)
+    pc, pt = plain.load_folder(folder)
+    prompts_file = tmp_path / "p.txt"
+    prompts_file.write_text("9 8 7 6\n\n1, 2\n")
+    common = ["generate", "--model", str(folder), "--dtype", "float32", "--cache-tokens", "256", "--max-tokens", "5"]
+    assert main(common + ["--temperature", "0", "--stop-id", "3", "--prompt-ids", "5 17 3", "--prompt-ids", str(prompts_file)],
+                ops=TorchOps(torch.float32)) == 0
+    recs = [json.loads(x) for x in capsys.readouterr().out.strip().splitlines()]
+    assert [r["prompt_tokens"] for r in recs] == [3, 4, 2]
+    for p, r in zip([[5, 17, 3], [9, 8, 7, 6], [1, 2]], recs):
+        assert r["tokens"] == plain.generate_greedy(pc, pt, p, 5, [3])
+        assert r["finish_reason"] == ("length" if len(r["tokens"]) == 5 else "stop")
+    outs = []
+    for seed in ("4", "4", "5"):
+        assert main(common + ["--temperature", "1.5", "--sample-seed", seed, "--prompt-ids", "5 17 3"],
+                    ops=TorchOps(torch.float32)) == 0
+        outs.append(capsys.readouterr().out)
+    assert outs[0] == outs[1] and outs[0] != outs[2]
+    with pytest.raises(SystemExit, match="nothing to generate"):
+        main(common, ops=TorchOps(torch.float32))
