@@ -481,14 +481,17 @@ RB_EXPORT int rb_gather_rows(float* out, const float* x, const int* rows, int R,
 
 // ---------------------------------------------------------------- decode bookkeeping on the device
 // After a decode step has sampled: the sampled ids become the next step's tokens and every
-// position moves on by one, so that steps can follow one another without the host.
+// position moves on by one, so that steps can follow one another without the host.  Only the first
+// *n_live rows move (n_live null: all B): rows behind them belong to the padding sequence, which
+// rewrites its position 0 at every step.
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ tok_pos,
-                                      const int* __restrict__ sampled, int B, const int* flag_a,
-                                      const int* flag_b, int* __restrict__ flag_out) {
+                                      const int* __restrict__ sampled, int B, const int* __restrict__ n_live,
+                                      const int* flag_a, const int* flag_b, int* __restrict__ flag_out) {
   rb_pdl_launch_dependents();
   rb_pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < B) {
+  const int live = n_live != nullptr ? *n_live : B;
+  if (i < B && i < live) {
     token_ids[i] = sampled[i];
     tok_pos[i] += 1;
   }
@@ -499,11 +502,11 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restri
   }
 }
 
-RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled, int B, const int* flag_a,
-                                const int* flag_b, int* flag_out, cudaStream_t stream) {
+RB_EXPORT int rb_decode_advance(int* token_ids, int* tok_pos, const int* sampled, int B, const int* n_live,
+                                const int* flag_a, const int* flag_b, int* flag_out, cudaStream_t stream) {
   if (B == 0) return 0;
   RB_LAUNCH("decode_advance_kernel", (decode_advance_kernel), (B + 127) / 128, 128, 0, stream, token_ids, tok_pos, sampled, B,
-            flag_a, flag_b, flag_out);
+            n_live, flag_a, flag_b, flag_out);
   RB_CHECK_LAUNCH("rb_decode_advance");
   return 0;
 }

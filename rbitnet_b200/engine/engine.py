@@ -92,6 +92,7 @@ class Engine:
         self._tokenizer = None
         self._graphs = {}
         self._graph_pool = None
+        self._last_slots, self._last_graph = [], None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -199,37 +200,58 @@ class Engine:
         """Batch sizes that get a captured step of their own: 1, 2, 4, then multiples of 8."""
         return n if n <= 2 else (4 if n <= 4 else -(-n // 8) * 8)
 
-    def _decode_step(self, feed, temperatures, uniforms) -> List[int]:
-        slots = [s for s, _ in feed]
+    def _decode_launch(self, feed, temperatures, uniforms):
+        """Launches one captured decode step and returns a ticket for ``_decode_fetch``.  ``feed``:
+        (slot, [token]) pairs with the tokens from the host; or None: the same sequences as the launch
+        before, whose tokens and positions that step left on the device (only the uniform numbers are
+        copied), which is how a step is launched before the ids of the step before it have been read.
+        The sequences' lengths move on at once."""
+        if feed is not None:
+            slots = [s for s, _ in feed]
+            tokens = [t[0] for _, t in feed]
+        else:
+            slots = self._last_slots
+        n = len(slots)
         positions = self.cache.lengths(slots)
         self.cache.reserve_one_each(slots)
-        n = len(feed)
-        tokens = [t[0] for _, t in feed]
         temperatures, uniforms = list(temperatures), list(uniforms)
         batch = self._graph_batch(n)
-        run_slots = list(slots)
-        if batch > n:
-            # rows of the padding sequence: they rewrite its position 0 and their results are dropped
-            extra = batch - n
-            run_slots += [self._pad_slot] * extra
-            tokens += [0] * extra
-            positions = positions + [0] * extra
+        extra = batch - n
+        if extra:
             temperatures += [0.0] * extra
             uniforms += [0.0] * extra
         self.cache.upload_tables()
         g = self.decode_graph(batch)
-        g.stage(run_slots, tokens, positions, temperatures, uniforms)
-        if g.graph is None:
-            g.capture(pool=self._graph_pool)
-            if self._graph_pool is None:
-                self._graph_pool = g.graph.pool()
-        g.replay()
-        ids = g.read()[:n]
+        if feed is not None or g.graph is None:
+            if feed is None:
+                raise RuntimeError("a decode step without tokens needs the captured step of the launch before it")
+            # rows of the padding sequence fill the step up: they rewrite its position 0 and their results are dropped
+            g.stage(slots + [self._pad_slot] * extra, tokens + [0] * extra, positions + [0] * extra,
+                    temperatures, uniforms, n_live=n)
+            if g.graph is None:
+                g.capture(pool=self._graph_pool)
+                if self._graph_pool is None:
+                    self._graph_pool = g.graph.pool()
+        else:
+            g.stage_uniforms(uniforms)
+        ticket = g.launch()
+        self.cache.advance_one_each(slots)
+        self._last_slots, self._last_graph = slots, g
+        return (g, ticket, n)
+
+    def _decode_fetch(self, ticket) -> List[int]:
+        g, t, n = ticket
+        ids = g.fetch(t)[:n]
         if g.error_code:
             self.ops.check_errors()            # raises with the code, and clears the word
-        self.cache.advance_one_each(slots)
-        self._last_graph = g
         return ids
+
+    def _decode_step(self, feed, temperatures, uniforms) -> List[int]:
+        return self._decode_fetch(self._decode_launch(feed, temperatures, uniforms))
+
+    # the generation loop's names for the two halves of a decode step
+    decode_launch = _decode_launch
+    decode_fetch = _decode_fetch
 
     def _step_sample(self, feed, temperatures, uniforms) -> List[int]:
         if self.use_graphs and all(len(t) == 1 for _, t in feed):
@@ -249,7 +271,8 @@ class Engine:
         """Token-id prompts in, generated ids out, one result per prompt in order.
         temperature <= 0 is greedy.  Defaults are the reference server's
         (crates/bitnet-server/src/lib.rs:317, :358)."""
-        loop = GenerationLoop(self._step_sample, self.cache, max_batch or self.max_batch)
+        loop = GenerationLoop(self._step_sample, self.cache, max_batch or self.max_batch,
+                              decoder=self if self.use_graphs else None)
         out = loop.run(prompts, max_tokens, temperature, seed,
                        self.stop_ids if stop_ids is None else stop_ids)
         self.last_stats = {"steps": loop.steps, "prefill_tokens": loop.prefill_tokens,

@@ -27,7 +27,7 @@ _SIGNATURES = {
     "rb_gemm_tc": [P, L, I, P, L, I, P, L, I, I, I, I, I, I, I, F, P],
     "rb_gemm_tc_qkv": [P, P, L, I, P, L, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "rb_read_error_flag": [P, I],
-    "rb_decode_advance": [P, P, P, I, P, P, P, P],
+    "rb_decode_advance": [P, P, P, I, P, P, P, P, P],
     "rb_error_flag_addresses": [P, P],
     "rb_attention_prefill": [P, P, P, P, P, I, I, P, P, P, P, I, I, I, I, F, I, P],
     "rb_attention_decode": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, P, P, I, P],

@@ -337,8 +337,9 @@ class CudaOps:
         return out
 
     def decode_advance(self, token_ids: torch.Tensor, tok_pos: torch.Tensor, sampled: torch.Tensor,
-                       flag_out: Optional[torch.Tensor] = None) -> None:
-        """token_ids <- sampled; tok_pos += 1 (the next decode step's inputs, made on the device).
+                       flag_out: Optional[torch.Tensor] = None, n_live: Optional[torch.Tensor] = None) -> None:
+        """token_ids <- sampled; tok_pos += 1 (the next decode step's inputs, made on the device), for the
+        first ``n_live[0]`` rows (a device int32; all rows if None).
         With ``flag_out`` (one int32) the kernels' error word is written there too, so that it comes
         back with the step's results (0: no bounded wait ran out)."""
         if self._flag_ptrs is None:
@@ -348,4 +349,4 @@ class CudaOps:
             self._flag_ptrs = (a, b)
         a, b = self._flag_ptrs if flag_out is not None else (c_void_p(0), c_void_p(0))
         self.lib.call("rb_decode_advance", _ptr(token_ids), _ptr(tok_pos), _ptr(sampled), token_ids.shape[0],
-                      a, b, _ptr(flag_out), self._stream())
+                      _ptr(n_live), a, b, _ptr(flag_out), self._stream())

@@ -302,3 +302,97 @@ def test_pages_behind_a_window_are_given_back_and_never_a_visible_one():
         book.advance(s, 1)
     assert most <= book.pages_needed(0, 100, 400) == 7                        # the prompt's 7 pages, then 3 at most
     assert sum(p >= 0 for p in book.pages[s][0]) <= (20 - 1) // 16 + 2
+
+
+class _FakeDevice:
+    """Stands in for an engine whose decode steps leave the next step's tokens on the device: the loop's
+    ``step_sample`` (prompts), ``decode_launch`` and ``decode_fetch``.  Every sequence emits its request's
+    scripted tokens in order; a launch without tokens feeds what the launch before it sampled, as the
+    captured step does."""
+
+    def __init__(self, cache, script):
+        self.cache, self.script = cache, script
+        self.slot_req, self.count = {}, {}
+        self.launches = []            # (slots, tokens fed, had explicit tokens)
+        self.results = []
+        self.fetched = 0
+
+    def _emit(self, slot):
+        r = self.slot_req[slot]
+        toks = self.script[r][1]
+        i = self.count[r]
+        self.count[r] += 1
+        return toks[i] if i < len(toks) else -7      # past its script: a sequence that has ended; dropped by the loop
+
+    def step_sample(self, feed, temps, us):
+        out = []
+        for s, toks in feed:
+            assert self.cache.len[s] == 0, "only prompts go through step_sample here"
+            self.slot_req[s] = next(r for r, (p, _) in enumerate(self.script) if list(p) == list(toks))
+            self.count[self.slot_req[s]] = 0
+            self.cache.len[s] += len(toks)
+            out.append(self._emit(s))
+        return out
+
+    def decode_launch(self, feed, temps, us):
+        assert len(self.results) - self.fetched <= 1, "at most two launches are outstanding"
+        if feed is not None:
+            slots, tokens = [s for s, _ in feed], [t[0] for _, t in feed]
+        else:
+            slots, tokens = self.launches[-1][0], self.results[-1]
+        assert len(temps) == len(us) == len(slots)
+        for s in slots:
+            if s in self.cache.len:                  # (a slot given back meanwhile is only written to, never read)
+                self.cache.len[s] += 1
+                assert self.cache.len[s] <= self.cache.max_seq
+        self.launches.append((list(slots), list(tokens), feed is not None))
+        self.results.append([self._emit(s) for s in slots])
+        return len(self.results) - 1
+
+    def decode_fetch(self, ticket):
+        assert ticket >= len(self.results) - 2
+        self.fetched = max(self.fetched, ticket + 1)
+        return self.results[ticket]
+
+
+@pytest.mark.parametrize("case", range(5))
+def test_loop_that_launches_ahead_gives_the_same_results(case):
+    """With a decoder the loop launches step k+1 before it reads step k; whatever the scripts (stops at
+    any step, several at once, lengths, a full slot), the results are those of the step-by-step loop,
+    every token a sequence is fed is the one it sampled before, and no launch follows a known end."""
+    scripts = [
+        [([1, 2, 3], [10, 11, 99, 12]), ([4], [20, 21, 22, 23, 24, 25, 26]), ([5, 6], [99]),
+         ([7, 8, 9, 9], [30, 31, 32, 33, 34, 35, 36])],
+        [([1], [5, 5, 5, 99]), ([2], [6, 6, 6, 99]), ([3], [7, 7, 7, 7, 7, 7, 7])],
+        [([1, 1], [8] * 9), ([2, 2, 2], [9] * 9)],
+        [([1] * 5, [3, 99]), ([2] * 4, [4, 4, 99]), ([3] * 3, [5, 5, 5, 99]), ([4] * 2, [6] * 8)],
+        [([1, 2, 3, 4], [5, 6, 7, 8, 9]), ([9], [1, 2, 99])],
+    ]
+    script = scripts[case]
+    max_tokens, max_seq = (6, 100) if case != 4 else (10, 6)
+    prompts = [p for p, _ in script]
+    seen = {True: [], False: []}
+    outs = {}
+    for ahead in (False, True):
+        cache = _FakeCache(n_slots=3, max_seq=max_seq)
+        dev = _FakeDevice(cache, script)
+        loop = GenerationLoop(dev.step_sample if ahead else _script(cache, script)[0], cache, 3,
+                              decoder=dev if ahead else None)
+        outs[ahead] = loop.run(prompts, max_tokens=max_tokens, stop_ids=[99],
+                               on_token=lambda r, t, a=ahead: seen[a].append((r, t)))
+        assert cache.len == {} and sorted(cache.free_slots) == [0, 1, 2]
+        if ahead:
+            assert any(not explicit for _, _, explicit in dev.launches) or case == 4 or max(len(t) for _, t in script) < 3
+            for (slots, tokens, explicit), prev in zip(dev.launches[1:], dev.launches[:-1]):
+                if not explicit:
+                    assert slots == prev[0]                       # the same sequences, their tokens from the device
+            # every explicitly fed token is the last one its sequence emitted
+            for slots, tokens, explicit in dev.launches:
+                if explicit:
+                    for s_, t_ in zip(slots, tokens):
+                        assert t_ != 99 and t_ != -7
+    got = [(r.tokens, r.finish_reason, r.prompt_tokens) for r in outs[True]]
+    assert got == [(r.tokens, r.finish_reason, r.prompt_tokens) for r in outs[False]]
+    assert sorted(seen[True]) == sorted(seen[False])
+    for r in range(len(script)):                                  # per request the tokens come in order
+        assert [t for q, t in seen[True] if q == r] == outs[True][r].tokens
