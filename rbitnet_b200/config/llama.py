@@ -13,7 +13,7 @@ the engine's ``max_seq`` option instead.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import ClassVar, List, Optional, Union
 
 from .base import ModelConfig, ConfigError
