@@ -143,3 +143,55 @@ def test_command_line_generate_on_the_stand_in(tmp_path, capsys):
     assert outs[0] == outs[1] and outs[0] != outs[2]
     with pytest.raises(SystemExit, match="nothing to generate"):
         main(common, ops=TorchOps(torch.float32))
+
+
+@pytest.mark.parametrize("window", [None, 20])
+def test_random_schedules_give_the_logits_of_whole_sequences(tmp_path, window):
+    """Forty random ways of cutting and batching the same kind of work (requests of random lengths, each cut
+    into steps of random sizes, run beside whatever else is live, in a cache so small that slots and
+    pages are used again and, with a window, given back while a sequence still runs): the logits at
+    every position are those of the whole sequence alone."""
+    import random
+    from rbitnet_b200 import StepEntry
+    cfg = dict(TINY_A, sliding_window=window) if window else TINY_A
+    folder = make_model_dir(tmp_path / "m", cfg, 3)
+    ref = PlainModel(folder)
+    from rbitnet_b200 import Engine
+    eng = Engine.load_path(folder, dtype="float32", ops=TorchOps(torch.float32), max_tokens=256, page_size=16,
+                           max_batch_tokens=37)
+    rnd = random.Random(11)
+    V, top = cfg["vocab_size"], cfg["max_position_embeddings"]
+    for trial in range(40):
+        n_req = rnd.randint(1, 4)
+        reqs = [[rnd.randrange(V) for _ in range(rnd.choice([1, 2, 15, 16, 17, 33, 60]))] for _ in range(n_req)]
+        reqs = [r[:min(len(r), 256 // n_req // 16 * 16, top)] for r in reqs]
+        slots = [eng.new_sequence() for _ in reqs]
+        done = [0] * n_req
+        got = [[] for _ in reqs]
+        while any(d < len(r) for d, r in zip(done, reqs)):
+            entries, who = [], []
+            for i, r in enumerate(reqs):
+                if done[i] < len(r) and (rnd.random() < 0.7 or not entries):
+                    n = min(len(r) - done[i], rnd.choice([1, 1, 2, 5, 16, 40]))
+                    want = sorted(rnd.sample(range(n), rnd.randint(0, n)))
+                    entries.append(StepEntry(slots[i], r[done[i]:done[i] + n], want))
+                    who.append((i, done[i], want))
+                    done[i] += n
+            out = eng.step(entries)
+            off = 0
+            for i, base, want in who:
+                for w in want:
+                    got[i].append((base + w, out[off]))
+                    off += 1
+            assert (out is None and off == 0) or off == out.shape[0]
+            for i in range(n_req):            # a finished request leaves at once; its slot and pages go to the next trial
+                if done[i] == len(reqs[i]) and slots[i] is not None:
+                    eng.end_sequence(slots[i])
+                    slots[i] = None
+        for i, r in enumerate(reqs):
+            if got[i]:
+                places = [p for p, _ in got[i]]
+                assert_close(torch.stack([row for _, row in got[i]]), ref.logits(r)[places], "float32",
+                             f"trial {trial} request {i}")
+        assert eng.live_sequences() == []
+    assert all(pool.n_free == pool.n for pool in eng.cache.book.pools)

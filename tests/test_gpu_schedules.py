@@ -352,3 +352,49 @@ def test_checked_build_records_a_bad_cache_address_and_does_not_use_it(folders, 
                        text=True, env=env, timeout=900)
     assert p.returncode == 0, p.stdout[-1500:] + p.stderr[-3000:]
     assert "RECORDED" in p.stdout and "slot 0, position 128" in p.stdout and p.stdout.strip().endswith("OK"), p.stdout
+
+
+# --------------------------------------------------------------------------- random ways of cutting the work
+@pytest.mark.parametrize("name,dtype", _cases(("B", "W")))
+def test_random_schedules_give_the_logits_of_whole_sequences(folders, name, dtype):
+    """Random requests cut into steps of random sizes, run beside whatever else is live, some steps through
+    the captured decode step, in a cache small enough that slots and pages are used again (and, in the
+    windowed model, given back while a sequence still runs): every logit is that of its whole sequence."""
+    import random
+    from rbitnet_b200 import Engine, StepEntry
+    eng = Engine.load_path(folders[name, dtype], dtype=dtype, max_tokens=4 * 256, max_batch_tokens=150)
+    ref = PlainModel(folders[name, dtype])
+    rnd = random.Random(23)
+    V, top = eng.config.vocab_size, min(eng.config.max_position_embeddings, 256)
+    for trial in range(12):
+        n_req = rnd.randint(1, 4)
+        reqs = [[rnd.randrange(V) for _ in range(min(top, rnd.choice([1, 2, 63, 64, 65, 130, 200])))] for _ in range(n_req)]
+        slots = [eng.new_sequence() for _ in reqs]
+        done = [0] * n_req
+        got = [[] for _ in reqs]
+        while any(d < len(r) for d, r in zip(done, reqs)):
+            entries, who = [], []
+            single = rnd.random() < 0.5
+            for i, r in enumerate(reqs):
+                if done[i] < len(r) and (rnd.random() < 0.7 or not entries):
+                    n = 1 if single else min(len(r) - done[i], rnd.choice([1, 2, 7, 64, 100]))
+                    want = sorted(rnd.sample(range(n), rnd.randint(0 if not single else 1, n)))
+                    entries.append(StepEntry(slots[i], r[done[i]:done[i] + n], want))
+                    who.append((i, done[i], want))
+                    done[i] += n
+            out = eng.step(entries, captured=single and rnd.random() < 0.7)
+            off = 0
+            for i, base, want in who:
+                for w in want:
+                    got[i].append((base + w, out[off].clone()))
+                    off += 1
+            for i in range(n_req):
+                if done[i] == len(reqs[i]) and slots[i] is not None:
+                    eng.end_sequence(slots[i])
+                    slots[i] = None
+        for i, r in enumerate(reqs):
+            if got[i]:
+                places = [p for p, _ in got[i]]
+                assert_close(torch.stack([row for _, row in got[i]]), ref.logits(r)[places], dtype,
+                             f"{name} trial {trial} request {i}")
+        assert eng.live_sequences() == []
