@@ -590,6 +590,9 @@ int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmPar
     case 32: return launch<32, 5, EPI, OutT, 2>(tw, tx, p, stream);
     case 64: return launch<64, 4, EPI, OutT, 2>(tw, tx, p, stream);
     case 128: return launch<128, 6, EPI, OutT, 1>(tw, tx, p, stream);
+    case 160: return launch<160, 5, EPI, OutT, 1>(tw, tx, p, stream);
+    case 192: return launch<192, 5, EPI, OutT, 1>(tw, tx, p, stream);
+    case 224: return launch<224, 4, EPI, OutT, 1>(tw, tx, p, stream);
     case 256: return launch<256, 4, EPI, OutT, 1>(tw, tx, p, stream);
   }
   RB_FAIL("rb_gemm_tc: no kernel for a token tile of %d", bn);
@@ -683,16 +686,22 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   int bn = token_tile;
   if (bn == 0) {
     bn = n_tokens <= 16 ? 16 : n_tokens <= 32 ? 32 : n_tokens <= 64 ? 64 : n_tokens <= 128 ? 128 : 256;
-    if (n_tokens > 128 && n_tokens <= 1024) {
-      // Few enough tokens that tiles of 256 may leave most SMs without an item: take tiles of 128
-      // where that needs clearly less time, counted as rounds of the SMs times what an item costs.
-      // An item of 128 tokens costs about 0.7 of one of 256, not half (measured: with half, a
-      // 1,024-token prefill took 16.7 ms instead of 13.9 because the gate/up product moved to 128).
-      // Longer prompts run at the power limit whatever the tile; they keep 256.
+    if (n_tokens > 128 && n_tokens <= 4096) {
+      // Few enough tokens that tiles of 256 may leave most SMs without an item, or with a last round
+      // of few: take the tile (128 to 256 tokens in steps of 32) that needs the least time, counted as
+      // rounds of the SMs times what an item costs.  An item of 128 tokens costs about 0.7 of one
+      // of 256, not half (measured: with half, a 1,024-token prefill took 16.7 ms instead of 13.9
+      // because the gate/up product moved to 128); between them the cost is taken as linear.  Measured
+      // against tiles of 128 and 256 alone: 300 tokens 7.6 ms instead of 8.2, 768 tokens 10.5 instead
+      // of 11.35, 1,200 tokens 16.7 instead of 18.2, 1,500 tokens 19.2 instead of 20.4; 2,048 and 4,096
+      // tokens take 256 as before.  Beyond 4,096 tokens the rounds are many and 256 stays.
       const long long w_tiles = (n_out + BM - 1) / BM, sms = rb_sm_count();
-      const long long rounds128 = (w_tiles * ((n_tokens + 127) / 128) + sms - 1) / sms;
-      const long long rounds256 = (w_tiles * ((n_tokens + 255) / 256) + sms - 1) / sms;
-      bn = 7 * rounds128 < 10 * rounds256 ? 128 : 256;
+      double best = 0.0;
+      for (int cand = 128; cand <= 256; cand += 32) {
+        const long long rounds = (w_tiles * ((n_tokens + cand - 1) / cand) + sms - 1) / sms;
+        const double cost = (double)rounds * (0.4 + 0.6 * cand / 256.0);
+        if (cand == 128 || cost < best - 1e-9) { best = cost; bn = cand; }
+      }
     }
   }
   RB_REQUIRE(epilogue != EPI_GATED || (n_out % 32 == 0 && n_features > 0 && n_features <= n_out / 2),
