@@ -141,3 +141,25 @@ def test_schedule_with_a_repeated_layer_and_a_shared_cache_changes_the_result():
     b = plain.forward(TINY_A, t, p, schedule=[(0, None), (1, None), (0, None)])
     c = plain.forward(TINY_A, t, p, schedule=[(0, None), (1, 0)])
     assert not torch.allclose(a, b) and not torch.allclose(a, c)
+
+
+def test_plain_implementation_and_weight_generator_against_committed_numbers():
+    """tests/golden/plain_tiny.json was written by tests/golden/make_golden.py: the oracle's logits for a
+    fixed prompt on the seeded random weights of both tiny configurations.  (No output of the
+    reference's own code exists to compare with: it cannot be compiled here.)"""
+    import importlib.util
+    import json
+    from pathlib import Path
+    here = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_golden", here / "make_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    want = json.loads((here / "plain_tiny.json").read_text())
+    got = mod.golden()
+    for name in ("A", "B"):
+        assert got[name]["prompt"] == want[name]["prompt"]
+        assert got[name]["first_weights"] == want[name]["first_weights"]              # bit for bit
+        assert got[name]["argmax_per_row"] == want[name]["argmax_per_row"]
+        for a, b in zip(got[name]["last_row_first_8"], want[name]["last_row_first_8"]):
+            assert abs(a - b) <= 1e-9 * max(1.0, abs(b))          # float64 sums may be ordered otherwise on another CPU
+        assert abs(got[name]["sum_abs"] - want[name]["sum_abs"]) <= 1e-9 * want[name]["sum_abs"]
