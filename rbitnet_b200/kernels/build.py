@@ -93,6 +93,10 @@ def library_path(verbose: bool = True, ptxas_info: bool = False) -> Path:
     name = f"librbitnet_b200_{key}.so"
     for d in _build_dirs():
         if (d / name).is_file():
+            try:
+                os.utime(d / name)             # in use: the clean-up below removes the builds not used longest
+            except OSError:
+                pass
             return d / name
     out_dir = next((d for d in _build_dirs() if _writable(d)), None)
     if out_dir is None:
@@ -135,7 +139,7 @@ def library_path(verbose: bool = True, ptxas_info: bool = False) -> Path:
         for old in sorted(out_dir.glob("librbitnet_b200_*.so"), key=lambda p: p.stat().st_mtime, reverse=True):
             if old.name in keep:
                 continue
-            if len(keep) < 2:          # the newest other build stays: the plain and the checked library live side by side
+            if len(keep) < 3:          # the builds used last stay: the plain and the checked library live side by side
                 keep.add(old.name)
                 continue
             try:
