@@ -267,14 +267,15 @@ class Engine:
     # ------------------------------------------------------------------ generation
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.7,
                  seed: int = 0, stop_ids: Optional[Sequence[int]] = None,
-                 max_batch: Optional[int] = None) -> List[GenerationResult]:
+                 max_batch: Optional[int] = None, on_token=None) -> List[GenerationResult]:
         """Token-id prompts in, generated ids out, one result per prompt in order.
         temperature <= 0 is greedy.  Defaults are the reference server's
-        (crates/bitnet-server/src/lib.rs:317, :358)."""
+        (crates/bitnet-server/src/lib.rs:317, :358).  ``on_token(request index, token id)`` is
+        called for every emitted token as soon as the host has it."""
         loop = GenerationLoop(self._step_sample, self.cache, max_batch or self.max_batch,
                               decoder=self if self.use_graphs else None)
         out = loop.run(prompts, max_tokens, temperature, seed,
-                       self.stop_ids if stop_ids is None else stop_ids)
+                       self.stop_ids if stop_ids is None else stop_ids, on_token=on_token)
         self.last_stats = {"steps": loop.steps, "prefill_tokens": loop.prefill_tokens,
                            "decode_tokens": loop.decode_tokens}
         return out
