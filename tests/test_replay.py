@@ -128,3 +128,44 @@ def test_trace_run_program(tmp_path, name, dtype):
             got, _ = collect_by_manifest(out)
         for r, t in reqs.items():
             assert_close(got[r], ref.logits(t), dtype, f"{mode} {r}")
+
+
+def test_request_files_and_schedules(tmp_path):
+    """Both request file formats, and the schedules the program makes from them."""
+    from rbitnet_b200.replay import read_requests, schedule_whole, schedule_tail32, schedule_batches
+    reqs = {"a": [1, 2, 3], "b": list(range(40)), "c": [7]}
+    (tmp_path / "lines.jsonl").write_text("\n".join(json.dumps({"id": k, "tokens": v}) for k, v in reqs.items()) + "\n\n")
+    (tmp_path / "object.json").write_text(json.dumps(reqs))
+    (tmp_path / "empty.jsonl").write_text("")
+    assert read_requests(tmp_path / "lines.jsonl") == reqs and read_requests(tmp_path / "object.json") == reqs
+    assert read_requests(tmp_path / "empty.jsonl") == {}
+
+    def fed(steps):          # request -> tokens in the order they are fed; ends exactly once, after the last token
+        out, ended = {}, []
+        for i, st in enumerate(steps):
+            assert st["step"] == i
+            for e in st["entries"]:
+                assert e["id"] not in ended and e["want"] == list(range(len(e["tokens"])))
+                out.setdefault(e["id"], []).extend(e["tokens"])
+            ended += st["end"]
+        assert sorted(ended) == sorted(reqs)
+        return out
+
+    assert fed(schedule_whole(reqs)) == reqs
+    tail = schedule_tail32(reqs)
+    assert fed(tail) == reqs
+    assert [len(e["tokens"]) for st in tail for e in st["entries"] if e["id"] == "b"] == [8] + [1] * 32
+    for size in (1, 2, 3):
+        steps = schedule_batches(reqs, size)
+        assert fed(steps) == reqs
+        first = steps[0]["entries"]
+        assert len(first) == min(size, 3) and all(len(e["tokens"]) >= 1 for e in first)
+        # after a batch's first step every entry brings one token, and no request joins a running batch
+        batch_ids = {e["id"] for e in first}
+        for st in steps[1:]:
+            ids = {e["id"] for e in st["entries"]}
+            if ids <= batch_ids:
+                assert all(len(e["tokens"]) == 1 for e in st["entries"])
+            else:
+                assert not (ids & batch_ids)
+                batch_ids = ids
