@@ -163,6 +163,31 @@ def time_decode_e2e(engine, batch, context, steps, warmup):
     return dt / steps * 1e3, g.h2d_bytes, g.d2h_bytes
 
 
+def time_generate(engine, batch, context, steps, warmup):
+    """Decode through ``Engine.generate`` itself: ``batch`` prompts of ``context`` host token ids in, every
+    generated id out through ``on_token``; the time between the first token after ``warmup + 64`` steps
+    and the last one, by the host's clock.  The 64 further steps are left out because the steps of the
+    first 0.1 s after a prompt of this size run up to 18 % slower, at the clocks the power limit left
+    after the prefill (the same captured step, replayed after a second's pause, is as fast as on a cache
+    that no prefill filled).  generate launches a decode step before it has read the ids of the step
+    before, so this is not the plain step of ``e2e``; it is reported beside it."""
+    import torch
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, engine.config.vocab_size, (context,), generator=g).tolist() for _ in range(batch)]
+    stamps = []
+
+    def on_token(request, token):
+        if request == 0:
+            stamps.append(time.perf_counter())
+
+    skip = warmup + 64
+    engine.generate(prompts, max_tokens=skip + steps + 1, temperature=0.0, stop_ids=[], on_token=on_token)
+    torch.cuda.synchronize()
+    if len(stamps) < skip + steps + 1:
+        return None
+    return (stamps[skip + steps] - stamps[skip]) / steps * 1e3
+
+
 def time_prefill(engine, tokens, reps=3):
     import torch
     from rbitnet_b200 import StepEntry
@@ -504,7 +529,7 @@ def main():
     layers = full_layers if args.layers == FULL_LAYERS else min(args.layers, full_layers)
     cfg = dict(model, num_hidden_layers=layers)
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
-    room = steps + warmup + 16
+    room = steps + warmup + 64 + 16     # time_generate leaves 64 further steps out
     ctx = max(1, min(max_seq - room, args.context))
     max_tokens = max(b * (-(-(max(ctx, PROMPT_LEN) + room) // 64) * 64) for b in batches) + 64 * 64
     t_build = time.time()
@@ -540,6 +565,7 @@ def main():
     try:
         ms, launches, clocks = time_decode(engine, args.batch, ctx, steps, warmup, sampler)
         e2e_ms, h2d, d2h = time_decode_e2e(engine, args.batch, ctx, steps, warmup)
+        gen_ms = None if args.no_points else time_generate(engine, args.batch, ctx, steps, warmup)
         points, prefill = {}, None
         if not args.no_points:
             for b in (1, 64):
@@ -589,6 +615,10 @@ def main():
     if prefill is not None:
         line["prefill"] = prefill
         line["points"] = points
+    if gen_ms:
+        line["generate"] = {"value": round(args.batch / gen_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(gen_ms, 4),
+                            "what": "the same decode steps through Engine.generate (host prompts in, ids out by "
+                                    "callback; a step is launched ahead of the ids it reads)"}
     print(json.dumps(line))
     return 0
 
