@@ -77,7 +77,19 @@ struct GemmParams {
   int n_items;        // weight tiles * token tiles * splits
   int cluster;        // 1: the splits of a tile form a thread-block cluster and are summed through shared memory
   float alpha;        // multiplies the finished sum of a stored or added product (x * 1.0f is x exactly)
+  // Shared ranges (sk_len > 0; token tiles of 128 and more, no cluster): see the kernel's comment.
+  int sk_len;         // 64-wide k blocks per team of CTAs
+  int n_w_tiles;      // 128-row tiles of W
+  int* sk_finished;   // [weight tile][token tile]: parts of the tile that are in C; zero between launches
   QkvTail qkv;        // EPI_QKV only
+};
+
+// What one pass of a CTA's three roles covers: k blocks kb_begin .. kb_begin + nkb - 1 of the tile
+// at (n0, t0).  With shared ranges a tile's K may be covered by `parts` teams, of which this is
+// number `part` (teams first_team .. first_team + parts - 1, in the order of their k blocks).
+struct Piece {
+  int n0, t0, kb_begin, nkb;
+  int w_tile, part, parts, first_team;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -95,25 +107,52 @@ __device__ __forceinline__ void cluster_sync_all() {
 // MINB: CTAs that share an SM (2 for the small token tiles of a decode step: twice as many, smaller
 // items stream W together and finish together, which evens out an item count that does not
 // divide by the number of SMs).
+//
+// Shared ranges (p.sk_len > 0; products added to C, token tiles of 128 and more).  Tiles in turn
+// leave SMs idle in the last round whenever the tiles are not a multiple of the SMs (2,048 tokens
+// times 4,096 rows: 256 tiles on 148 SMs take two rounds for 1.73 rounds of work).  Here the CTAs
+// form teams of as many CTAs as there are token tiles; the k blocks of all weight tiles, laid end to
+// end, are cut into equal ranges, one per team, and the CTAs of a team walk the team's range
+// together, each on its own token tile, so that a tile of W is still fetched once for all token
+// tiles.  Where a range begins or ends inside a weight tile, that tile's K is shared by two or more
+// teams.  Each adds its part to C (the memory system does the addition, as for a whole tile), and
+// the parts are added in the order of their k blocks, so that the sum is the same every time: a
+// part's first box waits until the tile's count of finished parts has reached the part's number.  A
+// part that waits is never the first piece of a range that ends inside a tile, which is the piece
+// that holds the tile's first k blocks and is taken first; so the part that everybody else waits
+// for waits for nobody, all CTAs of the launch are resident (one per SM at most), and every wait is
+// bounded like the others.  The last part sets the count back to zero.
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 __global__ void __launch_bounds__(192, MINB)
-gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, GemmParams p) {
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+               const __grid_constant__ CUtensorMap tmC, GemmParams p) {
   constexpr int X_TILE_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
   constexpr int ACC_COLS = BN;
   constexpr int NBUF = 2 * ACC_COLS <= 512 ? 2 : 1;
   constexpr int WANT_COLS = NBUF * ACC_COLS;
   constexpr int TMEM_COLS = WANT_COLS <= 32 ? 32 : (WANT_COLS <= 64 ? 64 : (WANT_COLS <= 128 ? 128 : (WANT_COLS <= 256 ? 256 : 512)));
+  constexpr bool SHARED_RANGES = BN >= 128 && EPI == EPI_ADD;     // compiled in for these only
+  // Token tiles of 128 and more leave through shared memory: 16 token rows of the tile at a time are
+  // staged there and go out as one TMA box (stored, or added to the residual stream by the memory
+  // system), two boxes in flight.  Stores a thread makes itself have one chunk of loads or stores in
+  // flight per thread, about 8 KB an SM, and an epilogue of a 128 x 256 tile then takes longer than
+  // the products of a short tile.
+  constexpr bool TMA_EPI = BN >= 128 && EPI != EPI_QKV;
+  constexpr int OUT_COLS = EPI == EPI_GATED ? BM / 2 : BM;          // values per token row of a staged box
+  constexpr int OUT_STAGE_BYTES = 16 * BM * 4;                      // room for 16 rows of float32
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
   static_assert(WANT_COLS <= 512, "tensor memory has 512 columns");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* out_stage = smem + (size_t)STAGES * STAGE_BYTES;          // TMA_EPI: two boxes of OUT_STAGE_BYTES
   __shared__ uint64_t full_bar[STAGES];
   __shared__ uint64_t empty_bar[STAGES];
   __shared__ uint64_t accum_full[NBUF];
   __shared__ uint64_t accum_empty[NBUF];
   __shared__ uint32_t tmem_holder;
+  __shared__ int epi_fail;
 
   rb_pdl_launch_dependents();     // the next kernel may be set up while this one runs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,6 +162,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   const int item_stride = p.cluster ? p.n_items : gridDim.x;
 
   if (threadIdx.x == 0) {
+    epi_fail = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -149,14 +189,46 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // epilogue warps before they touch C.  W is never written, so its first tiles are requested
   // before the wait and stream in while the kernel before this one finishes.
 
-  // what an item covers
-  auto item_of = [&](int item, int& n0, int& t0, int& kb_begin, int& nkb, int& split) {
-    split = item % p.splits;
+  // the li-th piece of this CTA's work (false: there is none)
+  const bool shared_ranges = SHARED_RANGES && p.sk_len > 0;
+  const int sk_team = shared_ranges ? (int)blockIdx.x / p.n_t_tiles : 0;
+  const int sk_tt = shared_ranges ? (int)blockIdx.x % p.n_t_tiles : 0;
+  auto piece_at = [&](int li, Piece& s) -> bool {
+    if (SHARED_RANGES && shared_ranges) {
+      const long long begin = (long long)sk_team * p.sk_len;
+      const long long total = (long long)p.n_w_tiles * nkb_total;
+      const long long end = begin + p.sk_len < total ? begin + p.sk_len : total;
+      // Pieces in the order of their k blocks: g0, g0 + 1, ..., g_last.  A piece that ends the range
+      // inside a weight tile is taken first instead of last: then both shared pieces of a team come
+      // before its whole tiles, whose products hide the passing of the parts through memory.
+      const int g0 = (int)(begin / nkb_total), g_last = (int)((end - 1) / nkb_total);
+      if (begin >= end || li > g_last - g0) return false;
+      const bool last_first = g_last > g0 && end < (long long)(g_last + 1) * nkb_total;
+      const int g = last_first ? (li == 0 ? g_last : g0 + li - 1) : g0 + li;
+      const long long from = g == g0 ? begin : (long long)g * nkb_total;
+      const long long g_begin = (long long)g * nkb_total, g_end = g_begin + nkb_total;
+      const long long to = g_end < end ? g_end : end;
+      s.w_tile = g;
+      s.n0 = g * BM;
+      s.t0 = sk_tt * BN;
+      s.kb_begin = (int)(from - g_begin);
+      s.nkb = (int)(to - from);
+      s.first_team = (int)(g_begin / p.sk_len);
+      s.parts = (int)((g_end - 1) / p.sk_len) - s.first_team + 1;
+      s.part = sk_team - s.first_team;
+      return true;
+    }
+    const int item = first_item + li * item_stride;
+    if (item >= p.n_items) return false;
+    const int split = item % p.splits;
     const int tile = item / p.splits;
-    n0 = (tile / p.n_t_tiles) * BM;
-    t0 = (tile % p.n_t_tiles) * BN;
-    kb_begin = split * p.kb_per_split;
-    nkb = max(0, min(nkb_total, kb_begin + p.kb_per_split) - kb_begin);
+    s.w_tile = tile / p.n_t_tiles;
+    s.n0 = s.w_tile * BM;
+    s.t0 = (tile % p.n_t_tiles) * BN;
+    s.kb_begin = split * p.kb_per_split;
+    s.nkb = max(0, min(nkb_total, s.kb_begin + p.kb_per_split) - s.kb_begin);
+    s.part = 0; s.parts = 1; s.first_team = 0;
+    return true;
   };
 
   if (warp == 0) {
@@ -164,39 +236,36 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      // the first item's first stages: W before the wait, X after it
+      // the first piece's first stages: W before the wait, X after it
       int early = 0;
-      if (first_item < p.n_items) {
-        int n0, t0, kb_begin, nkb, split;
-        item_of(first_item, n0, t0, kb_begin, nkb, split);
-        early = min(nkb, STAGES);
+      Piece s;
+      if (piece_at(0, s)) {
+        early = min(s.nkb, STAGES);
         for (int i = 0; i < early; ++i) {
           uint8_t* stage = smem + (size_t)i * STAGE_BYTES;
           mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-          const int k = (kb_begin + i) * BK;
-          tma_load_2d(stage, &tmW, k, n0, &full_bar[i]);
+          const int k = (s.kb_begin + i) * BK;
+          tma_load_2d(stage, &tmW, k, s.n0, &full_bar[i]);
         }
         rb_pdl_wait();
         for (int i = 0; i < early; ++i) {
           uint8_t* stage = smem + (size_t)i * STAGE_BYTES;
-          tma_load_2d(stage + W_TILE_BYTES, &tmX, (kb_begin + i) * BK, t0, &full_bar[i]);
+          tma_load_2d(stage + W_TILE_BYTES, &tmX, (s.kb_begin + i) * BK, s.t0, &full_bar[i]);
         }
       }
-      for (int item = first_item; item < p.n_items && ok; item += item_stride) {
-        int n0, t0, kb_begin, nkb, split;
-        item_of(item, n0, t0, kb_begin, nkb, split);
+      for (int li = 0; ok && piece_at(li, s); ++li) {
         int i = 0;
-        if (item == first_item) { i = early; it = early; }
-        for (; i < nkb; ++i, ++it) {
-          const int s = it % STAGES;
+        if (li == 0) { i = early; it = early; }
+        for (; i < s.nkb; ++i, ++it) {
+          const int st = it % STAGES;
           const uint32_t phase = (it / STAGES) & 1;
-          ok = mbar_wait(&empty_bar[s], phase ^ 1, 1);
+          ok = mbar_wait(&empty_bar[st], phase ^ 1, 1);
           if (!ok) break;
-          uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-          const int k = (kb_begin + i) * BK;
-          tma_load_2d(stage, &tmW, k, n0, &full_bar[s]);
-          tma_load_2d(stage + W_TILE_BYTES, &tmX, k, t0, &full_bar[s]);
+          uint8_t* stage = smem + (size_t)st * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+          const int k = (s.kb_begin + i) * BK;
+          tma_load_2d(stage, &tmW, k, s.n0, &full_bar[st]);
+          tma_load_2d(stage + W_TILE_BYTES, &tmX, k, s.t0, &full_bar[st]);
         }
       }
     }
@@ -204,11 +273,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BN);
-      uint32_t it = 0, li = 0;
+      uint32_t it = 0;
       bool ok = true;
-      for (int item = first_item; item < p.n_items && ok; item += item_stride, ++li) {
-        int n0, t0, kb_begin, nkb, split;
-        item_of(item, n0, t0, kb_begin, nkb, split);
+      Piece s;
+      for (int li = 0; ok && piece_at(li, s); ++li) {
+        const int nkb = s.nkb;
         const int b = li % NBUF;
         ok = mbar_wait(&accum_empty[b], ((li / NBUF) & 1) ^ 1, 4);    // the epilogue has drained this accumulator
         if (!ok) break;
@@ -237,17 +306,19 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;        // tensor-memory lanes 32*quarter .. +31 belong to this warp
+    const int row = quarter * 32 + lane;
+    const bool issuer = warp == 2 && lane == 0;      // the one thread that sends the boxes of TMA_EPI
     rb_pdl_wait();                       // before C is read or written
-    uint32_t li = 0;
-    for (int item = first_item; item < p.n_items; item += item_stride, ++li) {
-      int n0, t0, kb_begin, nkb, split;
-      item_of(item, n0, t0, kb_begin, nkb, split);
+    uint32_t n_boxes = 0;
+    Piece s;
+    for (int li = 0; piece_at(li, s); ++li) {
+      const int n0 = s.n0, t0 = s.t0, nkb = s.nkb;
       const int b = li % NBUF;
-      const int n = n0 + quarter * 32 + lane;           // output column = weight row
+      const int n = n0 + row;                           // output column = weight row
       const bool n_ok = n < p.n_out;
-      // EPI_ADD: the values to add to do not depend on the accumulator.  They are fetched one chunk
-      // ahead, the first chunk while the products of this item still run, so that the epilogue
-      // waits for memory once per item and not once per chunk.
+      // EPI_ADD without TMA: the values to add to do not depend on the accumulator.  They are fetched
+      // one chunk ahead, the first chunk while the products of this item still run, so that the
+      // epilogue waits for memory once per item and not once per chunk.
       float ahead[16];
       auto fetch_old = [&](int c, float* into) {
         const int left = n_ok ? p.n_tokens - (t0 + c) : 0;
@@ -255,12 +326,29 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 16; ++j) into[j] = j < left ? src[(int64_t)j * p.ldc] : 0.f;
       };
-      if (EPI == EPI_ADD && !p.cluster) fetch_old(0, ahead);
+      if (EPI == EPI_ADD && !TMA_EPI && !p.cluster) fetch_old(0, ahead);
       bool ok = true;
       if (lane == 0) ok = mbar_wait(&accum_full[b], (li / NBUF) & 1, 3);
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (TMA_EPI) {
+        // the four warps meet at barriers below: they go on together or leave together
+        if (!ok && lane == 0) epi_fail = 1;
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        ok = *(volatile int*)&epi_fail == 0;
+      }
       if (!ok) break;
       tcgen05_fence_after();
+      // columns c .. c+15 of this warp's 32 rows of the accumulator
+      auto load_acc = [&](int c, uint32_t (&r)[16]) {
+        __syncwarp();
+        if (nkb > 0) {
+          tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * ACC_COLS + c), r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+      };
       if (p.cluster) {
         // this split's accumulator goes to shared memory (the stage ring is idle now: every MMA
         // that read it has completed); the splits are added up after the cluster barrier below
@@ -269,69 +357,110 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int c = 0; c < BN; c += 16) {
           if (t0 + c >= p.n_tokens) break;
           uint32_t r[16];
-          __syncwarp();
-          if (nkb > 0) {
-            tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * ACC_COLS + c), r);
-            tmem_ld_wait();
-          } else {
+          load_acc(c, r);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = 0u;
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) red[(c + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+          for (int j = 0; j < 16; ++j) red[(c + j) * BM + row] = __uint_as_float(r[j]);
         }
         break;        // one item per CTA in this mode
       }
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
-        if (t0 + c >= p.n_tokens) break;
-        uint32_t r[16];
-        __syncwarp();
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * ACC_COLS + c);
-        if (nkb > 0) {
-          tmem_ld16(taddr, r);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) r[j] = 0u;
+      if constexpr (TMA_EPI) {
+        // A tile whose K is shared: the parts are added to C in the order of their k blocks, so this
+        // part's first box waits until the count of finished parts has reached its own number.
+        int* finished = nullptr;
+        bool must_wait = false;
+        if (SHARED_RANGES && s.parts > 1) {
+          finished = p.sk_finished + (int64_t)s.w_tile * p.n_t_tiles + sk_tt;
+          must_wait = s.part > 0;
         }
-        // rows of this chunk that exist (none for a lane whose weight row is beyond the matrix);
-        // no lane leaves the loop early: tcgen05.ld is executed by the whole warp
-        const int t_left = n_ok ? p.n_tokens - (t0 + c) : 0;
-        if (EPI == EPI_ADD) {
-          float* dst = (float*)p.C + (int64_t)(t0 + c) * p.ldc + n;
-          float old[16];
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (t0 + c >= p.n_tokens) break;
+          uint32_t r[16];
+          load_acc(c, r);
+          // The 16 token rows of the chunk go to shared memory as [token][OUT_COLS values] and leave as
+          // one box; rows and columns beyond the matrix are dropped by the tensor map.
+          OutT* box = reinterpret_cast<OutT*>(out_stage + (n_boxes & 1) * OUT_STAGE_BYTES);
+          ++n_boxes;
+          if (EPI == EPI_GATED) {
+            // Lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features (feature =
+            // (weight row block of 32) * 16 + lane % 16).  Columns are taken in pairs: the lower lanes
+            // finish the even token of a pair, the upper lanes the odd one, so that every lane does one
+            // activation per two columns.  Every lane takes part in the shuffles.
+            const bool low = lane < 16;
+            OutT* dst = box + (low ? 0 : OUT_COLS) + quarter * 16 + (lane & 15);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) old[j] = ahead[j];
-          if (c + 16 < BN) fetch_old(c + 16, ahead);       // the next chunk's loads are in flight during these stores
+            for (int j = 0; j < 16; j += 2) {
+              const float mine = __uint_as_float(low ? r[j] : r[j + 1]);       // gate (low) or up (high) of my token
+              const float send = __uint_as_float(low ? r[j + 1] : r[j]);       // what the partner needs
+              const float got = __shfl_xor_sync(0xffffffffu, send, 16);
+              const float g = low ? mine : got, up = low ? got : mine;
+              // silu(g) * up = g * up / (1 + e^-g), with the hardware's exponential and reciprocal: their
+              // error (a few units of float32) is far below the rounding to bfloat16 that follows
+              store_out<OutT>(dst + j * OUT_COLS, __fdividef(g, 1.0f + __expf(-g)) * up);
+            }
+          } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]) * p.alpha;
-        } else if (EPI == EPI_GATED) {
-          // Lanes 0..15 hold gate rows, lanes 16..31 the up rows of the same 16 features (feature =
-          // (weight row block of 32) * 16 + lane % 16).  Columns are taken in pairs: the lower lanes
-          // finish the even token of a pair, the upper lanes the odd one, so that every lane does one
-          // activation per two columns.  Every lane takes part in the shuffles.
-          const bool low = lane < 16;
-          const int f = (n0 + quarter * 32) / 2 + (lane & 15);
-          const int f_left = f < p.n_features ? p.n_tokens - (t0 + c) : 0;
-          OutT* dst = (OutT*)p.C + (int64_t)(t0 + c + (low ? 0 : 1)) * p.ldc + f;
-#pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            const float mine = __uint_as_float(low ? r[j] : r[j + 1]);       // gate (low) or up (high) of my token
-            const float send = __uint_as_float(low ? r[j + 1] : r[j]);       // what the partner needs
-            const float got = __shfl_xor_sync(0xffffffffu, send, 16);
-            const float g = low ? mine : got, up = low ? got : mine;
-            // silu(g) * up = g * up / (1 + e^-g), with the hardware's exponential and reciprocal: their
-            // error (a few units of float32) is far below the rounding to bfloat16 that follows
-            const float v = __fdividef(g, 1.0f + __expf(-g)) * up;
-            if (j + (low ? 0 : 1) < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
+            for (int j = 0; j < 16; ++j) store_out<OutT>(box + j * OUT_COLS + row, __uint_as_float(r[j]) * p.alpha);
           }
-        } else {
-          OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
+          fence_async_shared();
+          if (issuer) bulk_wait_read_all();          // the box before this one has left its half of the staging area
+          asm volatile("bar.sync 3, 128;" ::: "memory");
+          if (issuer) {
+            if (must_wait) {
+              if (!wait_for_count(finished, s.part, 4)) epi_fail = 1;     // noticed at the next piece; the results are void
+              must_wait = false;
+            }
+            tma_store_2d(&tmC, box, EPI == EPI_GATED ? n0 / 2 : n0, t0 + c, EPI == EPI_ADD);
+            bulk_commit();
+          }
+        }
+        if (finished != nullptr && issuer) {
+          // this part is in C: count it, or, as the last part, set the count back for the next launch
+          bulk_wait_all();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          const int now = s.part + 1 == s.parts ? 0 : s.part + 1;
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(finished), "r"(now) : "memory");
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (t0 + c >= p.n_tokens) break;
+          uint32_t r[16];
+          load_acc(c, r);
+          // rows of this chunk that exist (none for a lane whose weight row is beyond the matrix);
+          // no lane leaves the loop early: tcgen05.ld is executed by the whole warp
+          const int t_left = n_ok ? p.n_tokens - (t0 + c) : 0;
+          if (EPI == EPI_ADD) {
+            float* dst = (float*)p.C + (int64_t)(t0 + c) * p.ldc + n;
+            float old[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]) * p.alpha);
+            for (int j = 0; j < 16; ++j) old[j] = ahead[j];
+            if (c + 16 < BN) fetch_old(c + 16, ahead);       // the next chunk's loads are in flight during these stores
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]) * p.alpha;
+          } else if (EPI == EPI_GATED) {
+            // as above, each lane storing its own values
+            const bool low = lane < 16;
+            const int f = (n0 + quarter * 32) / 2 + (lane & 15);
+            const int f_left = f < p.n_features ? p.n_tokens - (t0 + c) : 0;
+            OutT* dst = (OutT*)p.C + (int64_t)(t0 + c + (low ? 0 : 1)) * p.ldc + f;
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              const float mine = __uint_as_float(low ? r[j] : r[j + 1]);
+              const float send = __uint_as_float(low ? r[j + 1] : r[j]);
+              const float got = __shfl_xor_sync(0xffffffffu, send, 16);
+              const float g = low ? mine : got, up = low ? got : mine;
+              const float v = __fdividef(g, 1.0f + __expf(-g)) * up;
+              if (j + (low ? 0 : 1) < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
+            }
+          } else {
+            OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]) * p.alpha);
+          }
         }
       }
       // this warp has read its lanes of the accumulator: hand it back to the MMA issuer
@@ -339,6 +468,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&accum_empty[b]);
     }
+    if (TMA_EPI && issuer) bulk_wait_all();      // the last boxes are in global memory
   }
   if (p.cluster) {
     // every thread of every CTA of the cluster arrives here, also after a wait that gave up
@@ -353,8 +483,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       // and writes the one rounded result where it belongs.  All four epilogue warps pass the
       // barrier between the two steps, whatever their rows.
       static_assert(BN > 64 || 2 * BN * BM * 4 <= STAGES * STAGE_BYTES, "the ring holds the accumulators and the sums");
-      int n0, t0, kb_begin, nkb, split;
-      item_of(first_item, n0, t0, kb_begin, nkb, split);
+      Piece pc;
+      piece_at(0, pc);
+      const int n0 = pc.n0, t0 = pc.t0;
       const QkvTail& q = p.qkv;
       const int D = q.cache.head_dim, HD = q.H * D, KD = q.write_kv ? q.cache.n_kv_heads * D : 0;
       const int row = (warp & 3) * 32 + lane, n = n0 + row, d = n % D;
@@ -422,8 +553,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (EPI != EPI_GATED && EPI != EPI_QKV && warp >= 2 && first_item < p.n_items) {   // (the gated product is never split)
       // every CTA of the cluster adds up a share of the token columns (column c belongs to rank
       // c mod splits), reading all parts of a column in split order through distributed shared memory
-      int n0, t0, kb_begin, nkb, split;
-      item_of(first_item, n0, t0, kb_begin, nkb, split);
+      Piece pc;
+      piece_at(0, pc);
+      const int n0 = pc.n0, t0 = pc.t0;
       const int quarter = warp & 3;
       const int n = n0 + quarter * 32 + lane;
       const int my = (int)cluster_rank();
@@ -497,8 +629,10 @@ EncodeTiledFn encode_fn() {
 
 struct MapKey {
   const void* ptr; long long rows; int cols; int64_t ld; int box_rows;
+  int box_cols, elem_bytes;        // 0, 0: a bfloat16 operand (box of 64 columns, 128-byte swizzle)
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows &&
+           box_cols == o.box_cols && elem_bytes == o.elem_bytes;
   }
 };
 struct MapKeyHash {
@@ -508,6 +642,7 @@ struct MapKeyHash {
     h = h * 1000003u ^ (size_t)k.cols;
     h = h * 1000003u ^ (size_t)k.ld;
     h = h * 1000003u ^ (size_t)k.box_rows;
+    h = h * 1000003u ^ (size_t)(k.box_cols * 8 + k.elem_bytes);
     return h;
   }
 };
@@ -517,25 +652,30 @@ struct MapKeyHash {
 // functions of them.
 }  // namespace
 
-int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows) {
+static int get_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows, int box_cols,
+                   int elem_bytes) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  MapKey key{ptr, rows, cols, ld, box_rows};
+  MapKey key{ptr, rows, cols, ld, box_rows, box_cols, elem_bytes};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return 0; }
   }
+  const bool operand = elem_bytes == 0;
+  const int eb = operand ? 2 : elem_bytes;
   EncodeTiledFn fn = encode_fn();
   RB_REQUIRE(fn != nullptr, "rb_gemm: cuTensorMapEncodeTiled is not available from the driver");
   RB_REQUIRE(((uintptr_t)ptr & 15) == 0, "rb_gemm: matrix base %p is not 16-byte aligned", ptr);
-  RB_REQUIRE((ld * 2) % 16 == 0, "rb_gemm: row stride of %lld elements is not a multiple of 8", (long long)ld);
+  RB_REQUIRE((ld * eb) % 16 == 0, "rb_gemm: row stride of %lld elements is not a multiple of %d", (long long)ld, 16 / eb);
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * eb};
+  cuuint32_t box[2] = {(cuuint32_t)(operand ? BK : box_cols), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = fn(out, operand || eb == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                  const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  operand ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   RB_REQUIRE(r == CUDA_SUCCESS, "rb_gemm: cuTensorMapEncodeTiled failed with %d (rows %lld cols %d ld %lld)", (int)r,
              rows, cols, (long long)ld);
@@ -545,12 +685,22 @@ int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int col
   return 0;
 }
 
+int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows) {
+  return get_map(out, ptr, rows, cols, ld, box_rows, 0, 0);
+}
+
+int rb_get_output_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows, int box_cols,
+                      int elem_bytes) {
+  RB_REQUIRE(elem_bytes == 2 || elem_bytes == 4, "rb_get_output_map: element of %d bytes", elem_bytes);
+  return get_map(out, ptr, rows, cols, ld, box_rows, box_cols, elem_bytes);
+}
+
 namespace {
 
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
-int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+int launch(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
   constexpr int stage_bytes = W_TILE_BYTES + BN * BK * 2;
-  constexpr int smem = STAGES * stage_bytes + 1024;
+  constexpr int smem = STAGES * stage_bytes + 1024 + (BN >= 128 ? 2 * 16 * BM * 4 : 0);
   static_assert(smem * MINB <= 227 * 1024, "shared memory");
   auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT, MINB>;
   static RbOncePerDevice configured;
@@ -573,27 +723,32 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cu
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = rb_pdl_enabled() ? 2 : 1;
-    RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tw, tx, p));
+    RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tw, tx, tc, p));
     return 0;
   }
   const int slots = rb_sm_count() * MINB;
-  const int grid = p.n_items < slots ? p.n_items : slots;     // resident CTAs take items in turn
-  RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, p);
+  int grid = p.n_items < slots ? p.n_items : slots;     // resident CTAs take items in turn
+  if (p.sk_len > 0) {
+    RB_REQUIRE(BN >= 128 && EPI != EPI_QKV && p.n_items <= slots, "rb_gemm_tc: shared ranges with a token tile of %d, %d CTAs", BN, p.n_items);
+    grid = p.n_items;                                    // one CTA per team and token tile
+  }
+  RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, tc, p);
   RB_CHECK_LAUNCH("rb_gemm_tc");
   return 0;
 }
 
 template <int EPI, typename OutT>
-int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+int dispatch(int bn, const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, const GemmParams& p,
+             cudaStream_t stream) {
   switch (bn) {
-    case 16: return launch<16, 5, EPI, OutT, 2>(tw, tx, p, stream);
-    case 32: return launch<32, 5, EPI, OutT, 2>(tw, tx, p, stream);
-    case 64: return launch<64, 4, EPI, OutT, 2>(tw, tx, p, stream);
-    case 128: return launch<128, 6, EPI, OutT, 1>(tw, tx, p, stream);
-    case 160: return launch<160, 5, EPI, OutT, 1>(tw, tx, p, stream);
-    case 192: return launch<192, 5, EPI, OutT, 1>(tw, tx, p, stream);
-    case 224: return launch<224, 4, EPI, OutT, 1>(tw, tx, p, stream);
-    case 256: return launch<256, 4, EPI, OutT, 1>(tw, tx, p, stream);
+    case 16: return launch<16, 5, EPI, OutT, 2>(tw, tx, tc, p, stream);
+    case 32: return launch<32, 5, EPI, OutT, 2>(tw, tx, tc, p, stream);
+    case 64: return launch<64, 4, EPI, OutT, 2>(tw, tx, tc, p, stream);
+    case 128: return launch<128, 6, EPI, OutT, 1>(tw, tx, tc, p, stream);
+    case 160: return launch<160, 5, EPI, OutT, 1>(tw, tx, tc, p, stream);
+    case 192: return launch<192, 5, EPI, OutT, 1>(tw, tx, tc, p, stream);
+    case 224: return launch<224, 4, EPI, OutT, 1>(tw, tx, tc, p, stream);
+    case 256: return launch<256, 4, EPI, OutT, 1>(tw, tx, tc, p, stream);
   }
   RB_FAIL("rb_gemm_tc: no kernel for a token tile of %d", bn);
 }
@@ -662,6 +817,101 @@ RB_EXPORT int rb_gemm_tc_splits(int n_tokens, int n_out, int K) {
   return (blocks + per - 1) / per;          // no part may be empty
 }
 
+// ---------------------------------------------------------------- shared ranges: the plan and the counters
+namespace {
+constexpr int SK_MAX_COUNTS = 1 << 16;             // tiles whose finished parts can be counted
+struct SkWorkspace { void* ptr = nullptr; long long bytes = 0; };
+SkWorkspace g_sk_ws[64];
+std::mutex g_sk_mu;
+int g_sk_len_for_test = 0;       // > 0: k blocks per team whatever the estimate says (tests)
+
+double item_cost(int bn) { return 0.4 + 0.6 * bn / 256.0; }
+
+struct GemmPlan { int bn; int sk_len; int teams; int n_t; double cost; };
+
+// Tiles in turn against shared ranges for one token tile: the estimated time in units of one item of
+// 256 tokens.  In turn: rounds of the SMs.  Shared ranges (`shared_ok`: an added product with
+// counters to use): the weight tiles divided among the teams (SMs / token tiles of them); and since
+// the parts of a shared tile are added to C one after the other, as many times the leaving of a tile
+// as the tile with the most parts has parts.  A tile of 256 tokens that is added to C takes about as
+// long to leave as 12 of its k blocks take to multiply (5 us against 0.4 us; measured on 4,096 rows
+// times 4,096 and 14,336 with 300, 1,200 and 2,048 tokens).
+GemmPlan plan_for_tile(int n_tokens, int n_out, int K, int bn, int sms, bool shared_ok) {
+  const long long w_tiles = (n_out + BM - 1) / BM, n_t = (n_tokens + bn - 1) / bn, nkb = (K + BK - 1) / BK;
+  GemmPlan pl{bn, 0, 0, (int)n_t, 0.0};
+  const long long rounds = (w_tiles * n_t + sms - 1) / sms;
+  pl.cost = (double)rounds * item_cost(bn);
+  if (!shared_ok || bn < 128 || n_t > sms || w_tiles * n_t > SK_MAX_COUNTS) return pl;
+  const double leaving = 12.0 / nkb * bn / 256.0;
+  pl.cost += leaving;
+  const long long teams = sms / n_t, total = w_tiles * nkb;
+  long long len = (total + teams - 1) / teams;
+  len = (len + 3) / 4 * 4;                       // no part shorter than four k blocks where K allows it
+  const bool forced = g_sk_len_for_test > 0 && g_sk_len_for_test >= (total + teams - 1) / teams;
+  if (forced) len = g_sk_len_for_test;
+  if (len >= (1ll << 30)) return pl;
+  const long long used = (total + len - 1) / len;
+  const long long most_parts = len >= nkb ? 2 : (nkb + len - 1) / len + 1;
+  const double shared_cost = (double)len / nkb * item_cost(bn) + most_parts * leaving;
+  if (forced || shared_cost < pl.cost - 1e-9) { pl.cost = forced ? 0.0 : shared_cost; pl.sk_len = (int)len; pl.teams = (int)used; }
+  return pl;
+}
+
+GemmPlan plan_gemm(int n_tokens, int n_out, int K, int token_tile, int sms, bool shared_ok) {
+  if (token_tile != 0) return plan_for_tile(n_tokens, n_out, K, token_tile, sms, shared_ok);
+  const int bn = n_tokens <= 16 ? 16 : n_tokens <= 32 ? 32 : n_tokens <= 64 ? 64 : n_tokens <= 128 ? 128 : 256;
+  GemmPlan best = plan_for_tile(n_tokens, n_out, K, bn, sms, shared_ok);
+  if (n_tokens > 128) {
+    // Take the token tile (128 to 256 in steps of 32) that needs the least time.  An item of 128
+    // tokens costs about 0.7 of one of 256, not half (measured: with half, a 1,024-token prefill
+    // took 16.7 ms instead of 13.9 because the gate/up product moved to 128); between them the cost
+    // is taken as linear.
+    for (int cand = 128; cand <= 256; cand += 32) {
+      const GemmPlan pl = plan_for_tile(n_tokens, n_out, K, cand, sms, shared_ok);
+      if (cand == 128 || pl.cost < best.cost - 1e-9) best = pl;
+    }
+  }
+  return best;
+}
+}  // namespace
+
+// Bytes of device memory that rb_gemm_tc_set_workspace wants.
+RB_EXPORT long long rb_gemm_tc_workspace_bytes() { return (long long)SK_MAX_COUNTS * 4; }
+
+// Gives the products of the current device their counters for shared ranges (see the kernel): they
+// must be zero, and the kernels leave them zero.  Products on different streams must not overlap in
+// time: they share them.  Without them (or with ptr == nullptr, which takes them away) tiles are
+// taken in turn.
+RB_EXPORT int rb_gemm_tc_set_workspace(void* ptr, long long bytes) {
+  int dev = 0;
+  RB_CUDA(cudaGetDevice(&dev));
+  RB_REQUIRE(dev >= 0 && dev < 64, "rb_gemm_tc_set_workspace: device %d", dev);
+  RB_REQUIRE(ptr == nullptr || (bytes >= (long long)SK_MAX_COUNTS * 4 && ((uintptr_t)ptr & 15) == 0),
+             "rb_gemm_tc_set_workspace: %lld bytes at %p, wanted %lld, 16-byte aligned", bytes, ptr, (long long)SK_MAX_COUNTS * 4);
+  std::lock_guard<std::mutex> g(g_sk_mu);
+  g_sk_ws[dev].ptr = ptr;
+  g_sk_ws[dev].bytes = ptr ? bytes : 0;
+  return 0;
+}
+
+// For tests: added products share their weight tiles with this many k blocks per team (if the SMs
+// suffice for that), whatever the estimate says; 0 takes it back.
+RB_EXPORT int rb_gemm_tc_share_for_test(int blocks_per_team) {
+  RB_REQUIRE(blocks_per_team >= 0, "rb_gemm_tc_share_for_test: %d", blocks_per_team);
+  g_sk_len_for_test = blocks_per_team;
+  return 0;
+}
+
+// What rb_gemm_tc would do with these sizes on a device of `sms` SMs: out = {token tile, k blocks
+// per team (0: tiles in turn), teams, token tiles}.  `shared_ok`: an added product (epilogue 1) on a
+// device that has its counters.  No device is touched.
+RB_EXPORT int rb_gemm_tc_plan(int n_tokens, int n_out, int K, int token_tile, int sms, int shared_ok, int* out) {
+  RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0 && sms > 0 && out != nullptr, "rb_gemm_tc_plan: bad arguments");
+  const GemmPlan pl = plan_gemm(n_tokens, n_out, K, token_tile, sms, shared_ok != 0);
+  out[0] = pl.bn; out[1] = pl.sk_len; out[2] = pl.teams; out[3] = pl.n_t;
+  return 0;
+}
+
 // C (+)= X W^T on the tensor cores.
 //   epilogue 0: C[tokens, n_out] = alpha * product, c_dtype float32 or bfloat16
 //   epilogue 1: C (float32) += alpha * product
@@ -683,32 +933,30 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   RB_REQUIRE(splits <= 8, "rb_gemm_tc: at most 8 splits are summed on the device (%d asked)", splits);
   const int nkb = (K + BK - 1) / BK;
   RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
-  int bn = token_tile;
-  if (bn == 0) {
-    bn = n_tokens <= 16 ? 16 : n_tokens <= 32 ? 32 : n_tokens <= 64 ? 64 : n_tokens <= 128 ? 128 : 256;
-    if (n_tokens > 128 && n_tokens <= 4096) {
-      // Few enough tokens that tiles of 256 may leave most SMs without an item, or with a last round
-      // of few: take the tile (128 to 256 tokens in steps of 32) that needs the least time, counted as
-      // rounds of the SMs times what an item costs.  An item of 128 tokens costs about 0.7 of one
-      // of 256, not half (measured: with half, a 1,024-token prefill took 16.7 ms instead of 13.9
-      // because the gate/up product moved to 128); between them the cost is taken as linear.  Measured
-      // against tiles of 128 and 256 alone: 300 tokens 7.6 ms instead of 8.2, 768 tokens 10.5 instead
-      // of 11.35, 1,200 tokens 16.7 instead of 18.2, 1,500 tokens 19.2 instead of 20.4; 2,048 and 4,096
-      // tokens take 256 as before.  Beyond 4,096 tokens the rounds are many and 256 stays.
-      const long long w_tiles = (n_out + BM - 1) / BM, sms = rb_sm_count();
-      double best = 0.0;
-      for (int cand = 128; cand <= 256; cand += 32) {
-        const long long rounds = (w_tiles * ((n_tokens + cand - 1) / cand) + sms - 1) / sms;
-        const double cost = (double)rounds * (0.4 + 0.6 * cand / 256.0);
-        if (cand == 128 || cost < best - 1e-9) { best = cost; bn = cand; }
-      }
-    }
+  SkWorkspace ws;
+  if (splits == 1 && epilogue == EPI_ADD) {
+    int dev = 0;
+    RB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> g(g_sk_mu);
+    if (dev >= 0 && dev < 64) ws = g_sk_ws[dev];
   }
+  GemmPlan plan = plan_gemm(n_tokens, n_out, K, token_tile, rb_sm_count(), ws.ptr != nullptr);
+  // token tiles of 128 and more write their output by TMA, which wants a 16-byte aligned base and row
+  // stride; an output that is not (a width of 257 bfloat16 values) takes tiles of 64, which store by themselves
+  const int out_elem = (epilogue == EPI_ADD || c_dtype == RB_F32) ? 4 : 2;
+  if (plan.bn >= 128 && (((uintptr_t)C & 15) != 0 || (ldc * out_elem) % 16 != 0))
+    plan = plan_for_tile(n_tokens, n_out, K, 64, rb_sm_count(), false);
+  const int bn = plan.bn;
   RB_REQUIRE(epilogue != EPI_GATED || (n_out % 32 == 0 && n_features > 0 && n_features <= n_out / 2),
              "rb_gemm_tc: the gated product wants rows in blocks of 32 (%d rows, %d features)", n_out, n_features);
   CUtensorMap tw, tx;
   if (rb_get_tensor_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
   if (rb_get_tensor_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;
+  CUtensorMap tc = tw;               // token tiles below 128 store by themselves
+  if (bn >= 128 && epilogue != EPI_QKV) {
+    const int cols = epilogue == EPI_GATED ? n_features : n_out;
+    if (rb_get_output_map(&tc, C, n_tokens, cols, ldc, 16, epilogue == EPI_GATED ? BM / 2 : BM, out_elem) != 0) return -1;
+  }
   GemmParams p;
   p.C = C; p.ldc = ldc; p.n_tokens = n_tokens; p.n_out = n_out; p.K = K;
   p.n_features = n_features; p.kb_per_split = (nkb + splits - 1) / splits;
@@ -719,16 +967,22 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
   p.cluster = splits > 1 ? 1 : 0;
   p.alpha = alpha;
+  p.n_w_tiles = n_w_tiles;
+  p.sk_len = plan.sk_len;
+  p.sk_finished = (int*)ws.ptr;
+  if (p.sk_len > 0) {
+    p.n_items = plan.teams * n_t_tiles;        // CTAs: one per team and token tile
+  }
   RB_REQUIRE(!p.cluster || bn <= 64, "rb_gemm_tc: K is split only for token tiles of at most 64");
   if (epilogue == EPI_QKV) {
     RB_REQUIRE(tail != nullptr && p.cluster, "rb_gemm_tc: the q/k/v tail wants K split into a cluster");
     p.qkv = *tail;
-    return dispatch<EPI_QKV, __nv_bfloat16>(bn, tw, tx, p, stream);
+    return dispatch<EPI_QKV, __nv_bfloat16>(bn, tw, tx, tc, p, stream);
   }
-  if (epilogue == EPI_STORE && c_dtype == RB_BF16) return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, p, stream);
-  if (epilogue == EPI_STORE && c_dtype == RB_F32) return dispatch<EPI_STORE, float>(bn, tw, tx, p, stream);
-  if (epilogue == EPI_ADD && c_dtype == RB_F32) return dispatch<EPI_ADD, float>(bn, tw, tx, p, stream);
-  if (epilogue == EPI_GATED && c_dtype == RB_BF16) return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, p, stream);
+  if (epilogue == EPI_STORE && c_dtype == RB_BF16) return dispatch<EPI_STORE, __nv_bfloat16>(bn, tw, tx, tc, p, stream);
+  if (epilogue == EPI_STORE && c_dtype == RB_F32) return dispatch<EPI_STORE, float>(bn, tw, tx, tc, p, stream);
+  if (epilogue == EPI_ADD && c_dtype == RB_F32) return dispatch<EPI_ADD, float>(bn, tw, tx, tc, p, stream);
+  if (epilogue == EPI_GATED && c_dtype == RB_BF16) return dispatch<EPI_GATED, __nv_bfloat16>(bn, tw, tx, tc, p, stream);
   RB_FAIL("rb_gemm_tc: unsupported epilogue %d with output dtype %d", epilogue, c_dtype);
 }
 

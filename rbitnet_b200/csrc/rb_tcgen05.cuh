@@ -38,6 +38,9 @@ static inline int rb_file_error_flag_address(int** out) {
 // Tensor map of a row-major bfloat16 matrix [rows, cols] (cols contiguous, row stride ld elements),
 // box [box_rows, 64], 128-byte swizzle, zero fill outside; cached by its arguments.
 int rb_get_tensor_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows);
+// The same for an output: float32 (elem_bytes 4) or bfloat16 (2), box [box_rows, box_cols], no swizzle.
+int rb_get_output_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int64_t ld, int box_rows, int box_cols,
+                      int elem_bytes);
 
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -84,12 +87,50 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
     }
   }
 }
+// Bounded wait for a word in global memory to reach `value` (another CTA of the same launch stores
+// it with release): false, and the error word set to `code`, after `limit_ns`.
+__device__ __forceinline__ bool wait_for_count(const int* word, int value, int code, uint64_t limit_ns = 2000000000ull) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+      if (v == value) return true;
+      __nanosleep(64);
+    }
+    if (global_timer_ns() - t0 > limit_ns) {
+      atomicCAS(&g_error_flag, 0, code);
+      return false;
+    }
+  }
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
       : "memory");
 }
+// A box of shared memory to global memory through a tensor map (rows outside the tensor are
+// dropped); `add`: added to what is there, in the tensor's own type, instead of stored.  Bulk-group
+// completion: commit after issuing, wait before the shared memory is written again.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y, bool add) {
+  if (add)
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk groups have read their shared memory
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all of this thread's bulk groups are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

@@ -64,6 +64,10 @@ class KernelLibrary:
         self.declare("rb_attention_decode_tma_on_chip", [I, I, I])
         self.declare("rb_attention_decode_parts", [I, I, I])
         self.declare("rb_gemm_tc_splits", [I, I, I])
+        self.declare("rb_gemm_tc_workspace_bytes", [], restype=ctypes.c_longlong)
+        self.declare("rb_gemm_tc_set_workspace", [P, L])
+        self.declare("rb_gemm_tc_plan", [I, I, I, I, I, I, P])
+        self.declare("rb_gemm_tc_share_for_test", [I])
         self.declare("rb_device_sm_count", [])
         self.declare("rb_is_checked_build", [])
         for tu in CHECKED_FILES:

@@ -47,6 +47,28 @@ class GateUpWeight:
     block: int = 0
 
 
+#: per device: the workspace of the tensor-core products (arrival counters, then partial sums of
+#: tiles whose inner dimension is shared between teams of CTAs).  One per process and device, never
+#: freed: the library keeps its address.
+_GEMM_WORKSPACES = {}
+_GEMM_WORKSPACE_SET = set()
+_GEMM_COUNTER_BYTES = 4 << 16
+
+
+def _give_gemm_workspace(lib, device: torch.device) -> None:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if (lib.path, index) in _GEMM_WORKSPACE_SET:
+        return
+    with torch.cuda.device(index):
+        ws = _GEMM_WORKSPACES.get(index)
+        if ws is None:
+            n = int(lib.raw("rb_gemm_tc_workspace_bytes")())
+            ws = _GEMM_WORKSPACES[index] = torch.zeros(n, dtype=torch.uint8, device=device)
+            torch.cuda.synchronize(index)
+        lib.call("rb_gemm_tc_set_workspace", c_void_p(ws.data_ptr()), ws.numel(), launches=0)
+    _GEMM_WORKSPACE_SET.add((lib.path, index))
+
+
 class CudaOps:
     def __init__(self, dtype=torch.bfloat16, device="cuda:0", verbose_build: bool = True):
         if dtype not in _CODE:
@@ -66,6 +88,9 @@ class CudaOps:
         #: decode attention of head sizes 64 and 128 gets its keys and values by TMA (else by cp.async)
         self.decode_on_tma = True
         self._flag_ptrs = None
+        #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
+        #: between teams of CTAs (needs the workspace; tiles are taken in turn without it)
+        _give_gemm_workspace(self.lib, self.device)
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -82,6 +107,9 @@ class CudaOps:
         v = ctypes.c_int(0)
         self.lib.call("rb_read_error_flag", ctypes.byref(v), 1, launches=0)
         if v.value:
+            ws = _GEMM_WORKSPACES.get(self.device.index if self.device.index is not None else torch.cuda.current_device())
+            if ws is not None:
+                ws[:_GEMM_COUNTER_BYTES].zero_()      # a product that gave up may have left counts behind
             raise KernelError(f"a kernel gave up waiting (code {v.value}: 1 = loader, 2 = tensor-core issuer, "
                               "3 = epilogue); its results are not valid")
         if self.lib.raw("rb_is_checked_build")():

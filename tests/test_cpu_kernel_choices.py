@@ -81,3 +81,40 @@ def test_parts_of_a_product_and_of_the_plain_decode(lib):
         s = parts(batch, kvh, ctx)
         assert 1 <= s <= min(16, max(1, -(-ctx // 64))), (batch, kvh, ctx, s)
     assert parts(1, 1, 64) == 1 and parts(0, 8, 100) == 1
+
+
+def _plan(lib, T, N, K, sms=148, workspace=1, tile=0):
+    import ctypes
+    out = (ctypes.c_int * 4)()
+    lib.call("rb_gemm_tc_plan", T, N, K, tile, sms, workspace, out, launches=0)
+    return dict(tile=out[0], blocks_per_team=out[1], teams=out[2], token_tiles=out[3])
+
+
+def test_plan_of_a_product_of_many_tokens(lib):
+    """Tiles in turn, or (a product added to its output, on a device that has the counters: `workspace`)
+    the k blocks of all weight tiles shared out evenly among teams of CTAs."""
+    # 2,048 tokens, 4,096 rows: 256 tiles are 1.73 rounds of 148 SMs; 18 teams of 8 CTAs share 32 weight tiles
+    p = _plan(lib, 2048, 4096, 14336)
+    assert p["tile"] == 256 and p["token_tiles"] == 8 and p["teams"] == 18
+    assert p["blocks_per_team"] * 18 >= 32 * 224 > p["blocks_per_team"] * 17 and p["blocks_per_team"] % 4 == 0
+    # without the counters, and for few tokens, tiles are taken in turn
+    assert _plan(lib, 2048, 4096, 14336, workspace=0)["blocks_per_team"] == 0
+    assert _plan(lib, 64, 4096, 4096)["blocks_per_team"] == 0 and _plan(lib, 64, 4096, 4096)["tile"] == 64
+    # tiles that fill whole rounds stay as they are: 37 weight tiles x 8 token tiles = 2 x 148
+    assert _plan(lib, 2048, 37 * 128, 4096)["blocks_per_team"] == 0
+    # few tiles and a long inner dimension: every SM gets a share of some tile's inner dimension
+    p = _plan(lib, 300, 4096, 14336)
+    assert p["tile"] == 160 and p["token_tiles"] == 2 and p["teams"] > 64 and p["blocks_per_team"] > 0
+    # the parts of a tile are added one after the other: not worth it where the products are short
+    assert _plan(lib, 2048, 4096, 4096)["blocks_per_team"] == 0
+    # every part is at least one block, and the teams cover everything, at any size
+    for T in (129, 257, 300, 1000, 2048, 4097, 9000):
+        for N in (128, 130, 4096, 6144, 28672, 128256):
+            for K in (64, 72, 4096, 14336):
+                for sms in (148, 132, 16):
+                    p = _plan(lib, T, N, K, sms=sms)
+                    w_tiles, blocks = -(-N // 128), -(-K // 64)
+                    assert p["tile"] in (128, 160, 192, 224, 256) and p["token_tiles"] == -(-T // p["tile"])
+                    if p["blocks_per_team"]:
+                        assert p["teams"] * p["token_tiles"] <= sms
+                        assert p["teams"] * p["blocks_per_team"] >= w_tiles * blocks > (p["teams"] - 1) * p["blocks_per_team"]

@@ -624,3 +624,71 @@ def test_scales_of_the_embedding_and_of_a_product(ops32, ops16):
             assert _rel(acc, 1.0 - 2.0 * ref) < tol
             plain_ = ops.linear(x, lw, out_dtype=torch.float32)
             assert torch.equal(ops.linear(x, lw, out_dtype=torch.float32, scale=1.0), plain_)
+
+
+@pytest.mark.parametrize("T,N,K,share", [
+    (300, 128, 8192, 4),        # one weight tile, its inner dimension in 32 parts
+    (2048, 4096, 3584, 100),    # 32 weight tiles on 18 teams
+    (2048, 4096, 14336, 0),     # the down product of a 2,048-token prompt, as the library plans it
+    (2048, 520, 2056, 12),      # rows, and an inner size, that fill no tile
+    (1000, 6144, 4096, 88), (257, 130, 1032, 4), (700, 1000, 4096, 12), (4100, 1032, 520, 12)])
+def test_product_whose_weight_tiles_are_shared_between_teams(ops16, T, N, K, share):
+    """More than 256 tokens, a product that is added to its output: the k blocks of all weight tiles
+    are shared out among teams of CTAs (`share` blocks a team, asked for here; 0: what the library
+    takes by itself), and a tile whose inner dimension two or more teams hold gets their parts added in
+    the order of their k blocks.  Against float64 (with the stored and the gated product of the same
+    sizes, which take tiles in turn); twice, bit for bit; the counters of finished parts back at zero;
+    and the same without the counters (tiles in turn)."""
+    import ctypes
+    from ctypes import c_void_p
+    from rbitnet_b200.kernels import ops as ops_module
+    ops16.lib.call("rb_gemm_tc_share_for_test", share, launches=0)
+    try:
+        _shared_product_case(ops16, ops_module, T, N, K, share)
+    finally:
+        ops16.lib.call("rb_gemm_tc_share_for_test", 0, launches=0)
+
+
+def _shared_product_case(ops16, ops_module, T, N, K, share):
+    import ctypes
+    from ctypes import c_void_p
+    plan = (ctypes.c_int * 4)()
+    sms = ops16.lib.raw("rb_device_sm_count")()
+    ops16.lib.call("rb_gemm_tc_plan", T, N, K, 0, sms, 1, plan, launches=0)
+    assert plan[1] > 0 and (share == 0 or plan[1] == share), "these sizes were chosen to share weight tiles"
+    ws = ops_module._GEMM_WORKSPACES[torch.cuda.current_device()]
+    counters = ws[:ops_module._GEMM_COUNTER_BYTES].view(torch.int32)
+    g = torch.Generator(device="cuda").manual_seed(14)
+    x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    ref = x.double() @ w.double().T
+    lw = ops16.prepare_linear([w])
+    acc0 = torch.randn(T, N, device="cuda", generator=g)
+    F = N // 2
+    wg, wu = w[:F] * 2, w[F:2 * F]
+    gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+    gu = ops16.prepare_gate_up(wg, wu)
+
+    def run():
+        stored = ops16.linear(x, lw, out_dtype=F32)
+        acc = acc0.clone()
+        ops16.linear(x, lw, accumulate_into=acc, scale=0.5)
+        return stored, acc, ops16.gated_linear(x, gu)
+
+    first = run()
+    assert int(counters.abs().max()) == 0
+    assert _rel(first[0], ref) < 2e-5
+    assert _rel(first[1], acc0.double() + 0.5 * ref) < 2e-5
+    assert _rel(first[2], gate / (1 + torch.exp(-gate)) * up) < 6e-3
+    again = run()
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)
+    ops16.lib.call("rb_gemm_tc_set_workspace", c_void_p(0), 0, launches=0)
+    try:
+        in_turn = run()
+    finally:
+        ops16.lib.call("rb_gemm_tc_set_workspace", c_void_p(ws.data_ptr()), ws.numel(), launches=0)
+    assert _rel(in_turn[0], ref) < 2e-5 and _rel(in_turn[1], acc0.double() + 0.5 * ref) < 2e-5
+    assert _rel(in_turn[2], gate / (1 + torch.exp(-gate)) * up) < 6e-3
+    assert int(counters.abs().max()) == 0
+    ops16.check_errors()
