@@ -346,6 +346,9 @@ class KernelTimer:
         el = lambda t: t.numel() * t.element_size()
         if name in ("linear", "gated_linear", "project_rotate_append"):
             x, w = a[0], a[1]
+            pending = hasattr(x, "squares")       # rows with their norm pending: the bfloat16 rows and the sums of squares
+            extra = el(x.squares) if pending else 0
+            x = x.scaled if pending else x
             T, K = x.shape
             N = w.w.shape[0]
             n_out = getattr(w, "inner", N)
@@ -356,7 +359,12 @@ class KernelTimer:
                     "project_rotate_append": "q/k/v product + rotation + append"}[name]
             if kw.get("accumulate_into") is not None:
                 kind = "product + residual"
-            return f"{kind} [{T}x{K}]x[{N}x{K}]", el(w.w) + el(x) + out_b, 2.0 * T * N * K
+            if pending:
+                kind = "norm's factor, " + kind
+            if kw.get("then_norm") is not None and T <= 16:
+                kind += " + next norm's rows"
+                extra += T * n_out * 2
+            return f"{kind} [{T}x{K}]x[{N}x{K}]", el(w.w) + el(x) + out_b + extra, 2.0 * T * N * K
         if name == "attention":
             q, meta, view, H = a[0], a[1], a[2], a[3]
             T, _, D = q.shape

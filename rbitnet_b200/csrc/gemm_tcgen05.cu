@@ -81,6 +81,19 @@ struct GemmParams {
   int sk_len;         // 64-wide k blocks per team of CTAs
   int n_w_tiles;      // 128-row tiles of W
   int* sk_finished;   // [weight tile][token tile]: parts of the tile that are in C; zero between launches
+  // A norm that whoever made X left pending (norm_ss != nullptr; token tiles of at most 64): X holds
+  // the rows times the norm's weights, and the finished sums of token t are multiplied by
+  // 1 / sqrt(sum over parts of norm_ss[part][t] / norm_width + norm_eps).
+  const float* norm_ss;
+  int norm_parts;
+  float norm_width, norm_eps;
+  // EPI_ADD in a cluster, for the norm that follows: also leaves bfloat16(C_new * emit_g[column]) in
+  // emit_xb [tokens, emit_ld] and the sums of squares of C_new over every warp's 32 columns in
+  // emit_ss [4 * weight tiles][tokens].
+  __nv_bfloat16* emit_xb;
+  int64_t emit_ld;
+  const float* emit_g;
+  float* emit_ss;
   QkvTail qkv;        // EPI_QKV only
 };
 
@@ -153,6 +166,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   __shared__ uint64_t accum_empty[NBUF];
   __shared__ uint32_t tmem_holder;
   __shared__ int epi_fail;
+  __shared__ float norm_r[64];         // per token: the factor of a pending norm
 
   rb_pdl_launch_dependents();     // the next kernel may be set up while this one runs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,6 +323,21 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     const bool issuer = warp == 2 && lane == 0;      // the one thread that sends the boxes of TMA_EPI
     rb_pdl_wait();                       // before C is read or written
+    const bool normed = !TMA_EPI && p.norm_ss != nullptr;
+    if (normed) {
+      // (the parts are summed in their order, by one thread per token: the same sum in every CTA)
+      const int t = (int)threadIdx.x - 64;
+      if (t < 64) {
+        float r = 1.0f;
+        if (t < p.n_tokens) {
+          float ss = 0.f;
+          for (int q = 0; q < p.norm_parts; ++q) ss += p.norm_ss[(int64_t)q * p.n_tokens + t];
+          r = 1.0f / sqrtf(ss / p.norm_width + p.norm_eps);
+        }
+        norm_r[t] = r;
+      }
+      asm volatile("bar.sync 3, 128;" ::: "memory");
+    }
     uint32_t n_boxes = 0;
     Piece s;
     for (int li = 0; piece_at(li, s); ++li) {
@@ -439,7 +468,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (c + 16 < BN) fetch_old(c + 16, ahead);       // the next chunk's loads are in flight during these stores
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (j < t_left) dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]) * p.alpha;
+              if (j < t_left)
+                dst[(int64_t)j * p.ldc] = old[j] + __uint_as_float(r[j]) * (normed ? p.alpha * norm_r[t0 + c + j] : p.alpha);
           } else if (EPI == EPI_GATED) {
             // as above, each lane storing its own values
             const bool low = lane < 16;
@@ -451,7 +481,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               const float mine = __uint_as_float(low ? r[j] : r[j + 1]);
               const float send = __uint_as_float(low ? r[j + 1] : r[j]);
               const float got = __shfl_xor_sync(0xffffffffu, send, 16);
-              const float g = low ? mine : got, up = low ? got : mine;
+              const float rr = normed ? norm_r[t0 + c + j + (low ? 0 : 1)] : 1.0f;       // my token's pending norm
+              const float g = (low ? mine : got) * rr, up = (low ? got : mine) * rr;
               const float v = __fdividef(g, 1.0f + __expf(-g)) * up;
               if (j + (low ? 0 : 1) < f_left) store_out<OutT>(dst + (int64_t)j * p.ldc, v);
             }
@@ -459,7 +490,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             OutT* dst = (OutT*)p.C + (int64_t)(t0 + c) * p.ldc + n;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (j < t_left) store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]) * p.alpha);
+              if (j < t_left)
+                store_out<OutT>(dst + (int64_t)j * p.ldc, __uint_as_float(r[j]) * (normed ? p.alpha * norm_r[t0 + c + j] : p.alpha));
           }
         }
       }
@@ -532,12 +564,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       asm volatile("bar.sync 2, 128;" ::: "memory");                 // the four epilogue warps
       if (live) {
         const float inv = is_v ? 0.f : q.inv_freq[pair];
+        const bool normed = p.norm_ss != nullptr;
         for (int col = my; col < BN && t0 + col < p.n_tokens; col += p.splits) {
-          const float x = sums[col * BM + row];
           const int t = t0 + col, pos = q.tok_pos[t];
+          const float rr = normed ? norm_r[t] : 1.0f;            // a pending norm of the input rows
+          const float x = sums[col * BM + row] * rr;
           float y = x;
           if (!is_v) {
-            const float xp = sums[col * BM + prow];
+            const float xp = sums[col * BM + prow] * rr;
             float sn, cs;
             sincosf((float)pos * inv, &sn, &cs);
             y = first ? x * cs - xp * sn : xp * sn + x * cs;
@@ -564,7 +598,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
       for (int r = 0; r < 8; ++r)
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote[r]) : "r"(red), "r"((uint32_t)(r < p.splits ? r : 0)));
-      if (n < p.n_out) {
+      // (every lane walks the loop, also one whose weight row is beyond the matrix: the warp adds up
+      // squares together below)
+      const bool n_in = n < p.n_out;
+      const bool normed = p.norm_ss != nullptr;
+      const bool emit = EPI == EPI_ADD && p.emit_xb != nullptr;
+      const float g_n = emit && n_in ? p.emit_g[n] : 0.f;
+      {
         constexpr int CPI = BN >= 64 ? 8 : (BN >= 32 ? 4 : 2);      // columns whose loads are in flight together
         for (int cb = 0; cb < BN; cb += CPI * p.splits) {
           int col[CPI];
@@ -573,7 +613,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
           for (int h = 0; h < CPI; ++h) {
             col[h] = cb + h * p.splits + my;
-            ok[h] = col[h] < BN && t0 + col[h] < p.n_tokens;
+            ok[h] = n_in && col[h] < BN && t0 + col[h] < p.n_tokens;
             old[h] = 0.f;
             if (EPI == EPI_ADD && ok[h]) old[h] = ((const float*)p.C)[(int64_t)(t0 + col[h]) * p.ldc + n];
           }
@@ -587,14 +627,29 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
 #pragma unroll
           for (int h = 0; h < CPI; ++h) {
-            if (!ok[h]) continue;
-            float v = part[h][0];
+            const bool column = col[h] < BN && t0 + col[h] < p.n_tokens;       // the same in every lane
+            float now = 0.f;
+            if (ok[h]) {
+              float v = part[h][0];
 #pragma unroll
-            for (int r = 1; r < 8; ++r) v += part[h][r];
-            v *= p.alpha;
-            const int64_t at = (int64_t)(t0 + col[h]) * p.ldc + n;
-            if (EPI == EPI_ADD) ((float*)p.C)[at] = old[h] + v;
-            else store_out<OutT>((OutT*)p.C + at, v);
+              for (int r = 1; r < 8; ++r) v += part[h][r];
+              v *= normed ? p.alpha * norm_r[t0 + col[h]] : p.alpha;
+              const int64_t at = (int64_t)(t0 + col[h]) * p.ldc + n;
+              if (EPI == EPI_ADD) {
+                now = old[h] + v;
+                ((float*)p.C)[at] = now;
+                if (emit) p.emit_xb[(int64_t)(t0 + col[h]) * p.emit_ld + n] = __float2bfloat16_rn(now * g_n);
+              } else {
+                store_out<OutT>((OutT*)p.C + at, v);
+              }
+            }
+            if (emit && column) {
+              // the squares of this warp's 32 columns of C, lane 0 .. lane 31 in a fixed tree
+              float sq = now * now;
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+              if (lane == 0) p.emit_ss[(int64_t)((n0 / BM) * 4 + quarter) * p.n_tokens + t0 + col[h]] = sq;
+            }
           }
         }
       }
@@ -912,6 +967,38 @@ RB_EXPORT int rb_gemm_tc_plan(int n_tokens, int n_out, int K, int token_tile, in
   return 0;
 }
 
+// ---------------------------------------------------------------- a norm between two products
+// The product that adds to the residual stream can leave what the norm after it needs, and the
+// product after the norm can finish it, so that a decode step has no kernel for the norm: see
+// GemmParams.  Both requests hold for the NEXT rb_gemm_tc or rb_gemm_tc_qkv call of the calling
+// thread and are forgotten after it, whether it succeeded or not.
+namespace {
+struct NormOptions {
+  const float* in_ss = nullptr; int in_parts = 0; float in_width = 0.f, in_eps = 0.f;
+  void* out_xb = nullptr; int64_t out_ld = 0; const float* out_g = nullptr; float* out_ss = nullptr;
+};
+thread_local NormOptions t_norm;
+}  // namespace
+
+// The rows of X are rows * norm weight with the norm's factor pending: ss [parts, n_tokens] float32
+// holds sums of squares of the rows (over `width` values in all).  At most 64 tokens.
+RB_EXPORT int rb_gemm_tc_pending_norm(const float* ss, int parts, float width, float eps) {
+  RB_REQUIRE(ss != nullptr && parts > 0 && width > 0.f, "rb_gemm_tc_pending_norm: bad arguments");
+  t_norm.in_ss = ss; t_norm.in_parts = parts; t_norm.in_width = width; t_norm.in_eps = eps;
+  return 0;
+}
+
+// The next product (epilogue 1, K split into a cluster) also leaves bfloat16(C_new * g[column]) in
+// xb [n_tokens, ld] and sums of squares of C_new in ss [rb_gemm_tc_norm_parts(n_out), n_tokens].
+RB_EXPORT int rb_gemm_tc_leave_norm(void* xb, int64_t ld, const float* g, float* ss) {
+  RB_REQUIRE(xb != nullptr && g != nullptr && ss != nullptr && ld > 0, "rb_gemm_tc_leave_norm: bad arguments");
+  t_norm.out_xb = xb; t_norm.out_ld = ld; t_norm.out_g = g; t_norm.out_ss = ss;
+  return 0;
+}
+
+// Rows of the sums of squares that rb_gemm_tc_leave_norm fills for n_out output columns.
+RB_EXPORT int rb_gemm_tc_norm_parts(int n_out) { return 4 * ((n_out + BM - 1) / BM); }
+
 // C (+)= X W^T on the tensor cores.
 //   epilogue 0: C[tokens, n_out] = alpha * product, c_dtype float32 or bfloat16
 //   epilogue 1: C (float32) += alpha * product
@@ -924,6 +1011,8 @@ RB_EXPORT int rb_gemm_tc_plan(int n_tokens, int n_out, int K, int token_tile, in
 static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx, int n_tokens, const void* W,
                    int64_t ldw, int w_rows, int n_out, int K, int epilogue, int n_features, int splits,
                    int token_tile, const QkvTail* tail, float alpha, cudaStream_t stream) {
+  const NormOptions norm = t_norm;
+  t_norm = NormOptions();
   if (n_tokens == 0 || n_out == 0) return 0;
   RB_REQUIRE(alpha == 1.0f || epilogue == EPI_STORE || epilogue == EPI_ADD, "rb_gemm_tc: alpha %g with epilogue %d", alpha, epilogue);
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
@@ -967,6 +1056,12 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   p.n_t_tiles = n_t_tiles; p.splits = splits; p.n_items = (int)items;
   p.cluster = splits > 1 ? 1 : 0;
   p.alpha = alpha;
+  p.norm_ss = norm.in_ss; p.norm_parts = norm.in_parts; p.norm_width = norm.in_width; p.norm_eps = norm.in_eps;
+  RB_REQUIRE(norm.in_ss == nullptr || (bn <= 64 && n_tokens <= 64),
+             "rb_gemm_tc: a pending norm with %d tokens in tiles of %d (at most 64)", n_tokens, bn);
+  p.emit_xb = (__nv_bfloat16*)norm.out_xb; p.emit_ld = norm.out_ld; p.emit_g = norm.out_g; p.emit_ss = norm.out_ss;
+  RB_REQUIRE(norm.out_xb == nullptr || (epilogue == EPI_ADD && p.cluster),
+             "rb_gemm_tc: only an added product whose K is split into a cluster leaves a norm's inputs");
   p.n_w_tiles = n_w_tiles;
   p.sk_len = plan.sk_len;
   p.sk_finished = (int*)ws.ptr;

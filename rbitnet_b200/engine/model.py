@@ -97,8 +97,16 @@ class Model:
         """Runs the step's tokens; returns float32 logits [wanted rows, vocab] or None."""
         ops, meta = ctx.ops, ctx.meta
         x = ops.embed(meta.token_ids, self.embedding, self.embedding_scale)   # float32 residual stream [T, E]
-        for e, entry in enumerate(self.spec.schedule):
-            self.blocks[entry.layer].run(ctx, x, e)
+        schedule, pending = self.spec.schedule, None
+        for e, entry in enumerate(schedule):
+            block = self.blocks[entry.layer]
+            if not getattr(block, "chains_norms", False):
+                block.run(ctx, x, e)
+                continue
+            # a block that can hand the rows of the next block's first norm on (see parts/block.py)
+            after = self.blocks[schedule[e + 1].layer] if e + 1 < len(schedule) else None
+            next_norm = after.first_norm() if getattr(after, "chains_norms", False) else None
+            pending = block.run(ctx, x, e, pending=pending, next_norm=next_norm)
         if meta.n_want == 0:
             return None
         rows = x if meta.want_every_row else ops.gather_rows(x, meta.want_rows)

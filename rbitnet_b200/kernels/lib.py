@@ -68,6 +68,9 @@ class KernelLibrary:
         self.declare("rb_gemm_tc_set_workspace", [P, L])
         self.declare("rb_gemm_tc_plan", [I, I, I, I, I, I, P])
         self.declare("rb_gemm_tc_share_for_test", [I])
+        self.declare("rb_gemm_tc_pending_norm", [P, I, F, F])
+        self.declare("rb_gemm_tc_leave_norm", [P, L, P, P])
+        self.declare("rb_gemm_tc_norm_parts", [I])
         self.declare("rb_device_sm_count", [])
         self.declare("rb_is_checked_build", [])
         for tu in CHECKED_FILES:

@@ -47,6 +47,33 @@ class GateUpWeight:
     block: int = 0
 
 
+@dataclass
+class NormRequest:
+    """Asks the product that adds to the residual stream to leave what the norm after it needs
+    (``CudaOps.linear(..., then_norm=request)``).  ``result`` is the ``NormedRows`` if it did."""
+    weight: torch.Tensor          # float32 [width]
+    eps: float
+    result: Optional["NormedRows"] = None
+
+
+@dataclass
+class NormedRows:
+    """Rows of the residual stream with an RMS norm pending: a product that takes them multiplies its
+    finished sums by each row's 1/sqrt(mean of squares + eps) (``CudaOps.linear``, ``gated_linear`` and
+    ``project_rotate_append`` take them in place of the normed rows; ``CudaOps.normed`` gives the normed
+    rows themselves).  The norm is the same float32 arithmetic either way; what is rounded to bfloat16
+    is row * weight instead of row * factor * weight."""
+    x: torch.Tensor               # the rows themselves, float32 [T, width]
+    weight: torch.Tensor          # float32 [width]
+    eps: float
+    scaled: torch.Tensor          # bfloat16 [T, width]: x * weight
+    squares: torch.Tensor         # float32 [parts, T]: sums of squares of x over parts of the width
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
 #: per device: the workspace of the tensor-core products (arrival counters, then partial sums of
 #: tiles whose inner dimension is shared between teams of CTAs).  One per process and device, never
 #: freed: the library keeps its address.
@@ -88,6 +115,9 @@ class CudaOps:
         #: decode attention of head sizes 64 and 128 gets its keys and values by TMA (else by cp.async)
         self.decode_on_tma = True
         self._flag_ptrs = None
+        #: a decode step's norms between two products are folded into them (see ``NormedRows``)
+        self.fold_norms = True
+        self.fold_norms_up_to = 16
         #: tensor-core products of more than 256 tokens may share a weight tile's inner dimension
         #: between teams of CTAs (needs the workspace; tiles are taken in turn without it)
         _give_gemm_workspace(self.lib, self.device)
@@ -171,10 +201,18 @@ class CudaOps:
         self.lib.call("rb_rmsnorm", _ptr(out), _CODE[out.dtype], _ptr(x), _ptr(w), T, E, float(eps), self._stream())
         return out
 
-    def linear(self, x: torch.Tensor, weight: LinearWeight, out_dtype=None,
-               accumulate_into: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    def linear(self, x, weight: LinearWeight, out_dtype=None, accumulate_into: Optional[torch.Tensor] = None,
+               scale: float = 1.0, then_norm: Optional[NormRequest] = None) -> torch.Tensor:
         """scale * x[T, in] * W[out, in]^T (the scale multiplies the finished float32 sums).  With
-        ``accumulate_into`` (float32 [T, out]) the product is added to it in float32 and it is returned."""
+        ``accumulate_into`` (float32 [T, out]) the product is added to it in float32 and it is returned.
+        ``x`` may be ``NormedRows``.  ``then_norm``: see ``NormRequest`` (granted for a few tokens, where
+        the product's parts along the inner dimension meet on chip)."""
+        pending = x if isinstance(x, NormedRows) else None
+        if pending is not None:
+            if self._takes_pending(pending, weight.w):
+                x = pending.scaled
+            else:
+                x, pending = self.normed(pending), None
         self._check(x, self.dtype, "linear input")
         T, K = x.shape
         if K != weight.n_in:
@@ -188,13 +226,49 @@ class CudaOps:
         if self._tensor_core_ok(x, weight.w):
             # few tokens and few weight tiles: K is cut into parts so that every SM streams a piece
             # of W; the parts of a tile are one thread-block cluster and are summed on chip
+            splits = self._k_splits(T, N, K)
+            if pending is not None:
+                self._pending_norm(pending)
+            # (up to 16 tokens: measured at batch 1 and 8 a step gains 2.8 and 1.5 %, at batch 64 it loses 1 %:
+            # the norm's kernel also was the time in which the next product's first tiles of W arrived)
+            if then_norm is not None and acc and splits >= 2 and T <= self.fold_norms_up_to and out.is_contiguous():
+                then_norm.result = self._leave_norm(out, then_norm, T, N)
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0), T,
-                          _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, self._k_splits(T, N, K),
+                          _ptr(weight.w), weight.w.stride(0), N, N, K, acc, 0, splits,
                           64 if 64 < T <= 256 else 0, float(scale), self._stream())
         else:
             self.lib.call("rb_gemm_simple", _ptr(out), out.stride(0), _CODE[out.dtype], _ptr(x), x.stride(0),
                           _ptr(weight.w), weight.w.stride(0), self.code, T, N, K, acc, float(scale), self._stream())
         return out
+
+    # ------------------------------------------------------------------ a norm between two products
+    def norm_request(self, weight: torch.Tensor, eps: float) -> Optional[NormRequest]:
+        """A request for ``linear(..., then_norm=)``, or None where norms are not folded into products
+        (the float32 path keeps every norm a kernel of its own)."""
+        if self.dtype != torch.bfloat16 or not self.fold_norms:
+            return None
+        return NormRequest(weight, float(eps))
+
+    def normed(self, rows: NormedRows) -> torch.Tensor:
+        """The normed rows themselves, for whoever does not take ``NormedRows``."""
+        return self.rmsnorm(rows.x, rows.weight, rows.eps)
+
+    def _takes_pending(self, rows: NormedRows, w: torch.Tensor) -> bool:
+        return (self.dtype == torch.bfloat16 and rows.scaled.shape[0] <= 64 and self._tensor_core_ok(rows.scaled, w))
+
+    def _pending_norm(self, rows: NormedRows) -> None:
+        """For the next tensor-core product of this thread."""
+        self.lib.call("rb_gemm_tc_pending_norm", _ptr(rows.squares), rows.squares.shape[0], float(rows.x.shape[1]),
+                      float(rows.eps), launches=0)
+
+    def _leave_norm(self, out: torch.Tensor, request: NormRequest, T: int, N: int) -> NormedRows:
+        """For the next tensor-core product of this thread (one that adds into ``out``)."""
+        parts = self.lib.raw("rb_gemm_tc_norm_parts")(N)
+        scaled = torch.empty((T, N), dtype=torch.bfloat16, device=self.device)
+        squares = torch.empty((parts, T), dtype=torch.float32, device=self.device)
+        self.lib.call("rb_gemm_tc_leave_norm", _ptr(scaled), scaled.stride(0), _ptr(request.weight), _ptr(squares),
+                      launches=0)
+        return NormedRows(out, request.weight, request.eps, scaled, squares)
 
     def _k_splits(self, T: int, N: int, K: int) -> int:
         """Parts to cut the inner dimension into: the library's choice for this device (1 beyond 256
@@ -211,12 +285,20 @@ class CudaOps:
 
     def gated_linear(self, x: torch.Tensor, weight: GateUpWeight) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) -> [T, inner] in the compute dtype."""
+        pending = x if isinstance(x, NormedRows) else None
+        if pending is not None:
+            if weight.block == 16 and self._takes_pending(pending, weight.w):
+                x = pending.scaled
+            else:
+                x, pending = self.normed(pending), None
         T = x.shape[0]
         out = torch.empty((T, weight.inner), dtype=self.dtype, device=self.device)
         rows = weight.w.shape[0]
         if weight.block == 16 and self._tensor_core_ok(x, weight.w):
             # one accumulator per tile; gate and up of a feature meet in the epilogue, and the
             # activation and the product happen on the way out
+            if pending is not None:
+                self._pending_norm(pending)
             self.lib.call("rb_gemm_tc", _ptr(out), out.stride(0), self.code, _ptr(x), x.stride(0), T,
                           _ptr(weight.w), weight.w.stride(0), rows, rows, weight.n_in, 3, weight.inner, 1, 0,
                           1.0, self._stream())
@@ -249,6 +331,12 @@ class CudaOps:
         """q/k/v product of the normed rows ``h``, rotation by position and cache append; returns the
         rotated q [T, H, D].  For a few tokens (a decode step) the product's own epilogue rotates and
         appends, from its float32 sums; otherwise the product is stored and ``rotate_append`` follows."""
+        pending = h if isinstance(h, NormedRows) else None
+        if pending is not None:
+            if self._takes_pending(pending, weight.w):
+                h = pending.scaled
+            else:
+                h, pending = self.normed(pending), None
         T, K = h.shape
         D, Kh = view.head_dim, view.n_kv_heads
         splits = self._k_splits(T, weight.n_out, K)
@@ -260,12 +348,14 @@ class CudaOps:
                 and weight.n_out == (n_heads + (2 * Kh if view.writes else 0)) * D
                 and self.lib.raw("rb_gemm_tc_qkv_supports")(T, D, splits)):
             q = torch.empty((T, n_heads, D), dtype=self.dtype, device=self.device)
+            if pending is not None:
+                self._pending_norm(pending)
             self.lib.call("rb_gemm_tc_qkv", _ptr(q), _ptr(h), h.stride(0), T, _ptr(weight.w), weight.w.stride(0), K,
                           splits, _ptr(inv_freq), _ptr(meta.tok_pos), _ptr(meta.tok_slot), _ptr(view.k), _ptr(view.v),
                           _ptr(view.page_table), view.max_pages, view.page_size, n_heads, Kh, D,
                           1 if view.writes else 0, 1 if interleaved else 0, rot_dim, self._stream())
             return q
-        return self.rotate_append(self.linear(h, weight), rotary, meta, view, n_heads)
+        return self.rotate_append(self.linear(pending if pending is not None else h, weight), rotary, meta, view, n_heads)
 
     def _zeros_freq(self, D):
         z = getattr(self, "_zf", None)

@@ -44,7 +44,10 @@ class Attention(Mixer):
         self.w_q = None  # for a run that reads another layer's cache: the q rows of w_qkv, as a view
         self.w_o = ops.prepare_linear([weights["o"]])
 
-    def forward(self, ctx, h, entry, accumulate_into):
+    #: ``h`` may be rows with their norm pending, and ``then_norm`` is handed to the last product
+    folds_norms = True
+
+    def forward(self, ctx, h, entry, accumulate_into, then_norm=None):
         ops = ctx.ops
         view = ctx.cache_view(entry)
         if view.writes:
@@ -55,7 +58,10 @@ class Attention(Mixer):
             w = self.w_q
         q = ops.project_rotate_append(h, w, self.position.rotary(), ctx.meta, view, self.n_heads)
         a = ops.attention(q, ctx.meta, view, self.n_heads, self.scale, self.window)
-        ops.linear(a, self.w_o, accumulate_into=accumulate_into)
+        if then_norm is None:
+            ops.linear(a, self.w_o, accumulate_into=accumulate_into)
+        else:
+            ops.linear(a, self.w_o, accumulate_into=accumulate_into, then_norm=then_norm)
 
 
 register_part("mixer", "attention", Attention)

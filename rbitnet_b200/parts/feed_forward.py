@@ -22,9 +22,15 @@ class GatedDense(FeedForward):
         self.w_gate_up = ops.prepare_gate_up(weights["gate"], weights["up"])
         self.w_down = ops.prepare_linear([weights["down"]])
 
-    def forward(self, ctx, h, accumulate_into):
+    #: ``h`` may be rows with their norm pending, and ``then_norm`` is handed to the last product
+    folds_norms = True
+
+    def forward(self, ctx, h, accumulate_into, then_norm=None):
         t = ctx.ops.gated_linear(h, self.w_gate_up)        # silu(gate h) * (up h)
-        ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into)
+        if then_norm is None:
+            ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into)
+        else:
+            ctx.ops.linear(t, self.w_down, accumulate_into=accumulate_into, then_norm=then_norm)
 
 
 register_part("feed_forward", "gated_dense", GatedDense)

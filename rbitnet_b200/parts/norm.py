@@ -23,5 +23,11 @@ class RMSNorm(Norm):
     def forward(self, ctx, x):
         return ctx.ops.rmsnorm(x, self.weight, self.eps)
 
+    def deferred(self, ops):
+        """What a product before this norm needs to prepare it, if the operations can fold a norm
+        into the products around it (see ``PreNormBlock``); else None."""
+        make = getattr(ops, "norm_request", None)
+        return make(self.weight, self.eps) if make is not None else None
+
 
 register_part("norm", "rmsnorm", RMSNorm)

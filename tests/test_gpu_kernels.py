@@ -370,10 +370,14 @@ def test_rotation_and_cache_append(ops32, ops16, H, Kh, D, interleaved):
 @pytest.mark.parametrize("H,Kh,D,interleaved,K,T,writes", [
     (4, 2, 16, True, 512, 5, True), (3, 1, 32, False, 1024, 6, True), (8, 8, 64, False, 2048, 1, True),
     (6, 2, 128, True, 4096, 6, True), (5, 1, 64, False, 1024, 6, False), (2, 1, 128, False, 520, 40, True)])
-def test_qkv_product_that_rotates_and_appends_in_its_epilogue(ops16, H, Kh, D, interleaved, K, T, writes):
+@pytest.mark.parametrize("pending", [False, True])
+def test_qkv_product_that_rotates_and_appends_in_its_epilogue(ops16, H, Kh, D, interleaved, K, T, writes, pending):
     """The q/k/v product of a few tokens whose epilogue rotates q and k and writes k and v into the paged
-    cache, against the product in float64 followed by the rotation; and the step's own choice of path."""
+    cache, against the product in float64 followed by the rotation; and the step's own choice of path.
+    ``pending``: the input rows come with their norm pending (rows times the norm's weights, and sums of
+    squares in three parts), and the product multiplies its sums by each row's factor."""
     from rbitnet_b200.cache import CacheLayerView
+    from rbitnet_b200.kernels.ops import NormedRows
     theta = 10000.0 if interleaved else 500000.0
     page, max_pages, n_slots = 16, 8, 6
     places = [(0, 0), (0, 1), (2, 100), (1, 15), (1, 16), (2, 127)]
@@ -393,8 +397,19 @@ def test_qkv_product_that_rotates_and_appends_in_its_epilogue(ops16, H, Kh, D, i
     splits = ops16._k_splits(T, n_out, K)
     fused = bool(ops16.lib.raw("rb_gemm_tc_qkv_supports")(T, D, splits))
     assert fused == (splits >= 2 and T <= 16), (splits, fused)
+    given = h
+    if pending:
+        rows_f = torch.randn(T, K, device="cuda", generator=g) * 3.0
+        gw = 1.0 + 0.5 * torch.randn(K, device="cuda", generator=g)
+        eps = 1e-5
+        scaled = (rows_f * gw).to(BF16)
+        cut = torch.rand(3, T, device="cuda", generator=g)
+        squares = (cut / cut.sum(0)) * (rows_f * rows_f).sum(-1)
+        given = NormedRows(rows_f, gw, eps, scaled, squares.contiguous())
+        factor = 1.0 / torch.sqrt((rows_f.double() ** 2).mean(-1) + eps)
+        h = scaled.double() * factor[:, None]                # what the product should see, in float64
     before = ops16.lib.launches
-    q = ops16.project_rotate_append(h, lw, (inv, interleaved, D), meta, view, H)
+    q = ops16.project_rotate_append(given, lw, (inv, interleaved, D), meta, view, H)
     assert ops16.lib.launches - before == (1 if fused else 2)
     ops16.check_errors()
 
@@ -691,4 +706,62 @@ def _shared_product_case(ops16, ops_module, T, N, K, share):
     assert _rel(in_turn[0], ref) < 2e-5 and _rel(in_turn[1], acc0.double() + 0.5 * ref) < 2e-5
     assert _rel(in_turn[2], gate / (1 + torch.exp(-gate)) * up) < 6e-3
     assert int(counters.abs().max()) == 0
+    ops16.check_errors()
+
+
+@pytest.mark.parametrize("T,E,K,F", [(1, 256, 4096, 352), (5, 1000, 520, 176), (16, 4096, 1024, 1000),
+                                     (33, 520, 2048, 352), (64, 1032, 4096, 500), (8, 4096, 14336, 2000)])
+def test_norm_folded_into_the_products_around_it(ops16, T, E, K, F):
+    """The product that adds to the residual stream leaves the rows times the next norm's weights and
+    their sums of squares; the stored, the added and the gated product take those and multiply their
+    sums by each row's factor.  Each against float64, and against the norm kernel followed by the same
+    product."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    ops16.fold_norms_up_to = 64            # (a step folds up to 16 tokens; the kernels take 64)
+    try:
+        _folded_norm_case(ops16, g, T, E, K, F)
+    finally:
+        ops16.fold_norms_up_to = 16
+
+
+def _folded_norm_case(ops16, g, T, E, K, F):
+    x0 = torch.randn(T, E, device="cuda", generator=g) * 2.0
+    a = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    w_o = (torch.randn(E, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    gw = 1.0 + 0.5 * torch.randn(E, device="cuda", generator=g)
+    eps = 1e-5
+    request = ops16.norm_request(gw, eps)
+    assert request is not None
+    x = x0.clone()
+    ops16.linear(a, ops16.prepare_linear([w_o]), accumulate_into=x, then_norm=request)
+    ref_x = x0.double() + a.double() @ w_o.double().T
+    assert _rel(x, ref_x) < 2e-5
+    rows = request.result
+    assert (rows is not None) == (ops16._k_splits(T, E, K) >= 2)
+    if rows is None:
+        pytest.skip("these sizes do not split the inner dimension on this device")
+    assert rows.x is x and rows.squares.shape[0] == 4 * -(-E // 128)
+    assert _rel(rows.squares.sum(0), (x.double() ** 2).sum(-1)) < 1e-5
+    assert _rel(rows.scaled, x.double() * gw.double()) < 4e-3             # one rounding to bfloat16
+    factor = 1.0 / torch.sqrt((x.double() ** 2).mean(-1) + eps)
+    h = rows.scaled.double() * factor[:, None]                             # what the next product should see
+    plain = ops16.rmsnorm(x, gw, eps)                                      # the norm as a kernel of its own
+    assert _rel(plain, h) < 8e-3
+
+    for N in (F, 4096):                     # few weight tiles (the inner dimension is split) and many
+        w1 = (torch.randn(N, E, device="cuda", generator=g) / math.sqrt(E)).to(BF16)
+        lw1 = ops16.prepare_linear([w1])
+        ref = h @ w1.double().T
+        assert _rel(ops16.linear(rows, lw1, out_dtype=F32), ref) < 2e-5
+        assert _rel(ops16.linear(rows, lw1, out_dtype=F32, scale=0.25), 0.25 * ref) < 2e-5
+        assert _rel(ops16.linear(plain, lw1, out_dtype=F32), ref) < 8e-3
+        acc0 = torch.randn(T, N, device="cuda", generator=g)
+        acc = acc0.clone()
+        ops16.linear(rows, lw1, accumulate_into=acc)
+        assert _rel(acc, acc0.double() + ref) < 2e-5
+    wg = (torch.randn(F, E, device="cuda", generator=g) / math.sqrt(E) * 2).to(BF16)
+    wu = (torch.randn(F, E, device="cuda", generator=g) / math.sqrt(E)).to(BF16)
+    gate, up = h @ wg.double().T, h @ wu.double().T
+    t = ops16.gated_linear(rows, ops16.prepare_gate_up(wg, wu))
+    assert _rel(t, gate / (1 + torch.exp(-gate)) * up) < 6e-3
     ops16.check_errors()
