@@ -64,6 +64,12 @@ struct QkvTail {
   int rot_dim;               // the first rot_dim values of a head are rotated, the rest pass unchanged
 };
 
+// The kernel's third tensor map, that of the output, exists only where the output leaves by TMA:
+// elsewhere the parameter is one word.
+template <bool BY_TMA> struct OutputMap { using type = CUtensorMap; };
+template <> struct OutputMap<false> { struct type { int none; }; };
+template <int BN, int EPI> constexpr bool leaves_by_tma() { return BN >= 128 && EPI != EPI_QKV; }
+
 struct GemmParams {
   void* C;            // output
   int64_t ldc;        // row stride of C in elements
@@ -81,7 +87,7 @@ struct GemmParams {
   int sk_len;         // 64-wide k blocks per team of CTAs
   int n_w_tiles;      // 128-row tiles of W
   int* sk_finished;   // [weight tile][token tile]: parts of the tile that are in C; zero between launches
-  // A norm that whoever made X left pending (norm_ss != nullptr; token tiles of at most 64): X holds
+  // A norm that whoever made X left pending (norm_ss != nullptr; token tiles of 16): X holds
   // the rows times the norm's weights, and the finished sums of token t are multiplied by
   // 1 / sqrt(sum over parts of norm_ss[part][t] / norm_width + norm_eps).
   const float* norm_ss;
@@ -138,7 +144,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 __global__ void __launch_bounds__(192, MINB)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-               const __grid_constant__ CUtensorMap tmC, GemmParams p) {
+               const __grid_constant__ typename OutputMap<leaves_by_tma<BN, EPI>()>::type tmC, GemmParams p) {
   constexpr int X_TILE_BYTES = BN * BK * 2;
   constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
   constexpr int ACC_COLS = BN;
@@ -151,7 +157,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // system), two boxes in flight.  Stores a thread makes itself have one chunk of loads or stores in
   // flight per thread, about 8 KB an SM, and an epilogue of a 128 x 256 tile then takes longer than
   // the products of a short tile.
-  constexpr bool TMA_EPI = BN >= 128 && EPI != EPI_QKV;
+  constexpr bool TMA_EPI = leaves_by_tma<BN, EPI>();
+  // A pending norm of the input rows and what a later norm needs (see GemmParams) are compiled for the
+  // 16-token tile only, which is where a step uses them: present in the 64-token tile's kernels, asked
+  // for or not, they cost each product of a batch of 64 about half a microsecond.
+  constexpr bool PENDING_NORM = BN <= 16;
   constexpr int OUT_COLS = EPI == EPI_GATED ? BM / 2 : BM;          // values per token row of a staged box
   constexpr int OUT_STAGE_BYTES = 16 * BM * 4;                      // room for 16 rows of float32
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N");
@@ -323,7 +333,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     const bool issuer = warp == 2 && lane == 0;      // the one thread that sends the boxes of TMA_EPI
     rb_pdl_wait();                       // before C is read or written
-    const bool normed = !TMA_EPI && p.norm_ss != nullptr;
+    const bool normed = PENDING_NORM && p.norm_ss != nullptr;
     if (normed) {
       // (the parts are summed in their order, by one thread per token: the same sum in every CTA)
       const int t = (int)threadIdx.x - 64;
@@ -564,7 +574,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       asm volatile("bar.sync 2, 128;" ::: "memory");                 // the four epilogue warps
       if (live) {
         const float inv = is_v ? 0.f : q.inv_freq[pair];
-        const bool normed = p.norm_ss != nullptr;
+        const bool normed = PENDING_NORM && p.norm_ss != nullptr;
         for (int col = my; col < BN && t0 + col < p.n_tokens; col += p.splits) {
           const int t = t0 + col, pos = q.tok_pos[t];
           const float rr = normed ? norm_r[t] : 1.0f;            // a pending norm of the input rows
@@ -601,8 +611,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       // (every lane walks the loop, also one whose weight row is beyond the matrix: the warp adds up
       // squares together below)
       const bool n_in = n < p.n_out;
-      const bool normed = p.norm_ss != nullptr;
-      const bool emit = EPI == EPI_ADD && p.emit_xb != nullptr;
+      const bool normed = PENDING_NORM && p.norm_ss != nullptr;
+      constexpr bool CAN_EMIT = EPI == EPI_ADD && PENDING_NORM;
+      const bool emit = CAN_EMIT && p.emit_xb != nullptr;
       const float g_n = emit && n_in ? p.emit_g[n] : 0.f;
       {
         constexpr int CPI = BN >= 64 ? 8 : (BN >= 32 ? 4 : 2);      // columns whose loads are in flight together
@@ -758,6 +769,8 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, 
   constexpr int smem = STAGES * stage_bytes + 1024 + (BN >= 128 ? 2 * 16 * BM * 4 : 0);
   static_assert(smem * MINB <= 227 * 1024, "shared memory");
   auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT, MINB>;
+  typename OutputMap<leaves_by_tma<BN, EPI>()>::type out_map;
+  if constexpr (leaves_by_tma<BN, EPI>()) out_map = tc; else out_map.none = 0;
   static RbOncePerDevice configured;
   if (configured.first()) {
     RB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -778,7 +791,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = rb_pdl_enabled() ? 2 : 1;
-    RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tw, tx, tc, p));
+    RB_CUDA(cudaLaunchKernelEx(&cfg, kernel, tw, tx, out_map, p));
     return 0;
   }
   const int slots = rb_sm_count() * MINB;
@@ -787,7 +800,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, 
     RB_REQUIRE(BN >= 128 && EPI != EPI_QKV && p.n_items <= slots, "rb_gemm_tc: shared ranges with a token tile of %d, %d CTAs", BN, p.n_items);
     grid = p.n_items;                                    // one CTA per team and token tile
   }
-  RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, tc, p);
+  RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, out_map, p);
   RB_CHECK_LAUNCH("rb_gemm_tc");
   return 0;
 }
@@ -981,14 +994,14 @@ thread_local NormOptions t_norm;
 }  // namespace
 
 // The rows of X are rows * norm weight with the norm's factor pending: ss [parts, n_tokens] float32
-// holds sums of squares of the rows (over `width` values in all).  At most 64 tokens.
+// holds sums of squares of the rows (over `width` values in all).  At most 16 tokens.
 RB_EXPORT int rb_gemm_tc_pending_norm(const float* ss, int parts, float width, float eps) {
   RB_REQUIRE(ss != nullptr && parts > 0 && width > 0.f, "rb_gemm_tc_pending_norm: bad arguments");
   t_norm.in_ss = ss; t_norm.in_parts = parts; t_norm.in_width = width; t_norm.in_eps = eps;
   return 0;
 }
 
-// The next product (epilogue 1, K split into a cluster) also leaves bfloat16(C_new * g[column]) in
+// The next product (epilogue 1, at most 16 tokens, K split into a cluster) also leaves bfloat16(C_new * g[column]) in
 // xb [n_tokens, ld] and sums of squares of C_new in ss [rb_gemm_tc_norm_parts(n_out), n_tokens].
 RB_EXPORT int rb_gemm_tc_leave_norm(void* xb, int64_t ld, const float* g, float* ss) {
   RB_REQUIRE(xb != nullptr && g != nullptr && ss != nullptr && ld > 0, "rb_gemm_tc_leave_norm: bad arguments");
@@ -1057,11 +1070,11 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   p.cluster = splits > 1 ? 1 : 0;
   p.alpha = alpha;
   p.norm_ss = norm.in_ss; p.norm_parts = norm.in_parts; p.norm_width = norm.in_width; p.norm_eps = norm.in_eps;
-  RB_REQUIRE(norm.in_ss == nullptr || (bn <= 64 && n_tokens <= 64),
-             "rb_gemm_tc: a pending norm with %d tokens in tiles of %d (at most 64)", n_tokens, bn);
+  RB_REQUIRE(norm.in_ss == nullptr || (bn <= 16 && n_tokens <= 16),
+             "rb_gemm_tc: a pending norm with %d tokens in tiles of %d (at most 16 tokens)", n_tokens, bn);
   p.emit_xb = (__nv_bfloat16*)norm.out_xb; p.emit_ld = norm.out_ld; p.emit_g = norm.out_g; p.emit_ss = norm.out_ss;
-  RB_REQUIRE(norm.out_xb == nullptr || (epilogue == EPI_ADD && p.cluster),
-             "rb_gemm_tc: only an added product whose K is split into a cluster leaves a norm's inputs");
+  RB_REQUIRE(norm.out_xb == nullptr || (epilogue == EPI_ADD && p.cluster && bn <= 16),
+             "rb_gemm_tc: only an added product of at most 16 tokens whose K is split into a cluster leaves a norm's inputs");
   p.n_w_tiles = n_w_tiles;
   p.sk_len = plan.sk_len;
   p.sk_finished = (int*)ws.ptr;

@@ -254,7 +254,7 @@ class CudaOps:
         return self.rmsnorm(rows.x, rows.weight, rows.eps)
 
     def _takes_pending(self, rows: NormedRows, w: torch.Tensor) -> bool:
-        return (self.dtype == torch.bfloat16 and rows.scaled.shape[0] <= 64 and self._tensor_core_ok(rows.scaled, w))
+        return (self.dtype == torch.bfloat16 and rows.scaled.shape[0] <= 16 and self._tensor_core_ok(rows.scaled, w))
 
     def _pending_norm(self, rows: NormedRows) -> None:
         """For the next tensor-core product of this thread."""
