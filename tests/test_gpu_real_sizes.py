@@ -153,3 +153,34 @@ def test_bfloat16_against_float32_at_eight_layers():
     assert_close(outs["bfloat16"], outs["float32"], "bfloat16", "8 layers, bfloat16 against float32", rtol=bf16_rtol(8))
     agree = (outs["bfloat16"].argmax(1) == outs["float32"].argmax(1)).float().mean()
     assert agree >= 0.5, f"only {agree:.2f} of the arg-max agree"
+
+
+@pytest.mark.parametrize("name", ["llama3_8b", "tinyllama"])
+def test_a_decode_steps_norms_in_the_products_around_them_or_as_kernels(made, name):
+    """Up to 16 tokens a step's norms between two products ride in those products: two kernels fewer per
+    layer (but for the first layer's first norm), and logits that differ from the same step with every norm
+    a kernel only by where bfloat16 rounds (row x weight, or row x factor x weight)."""
+    from rbitnet_b200 import StepEntry
+    eng, ref = made(name, "bfloat16")
+    L = SHAPES[name]["num_hidden_layers"]
+    p = prompts([60], SHAPES[name]["vocab_size"], seed=9)[0]
+    got, launches = {}, {}
+    try:
+        for fold in (True, False):
+            eng.ops.fold_norms = fold
+            s = eng.new_sequence()
+            eng.step([StepEntry(s, p[:40], [])])
+            rows = []
+            for t in p[40:]:
+                before = eng.ops.lib.launches
+                rows.append(eng.step([StepEntry(s, [t], [0])]))           # (not captured: a captured step keeps its path)
+                launches[fold] = eng.ops.lib.launches - before
+            eng.end_sequence(s)
+            got[fold] = torch.cat(rows)
+    finally:
+        eng.ops.fold_norms = True
+    assert launches[False] - launches[True] == 2 * L - 1, launches
+    want = ref.logits(p, list(range(40, 60)))
+    assert_close(got[True], want, "bfloat16", f"{name} folded norms", rtol=bf16_rtol(L))
+    assert_close(got[False], want, "bfloat16", f"{name} norms as kernels", rtol=bf16_rtol(L))
+    assert_close(got[True], got[False].double().cpu(), "bfloat16", f"{name} folded against kernels", rtol=bf16_rtol(L))
