@@ -21,6 +21,10 @@
 // and SiLU(gate)*up (model.rs:297-302) from ONE accumulator: the caller interleaves the rows of the
 // gate and up matrices in blocks of 16, so that each warp of the epilogue holds 16 gate rows in its
 // lower lanes and the 16 up rows of the same features in its upper lanes, and a shuffle pairs them.
+// Token tiles of 128 and more leave through shared memory as TMA boxes (an added product is added by
+// the memory system), and an added product of many tokens may share its weight tiles between teams
+// of CTAs; for up to 16 tokens the RMS norm between two products (model.rs:93-100) rides in their
+// epilogues.  The kernel's own comment has each of these.
 //
 // Every wait on an mbarrier is bounded: after about two seconds the waiting thread records an
 // error code in a device word and the CTA leaves through the common exit, freeing its tensor
@@ -797,7 +801,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, 
   const int slots = rb_sm_count() * MINB;
   int grid = p.n_items < slots ? p.n_items : slots;     // resident CTAs take items in turn
   if (p.sk_len > 0) {
-    RB_REQUIRE(BN >= 128 && EPI != EPI_QKV && p.n_items <= slots, "rb_gemm_tc: shared ranges with a token tile of %d, %d CTAs", BN, p.n_items);
+    RB_REQUIRE(BN >= 128 && EPI == EPI_ADD && p.n_items <= slots, "rb_gemm_tc: shared ranges with a token tile of %d, %d CTAs", BN, p.n_items);
     grid = p.n_items;                                    // one CTA per team and token tile
   }
   RB_LAUNCH("kernel", (kernel), grid, 192, smem, stream, tw, tx, out_map, p);
@@ -860,6 +864,23 @@ __global__ void wait_probe_kernel(unsigned long long limit_ns, int code, int* __
     const bool ok = mbar_wait(&bar, 0, code, limit_ns);
     if (gave_up != nullptr) *gave_up = ok ? 0 : 1;
   }
+}
+
+// The same for the wait on a count in global memory (a tile's finished parts): `word` holds zero and
+// nobody ever stores the one that the thread waits for.
+__global__ void count_wait_probe_kernel(const int* __restrict__ word, unsigned long long limit_ns, int code,
+                                        int* __restrict__ gave_up) {
+  if (threadIdx.x == 0) {
+    const bool ok = wait_for_count(word, 1, code, limit_ns);
+    if (gave_up != nullptr) *gave_up = ok ? 0 : 1;
+  }
+}
+
+RB_EXPORT int rb_count_wait_probe(const int* word, long long limit_ns, int code, int* gave_up, cudaStream_t stream) {
+  RB_REQUIRE(word != nullptr && limit_ns > 0 && limit_ns <= 100000000ll, "rb_count_wait_probe: limit %lld ns (at most 0.1 s)", limit_ns);
+  count_wait_probe_kernel<<<1, 32, 0, stream>>>(word, (unsigned long long)limit_ns, code, gave_up);
+  RB_CHECK_LAUNCH("rb_count_wait_probe");
+  return 0;
 }
 
 RB_EXPORT int rb_wait_probe(long long limit_ns, int code, int* gave_up, cudaStream_t stream) {

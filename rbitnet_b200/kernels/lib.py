@@ -36,6 +36,7 @@ _SIGNATURES = {
     "rb_attention_decode_static": [P, P, P, P, P, I, I, P, P, I, I, I, I, F, I, I, P],
     "rb_set_error_flag_for_test": [I],
     "rb_wait_probe": [L, I, P, P],
+    "rb_count_wait_probe": [P, L, I, P, P],
 }
 
 

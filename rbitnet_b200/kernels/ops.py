@@ -141,7 +141,7 @@ class CudaOps:
             if ws is not None:
                 ws[:_GEMM_COUNTER_BYTES].zero_()      # a product that gave up may have left counts behind
             raise KernelError(f"a kernel gave up waiting (code {v.value}: 1 = loader, 2 = tensor-core issuer, "
-                              "3 = epilogue); its results are not valid")
+                              "3 = epilogue, 4 = the parts of a shared weight tile); its results are not valid")
         if self.lib.raw("rb_is_checked_build")():
             from .lib import CHECKED_FILES
             w = (ctypes.c_int * 4)()

@@ -239,6 +239,17 @@ def test_a_bounded_wait_gives_up_and_says_so():
     ops.check_errors()                                          # cleared by the read above
     with pytest.raises(KernelError, match="at most 0.1 s"):
         ops.lib.call("rb_wait_probe", 3_000_000_000, 7, ctypes.c_void_p(gave_up.data_ptr()), ops._stream())
+    # the wait on a count in global memory (the finished parts of a shared weight tile), same limit, same word
+    zero = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gave_up.zero_()
+    t0 = time.time()
+    ops.lib.call("rb_count_wait_probe", ctypes.c_void_p(zero.data_ptr()), 1_000_000, 4,
+                 ctypes.c_void_p(gave_up.data_ptr()), ops._stream())
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0 and int(gave_up[0]) == 1
+    with pytest.raises(KernelError, match="code 4"):
+        ops.check_errors()
+    ops.check_errors()
     # the context is as usable as before
     assert int((torch.ones(4, device="cuda") * 2).sum()) == 8
 
