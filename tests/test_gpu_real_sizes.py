@@ -184,3 +184,28 @@ def test_a_decode_steps_norms_in_the_products_around_them_or_as_kernels(made, na
     assert_close(got[True], want, "bfloat16", f"{name} folded norms", rtol=bf16_rtol(L))
     assert_close(got[False], want, "bfloat16", f"{name} norms as kernels", rtol=bf16_rtol(L))
     assert_close(got[True], got[False].double().cpu(), "bfloat16", f"{name} folded against kernels", rtol=bf16_rtol(L))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_prompt_of_the_benchmark_s_length_at_the_benchmark_s_layer_sizes(dtype):
+    """2,048 tokens in one step at the Llama-3-8B layer sizes (two layers), then three tokens one by one: the
+    products of many tokens (tiles that leave as TMA boxes, weight tiles shared between teams of CTAs) and
+    the tcgen05 attention over 16 key tiles, against the plain model in float64 at places all along the
+    prompt."""
+    from rbitnet_b200 import Engine, StepEntry
+    cfg = dict(SHAPES["llama3_8b"], max_position_embeddings=4096)
+    c, tensors = _tensors(cfg, 33, dtype)
+    p = prompts([2051], cfg["vocab_size"], seed=5)[0]
+    eng = Engine(c, dict(tensors), dtype=dtype, max_tokens=2304, max_seq=2304)
+    s = eng.new_sequence()
+    places = [0, 1, 127, 128, 255, 256, 1000, 1023, 1024, 1500, 2046, 2047]
+    rows = [eng.step([StepEntry(s, p[:2048], places)])]
+    for t in p[2048:]:
+        rows.append(eng.step([StepEntry(s, [t], [0])]))
+    eng.end_sequence(s)
+    got = torch.cat(rows).double().cpu()
+    del eng
+    torch.cuda.empty_cache()
+    want = plain.forward(cfg, tensors, list(p), torch.float64)[torch.as_tensor(places + [2048, 2049, 2050], device="cuda")].cpu()
+    rtol = bf16_rtol(cfg["num_hidden_layers"]) if dtype == "bfloat16" else None
+    assert_close(got, want, dtype, "2,048 tokens at the 8B layer sizes", rtol=rtol)
