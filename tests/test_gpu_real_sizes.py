@@ -209,3 +209,24 @@ def test_a_prompt_of_the_benchmark_s_length_at_the_benchmark_s_layer_sizes(dtype
     want = plain.forward(cfg, tensors, list(p), torch.float64)[torch.as_tensor(places + [2048, 2049, 2050], device="cuda")].cpu()
     rtol = bf16_rtol(cfg["num_hidden_layers"]) if dtype == "bfloat16" else None
     assert_close(got, want, dtype, "2,048 tokens at the 8B layer sizes", rtol=rtol)
+
+
+def test_one_prompt_cut_into_steps_in_seven_ways_at_the_benchmark_s_layer_sizes():
+    """1,500 tokens of the Llama-3-8B layer sizes (two layers, bfloat16) whole, and cut so that the cuts
+    fall on both sides of every choice the products make (tiles of 16 and 64, 257 tokens, shared weight
+    tiles, one token at the end): the logits at the last position against the plain model in float64."""
+    from rbitnet_b200 import Engine, StepEntry
+    cfg = dict(SHAPES["llama3_8b"], max_position_embeddings=4096)
+    c, tensors = _tensors(cfg, 33, "bfloat16")
+    eng = Engine(c, dict(tensors), dtype="bfloat16", max_tokens=4096, max_seq=2304)
+    p = prompts([1500], cfg["vocab_size"], seed=8)[0]
+    want = plain.forward(cfg, tensors, list(p), torch.float64)[-1:].cpu()
+    ways = ([1500], [300, 1200], [700, 800], [64] * 23 + [28], [257, 256, 255, 732], [1499, 1], [1000, 499, 1],
+            [16] * 93 + [12])
+    for cuts in ways:
+        s, at, out = eng.new_sequence(), 0, None
+        for n in cuts:
+            out = eng.step([StepEntry(s, p[at:at + n], [n - 1])])
+            at += n
+        eng.end_sequence(s)
+        assert_close(out, want, "bfloat16", f"cut as {cuts[:4]}... ({len(cuts)} steps)", rtol=bf16_rtol(cfg["num_hidden_layers"]))
