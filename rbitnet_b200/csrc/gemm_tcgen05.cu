@@ -598,7 +598,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
       }
     }
-    if (EPI != EPI_GATED && EPI != EPI_QKV && warp >= 2 && first_item < p.n_items) {   // (the gated product is never split)
+    if (EPI != EPI_QKV && warp >= 2 && first_item < p.n_items) {
       // every CTA of the cluster adds up a share of the token columns (column c belongs to rank
       // c mod splits), reading all parts of a column in split order through distributed shared memory
       Piece pc;
@@ -643,6 +643,19 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
           for (int h = 0; h < CPI; ++h) {
             const bool column = col[h] < BN && t0 + col[h] < p.n_tokens;       // the same in every lane
+            if (EPI == EPI_GATED) {
+              // lanes 0..15 hold the gate sums of 16 features, lanes 16..31 their up sums (see the epilogue
+              // above): every lane adds up its parts, the halves meet by a shuffle, the lower lanes finish
+              float v = part[h][0];
+#pragma unroll
+              for (int r = 1; r < 8; ++r) v += part[h][r];
+              if (normed) v *= norm_r[column ? t0 + col[h] : 0];
+              const float up = __shfl_xor_sync(0xffffffffu, v, 16);
+              const int f = (n0 + quarter * 32) / 2 + (lane & 15);
+              if (ok[h] && lane < 16 && f < p.n_features)
+                store_out<OutT>((OutT*)p.C + (int64_t)(t0 + col[h]) * p.ldc + f, __fdividef(v, 1.0f + __expf(-v)) * up);
+              continue;
+            }
             float now = 0.f;
             if (ok[h]) {
               float v = part[h][0];
@@ -767,12 +780,15 @@ int rb_get_output_map(CUtensorMap* out, const void* ptr, long long rows, int col
 
 namespace {
 
+thread_local int t_kernels_launched = 0;     // by this thread's product calls, for tests
+
 template <int BN, int STAGES, int EPI, typename OutT, int MINB>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
   constexpr int stage_bytes = W_TILE_BYTES + BN * BK * 2;
   constexpr int smem = STAGES * stage_bytes + 1024 + (BN >= 128 ? 2 * 16 * BM * 4 : 0);
   static_assert(smem * MINB <= 227 * 1024, "shared memory");
   auto kernel = gemm_wx_kernel<BN, STAGES, EPI, OutT, MINB>;
+  ++t_kernels_launched;
   typename OutputMap<leaves_by_tma<BN, EPI>()>::type out_map;
   if constexpr (leaves_by_tma<BN, EPI>()) out_map = tc; else out_map.none = 0;
   static RbOncePerDevice configured;
@@ -913,6 +929,7 @@ struct SkWorkspace { void* ptr = nullptr; long long bytes = 0; };
 SkWorkspace g_sk_ws[64];
 std::mutex g_sk_mu;
 int g_sk_len_for_test = 0;       // > 0: k blocks per team whatever the estimate says (tests)
+int g_tail_for_test = 0;         // < 0: a last round of few tiles stays in the one product (tests, measurements)
 
 double item_cost(int bn) { return 0.4 + 0.6 * bn / 256.0; }
 
@@ -991,6 +1008,15 @@ RB_EXPORT int rb_gemm_tc_share_for_test(int blocks_per_team) {
   return 0;
 }
 
+// Kernels that this thread's rb_gemm_tc and rb_gemm_tc_qkv calls have launched so far (a product may be two).
+RB_EXPORT int rb_gemm_tc_kernels_launched() { return t_kernels_launched; }
+
+// For tests and measurements: -1 keeps a last round of few tiles in the one product; 0 takes it back.
+RB_EXPORT int rb_gemm_tc_tail_for_test(int mode) {
+  g_tail_for_test = mode;
+  return 0;
+}
+
 // What rb_gemm_tc would do with these sizes on a device of `sms` SMs: out = {token tile, k blocks
 // per team (0: tiles in turn), teams, token tiles}.  `shared_ok`: an added product (epilogue 1) on a
 // device that has its counters.  No device is touched.
@@ -1052,7 +1078,6 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   RB_REQUIRE(n_tokens > 0 && n_out > 0 && K > 0, "rb_gemm_tc: bad sizes tokens=%d out=%d K=%d", n_tokens, n_out, K);
   RB_REQUIRE(K % 8 == 0, "rb_gemm_tc: inner size %d is not a multiple of 8", K);
   RB_REQUIRE(splits >= 1, "rb_gemm_tc: splits %d", splits);
-  RB_REQUIRE(epilogue != EPI_GATED || splits == 1, "rb_gemm_tc: the gated product cannot split K");
   RB_REQUIRE(splits <= 8, "rb_gemm_tc: at most 8 splits are summed on the device (%d asked)", splits);
   const int nkb = (K + BK - 1) / BK;
   RB_REQUIRE(splits <= nkb, "rb_gemm_tc: %d splits for %d blocks of K", splits, nkb);
@@ -1072,6 +1097,41 @@ static int gemm_tc(void* C, int64_t ldc, int c_dtype, const void* X, int64_t ldx
   const int bn = plan.bn;
   RB_REQUIRE(epilogue != EPI_GATED || (n_out % 32 == 0 && n_features > 0 && n_features <= n_out / 2),
              "rb_gemm_tc: the gated product wants rows in blocks of 32 (%d rows, %d features)", n_out, n_features);
+  // A last round of few tiles.  Tiles in turn pay a whole round of the SMs for it (2,048 tokens times
+  // 28,672 rows: 1,792 tiles are twelve rounds of 148 SMs and 16 tiles, whatever power of two times
+  // 224 the tiles are).  The weight tiles that whole rounds hold stay one product; the few that are
+  // left become a second one on all SMs: token tiles of 64, K cut into a cluster, as for few tokens.
+  if (token_tile == 0 && bn >= 128 && splits == 1 && plan.sk_len == 0 && g_tail_for_test >= 0 &&
+      (epilogue == EPI_GATED || epilogue == EPI_STORE)) {
+    const long long sms = rb_sm_count(), w_tiles = (n_out + BM - 1) / BM, n_t = (n_tokens + bn - 1) / bn;
+    const long long items = w_tiles * n_t, rounds = (items + sms - 1) / sms, left = items - (rounds - 1) * sms;
+    const long long w_main = (rounds - 1) * sms / n_t, w_tail = w_tiles - w_main;
+    const long long tail_tiles = w_tail * ((n_tokens + 63) / 64);
+    int parts = 1;
+    while (parts * 2 <= 8 && tail_tiles * parts * 2 <= 2 * sms && parts * 2 <= nkb / 4) parts *= 2;
+    // What the second product costs against the round it replaces, in microseconds.  Its tiles of 64 tokens
+    // are bound by what they fetch, every token tile its own copy of the rows of W (128 + 64 rows of K
+    // values a tile, at about 5 TB/s from L2), plus its start and its cluster's sum; a round is an item's k
+    // blocks at 0.4 us each for 256 tokens.  Measured at 4,096 values of K and 28,672 rows: 300 tokens 87 us
+    // instead of 99, 512 106 instead of 117, 1,024 171 instead of 180, 1,500 241 instead of 242; at 2,048 and
+    // 4,096 tokens the second product would be the longer one (314 against 311, 620 against 598).
+    const double tail_us = (double)tail_tiles * (BM + 64) * K * 2 / 5e6 + 4.0;
+    const double round_us = nkb * 0.4 * item_cost(bn);
+    if (rounds >= 2 && left * 4 <= sms && w_main >= 1 && w_tail >= 1 && parts >= 2 && tail_us < 0.8 * round_us) {
+      const int rows_main = (int)w_main * BM;
+      const int64_t out_off = epilogue == EPI_GATED ? rows_main / 2 : rows_main;       // columns of C the main product fills
+      const int feat_main = epilogue == EPI_GATED ? (n_features < out_off ? n_features : (int)out_off) : 0;
+      if (gemm_tc(C, ldc, c_dtype, X, ldx, n_tokens, W, ldw, rows_main, rows_main, K, epilogue, feat_main, 1, bn, nullptr,
+                  alpha, stream) != 0)
+        return -1;
+      if (epilogue == EPI_GATED && n_features <= out_off) return 0;                      // the rest is padding rows
+      char* c_tail = (char*)C + out_off * out_elem;
+      const char* w_rest = (const char*)W + (int64_t)rows_main * ldw * 2;
+      const int per = (nkb + parts - 1) / parts;
+      return gemm_tc(c_tail, ldc, c_dtype, X, ldx, n_tokens, w_rest, ldw, w_rows - rows_main, n_out - rows_main, K, epilogue,
+                     epilogue == EPI_GATED ? n_features - (int)out_off : 0, (nkb + per - 1) / per, 64, nullptr, alpha, stream);
+    }
+  }
   CUtensorMap tw, tx;
   if (rb_get_tensor_map(&tw, W, w_rows, K, ldw, BM) != 0) return -1;
   if (rb_get_tensor_map(&tx, X, n_tokens, K, ldx, bn) != 0) return -1;

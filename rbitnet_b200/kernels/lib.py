@@ -69,6 +69,8 @@ class KernelLibrary:
         self.declare("rb_gemm_tc_set_workspace", [P, L])
         self.declare("rb_gemm_tc_plan", [I, I, I, I, I, I, P])
         self.declare("rb_gemm_tc_share_for_test", [I])
+        self.declare("rb_gemm_tc_tail_for_test", [I])
+        self.declare("rb_gemm_tc_kernels_launched", [])
         self.declare("rb_gemm_tc_pending_norm", [P, I, F, F])
         self.declare("rb_gemm_tc_leave_norm", [P, L, P, P])
         self.declare("rb_gemm_tc_norm_parts", [I])

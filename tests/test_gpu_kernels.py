@@ -765,3 +765,41 @@ def test_norm_folded_into_the_products_around_it(ops16, T, E, K, F):
     t = ops16.gated_linear(rows, ops16.prepare_gate_up(wg, wu))
     assert _rel(t, gate / (1 + torch.exp(-gate)) * up) < 6e-3
     ops16.check_errors()
+
+
+@pytest.mark.parametrize("T,F,K", [(512, 14336, 2048), (300, 14336, 2048), (300, 14330, 4096)])
+def test_a_last_round_of_few_tiles_becomes_a_product_of_its_own(ops16, T, F, K):
+    """Tiles that are a few more than whole rounds of the SMs (448 = 3 x 148 + 4 here): the weight tiles of
+    the whole rounds stay one product, the few that are left become a second one with token tiles of 64
+    whose K is cut into a cluster; the gated product (whose cluster sum pairs gate and up) and the stored
+    one, against float64, with and without the second product."""
+    sms = ops16.lib.raw("rb_device_sm_count")()
+    if sms != 148:
+        pytest.skip("the sizes are chosen for 148 SMs")
+    g = torch.Generator(device="cuda").manual_seed(15)
+    x = torch.randn(T, K, device="cuda", generator=g).to(BF16)
+    wg = (torch.randn(F, K, device="cuda", generator=g) / math.sqrt(K) * 2).to(BF16)
+    wu = (torch.randn(F, K, device="cuda", generator=g) / math.sqrt(K)).to(BF16)
+    gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = gate / (1 + torch.exp(-gate)) * up
+    gu = ops16.prepare_gate_up(wg, wu)
+    ws = torch.cat([wg, wu])[:28672]
+    lw = ops16.prepare_linear([ws])
+    want_s = x.double() @ ws.double().T
+    launched = ops16.lib.raw("rb_gemm_tc_kernels_launched")
+    got, kernels = {}, {}
+    try:
+        for mode in (0, -1):
+            ops16.lib.call("rb_gemm_tc_tail_for_test", mode, launches=0)
+            before = launched()
+            got[mode] = (ops16.gated_linear(x, gu), ops16.linear(x, lw, out_dtype=F32))
+            kernels[mode] = launched() - before
+    finally:
+        ops16.lib.call("rb_gemm_tc_tail_for_test", 0, launches=0)
+    # both products in two kernels each; but a gated output whose rows TMA cannot address (14,330 bfloat16
+    # values) takes token tiles of 64 from the start, in one kernel
+    assert kernels[-1] == 2 and kernels[0] == (4 if F % 8 == 0 else 3), kernels
+    for mode in (0, -1):
+        assert _rel(got[mode][0], want) < 6e-3
+        assert _rel(got[mode][1], want_s) < 2e-5
+    ops16.check_errors()
