@@ -54,8 +54,8 @@ def test_requests_are_refused_with_a_message(lib):
     from rbitnet_b200.kernels.lib import KernelError
     with pytest.raises(KernelError, match="multiple of 8"):
         lib.call("rb_gemm_tc", 0, 50, 1, 0, 77, 9, 0, 77, 50, 50, 77, 0, 0, 1, 0, 1.0, 0)
-    with pytest.raises(KernelError, match="cannot split K"):
-        lib.call("rb_gemm_tc", 0, 64, 1, 0, 64, 8, 0, 64, 64, 64, 128, 3, 32, 2, 0, 1.0, 0)
+    with pytest.raises(KernelError, match="rows in blocks of 32"):
+        lib.call("rb_gemm_tc", 0, 64, 1, 0, 64, 8, 0, 64, 48, 48, 128, 3, 24, 1, 0, 1.0, 0)
     with pytest.raises(KernelError, match="at most 8 splits"):
         lib.call("rb_gemm_tc", 0, 64, 1, 0, 1024, 8, 0, 1024, 64, 64, 1024, 0, 0, 9, 0, 1.0, 0)
     with pytest.raises(KernelError, match="head_dim"):
